@@ -1,0 +1,170 @@
+/* FBLA compressed-KV attention for NVIDIA B200 (sm_100a): the C interface.
+ *
+ * This header is ABI-identical to the interface of mlops-attention 0.4.0 (reference: attention/include/mlops_fbla.h:1-189):
+ * the same type names, field order and sizes, enum values, function names and argument orders, so a program written
+ * against that header links against this library unchanged. The text below is a restatement; the layout facts it
+ * gives are the contract the kernels and the tests are written from.
+ *
+ * Model. Head dimension 128. The tokens of one KV head form groups of 128. A group that is complete and has been
+ * followed by at least one more token is "closed": every element x of K and of V is stored as a 6-bit code c with
+ *     x ~ base[channel] + c * step[channel],        c in 0..63,
+ * base = the channel's minimum over the group rounded down to BF16, step = fl32((max - base) * fl32(1/63)) rounded up
+ * to BF16, c = clamp(rint(fl32(fl32(x - base) * fl32(1/step))), 0, 63) (c = 0 where step is 0). The code is split in
+ * two planes: the coarse plane keeps the top CB bits (h = c >> FB), the fine plane the low FB bits (f = c & (2^FB-1));
+ * CB+FB is 3+3 or 4+2. An element read without its fine bits decodes to the middle of its coarse cell,
+ * base + step * (2^FB * h + (2^FB - 1) / 2). Group 0 (the attention sink) and the newest group (still filling) are
+ * additionally kept as BF16 and are always read as BF16.
+ *
+ * Decode reads all coarse planes once, and the fine planes only of those 16-token sub-blocks whose share of a
+ * query's softmax mass (estimated from the coarse scores) exceeds tau. Scores use a per-(query, group) int8 query:
+ * z = q * step_K (exact in FP32), qhat = rint(z * fl32(127 / max|z|)), sq = max|z| * sl / 127, sl = fl32(scale*log2 e):
+ *     score(log2 units) = sq * (qhat . code) + sl * (q . base_K).
+ * Softmax weights are formed per 16-token sub-block as integers p = round(255 * 2^(s - max_block)).
+ */
+#ifndef MLOPS_FBLA_H
+#define MLOPS_FBLA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef MLOPS_FBLA_NO_CUDA_RUNTIME /* host tools that only need the types (the CPU oracle, ctypes mirrors) */
+typedef struct CUstream_st *cudaStream_t;
+#else
+#include <cuda_runtime.h>
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference: mlops_fbla.h:29 */
+enum { MLOPS_FBLA_HEAD_DIM = 128, MLOPS_FBLA_GROUP = 128, MLOPS_FBLA_SUBBLOCK = 16 };
+
+/* reference: mlops_fbla.h:37-45 */
+typedef enum {
+  MLOPS_FBLA_3P3 = 0, /* 3 coarse + 3 fine bits; default tau 3e-4 */
+  MLOPS_FBLA_4P2 = 1  /* 4 coarse + 2 fine bits; default tau 1e-3 */
+} mlops_fbla_format;
+typedef enum {
+  MLOPS_FBLA_OK = 0,
+  MLOPS_FBLA_INVALID_VALUE = 1,
+  MLOPS_FBLA_CUDA_ERROR = 2
+} mlops_fbla_status;
+
+/* The cache of one attention layer (reference: mlops_fbla.h:47-73). All pointers are device memory owned by the caller.
+ *
+ * coarse / fine: one record per 16-token sub-block, 2*bits*256 bytes (bits = CB resp. FB: 1536, 2048 or 1024 bytes),
+ *   holding K and V of the sub-block's 16 tokens. 32 lanes own a record; lane l owns, per tensor, 16 slots of 4 codes:
+ *     K: lane l = token l%16, slot s, byte b  -> channel 64*(l/16) + 4*s + b
+ *     V: lane l = channels 4l..4l+3, slot s, byte b -> channel 4l + c(s), token 4*j(s) + b with (c, j) =
+ *        4 bit: s<8: (s%2, s/2); s>=8: (2 + s%2, (s-8)/2)      2 bit: s = 4m+k: (m, k)
+ *        3 bit: s=0..3: (0, s); s=4,5: (2, s-4); s=6..9: (1, s-6); s=10,11: (2, s-8); s=12..15: (3, s-12)
+ *   A lane's 16 slots of one tensor occupy 2*bits 32-bit words W[], packed per byte position:
+ *     4 bit: slot s<8 in bits 0-3 of W[s]; slot 8+k in bits 4-7 of W[k]
+ *     2 bit: slot 4m+k in bits 2m..2m+1 of W[k]
+ *     3 bit: slot s<6 in bits 0-2 of W[s]; slot 6+k (k<6) in bits 3-5 of W[k]; slot 12+r: code bits 0-1 in bits 6-7
+ *            of W[r], code bit 2 in bit 6 + r%2 of W[4 + r/2]
+ *   Byte offset of word w of lane l inside the record:
+ *     4 bit: K w<4: 16l+4w; K w>=4: 512+16l+4(w-4); V: the same + 1024
+ *     2 bit: K: 16l+4w; V: 512+16l+4w
+ *     3 bit: w<4: K 16l+4w, V 512+16l+4w; w=4,5: K 1024 + 16(l%16) + 8(l/16) + 4(w-4), V 1280 + 8l + 4(w-4)
+ * meta: 512 BF16 (1 KiB) per group: lane l's K base[4] then step[4] for channels 4l..4l+3 at byte 16l; V's at 512+16l.
+ * exact_sink_* / exact_open_*: [batch, kv_heads, 128, 128] BF16; the open group's tokens are rows 0..n-1.
+ * Unit placement: the 8 records (planes) / the KiB (meta) of (head h = b*kv_heads + kh, group g) is unit number
+ *   h*head_stride + g*group_stride; the defaults (0, 0) mean head_stride = groups of the capacity, group_stride = 1.
+ * tc_images: optional persistent prefill images of the reference's mma.sync prefill; this library keeps none
+ *   (mlops_fbla_images_bytes returns 0) and ignores the pointer beyond checking its alignment. */
+typedef struct {
+  uint8_t *coarse, *fine;
+  uint16_t *meta;
+  uint16_t *exact_sink_k, *exact_sink_v, *exact_open_k, *exact_open_v;
+  uint8_t *tc_images;
+} mlops_fbla_cache;
+
+/* reference: mlops_fbla.h:75-88 */
+typedef struct {
+  int batch, q_heads, kv_heads, tokens;
+  float scale;   /* 0: 1/sqrt(128) */
+  float tau;     /* refinement threshold on a sub-block's share of the softmax mass; 0: the format's default */
+  mlops_fbla_format format;
+  int capacity;  /* tokens the planes and metadata are laid out for; 0: tokens */
+  int head_stride, group_stride; /* units between KV heads / groups; 0, 0: the capacity's dense layout */
+  /* prefill output placement (BF16 elements): element (q head h, position i) at h*out_head_stride + i*out_token_stride;
+   * 0, 0: [batch, q_heads, count, 128]. Both nonzero requires batch 1 and multiples of 8. */
+  int64_t out_head_stride, out_token_stride;
+  int length_stride; /* the *_at calls: 0 = one device length for all batch rows, 1 = length[b] per row */
+} mlops_fbla_config;
+
+/* reference: mlops_fbla.h:111-116 */
+typedef struct {
+  size_t coarse, fine, meta;
+  size_t exact; /* each of the four exact planes */
+  size_t images;
+} mlops_fbla_sizes;
+
+/* reference: mlops_fbla.h:153-163 (inputs of the fused per-token step) */
+typedef struct {
+  const uint16_t *q, *k, *v;
+  int64_t batch_stride, q_group_stride, kv_group_stride;
+  const uint16_t *q_norm, *k_norm;
+  float eps;
+  const float *freq;
+  float attention_factor;
+  uint16_t *q_out;
+} mlops_fbla_token;
+
+/* Bytes of scratch one decode of cfg needs on the current device; 0 for an invalid cfg. The scratch needs no
+ * initial contents and may be reused by later calls that fit. reference: mlops_fbla.h:93 */
+size_t mlops_fbla_decode_scratch_bytes(const mlops_fbla_config *cfg);
+
+/* One query per q head: q, output [batch, q_heads, 128] BF16. Work is enqueued on `stream`; no host
+ * synchronisation. tokens <= 2^26. reference: mlops_fbla.h:98-100 */
+mlops_fbla_status mlops_fbla_decode(const mlops_fbla_config *cfg, const uint16_t *q,
+                                    const mlops_fbla_cache *cache, uint16_t *output,
+                                    void *scratch, size_t scratch_bytes, cudaStream_t stream);
+
+/* Bytes of mlops_fbla_cache.tc_images on the current device. This library keeps no images: always 0.
+ * reference: mlops_fbla.h:104 */
+size_t mlops_fbla_images_bytes(const mlops_fbla_config *cfg);
+
+/* Allocation sizes of a cache for cfg (batch, kv_heads, format, capacity or tokens, strides). Returns 1 and fills
+ * *out, or 0 (out untouched) for an invalid cfg. reference: mlops_fbla.h:117 */
+int mlops_fbla_cache_sizes(const mlops_fbla_config *cfg, mlops_fbla_sizes *out);
+
+/* Scratch of mlops_fbla_decode_at for cfg->capacity (> 0). per_head is accepted for source compatibility; this
+ * library's scratch layout does not depend on it (any per_head >= 0 gives the same size). reference: mlops_fbla.h:122 */
+size_t mlops_fbla_decode_scratch_bytes_for(const mlops_fbla_config *cfg, int per_head);
+
+/* Append `count` tokens k, v [batch, kv_heads, count, 128] BF16 to a cache holding cfg->tokens tokens: groups that
+ * become closed are quantized into the planes and metadata, the sink and open windows take their BF16 rows.
+ * With q != NULL (q, output [batch, q_heads, count, 128] BF16) also returns causal attention of the new positions:
+ * position tokens+i attends to 0..tokens+i, closed groups through their full 6-bit codes, the sink group and the
+ * position's own group in BF16. reference: mlops_fbla.h:130-132 */
+mlops_fbla_status mlops_fbla_prefill(const mlops_fbla_config *cfg, int count, const uint16_t *q,
+                                     const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache,
+                                     uint16_t *output, cudaStream_t stream);
+
+/* As mlops_fbla_prefill with the start (*length + cfg->tokens) and *count read on the device when the kernels run;
+ * launches are sized by max_count alone. cfg->capacity > 0. reference: mlops_fbla.h:142-144 */
+mlops_fbla_status mlops_fbla_prefill_at(const mlops_fbla_config *cfg, const int *length, const int *count, int max_count,
+                                        const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                        const mlops_fbla_cache *cache, uint16_t *output, cudaStream_t stream);
+
+/* Decode with the cache length *length (+ cfg->tokens) read on the device; cfg->capacity > 0 sizes the launches and
+ * the scratch. reference: mlops_fbla.h:151-153 */
+mlops_fbla_status mlops_fbla_decode_at(const mlops_fbla_config *cfg, const int *length, const uint16_t *q,
+                                       const mlops_fbla_cache *cache, uint16_t *output, void *scratch, size_t scratch_bytes,
+                                       cudaStream_t stream);
+/* One token per KV head (k, v [batch, kv_heads, 128]) appended at position *length + cfg->tokens.
+ * reference: mlops_fbla.h:154-155 */
+mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *cfg, const int *length, const uint16_t *k, const uint16_t *v,
+                                       const mlops_fbla_cache *cache, cudaStream_t stream);
+
+/* reference: mlops_fbla.h:185-186 */
+const char *mlops_fbla_status_string(mlops_fbla_status status);
+const char *mlops_fbla_last_error(void); /* thread-local; "" after a successful call */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLOPS_FBLA_H */
