@@ -1,0 +1,299 @@
+// Host layer of the FBLA library: argument validation, cache / scratch geometry and dispatch to the CUDA passes.
+// It mirrors the accept / reject behaviour and the status codes of the reference's host code
+// (attention/fbla/src/fbla.cu:16-20 error text, :62-80 shape rules, :90-138 decode preparation, :193-268 prefill
+// rules, :408-430 size queries) behind the same C interface (include/mlops_fbla.h). It allocates nothing, never
+// synchronises, and keeps only per-thread state (last error, device attribute cache), so calls may come from many
+// host threads at once.
+#include "../../../include/mlops_fbla.h"
+#include "../kernels/fbla_kernels.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace {
+
+constexpr int G = MLOPS_FBLA_GROUP, SBG = MLOPS_FBLA_GROUP / MLOPS_FBLA_SUBBLOCK, D = MLOPS_FBLA_HEAD_DIM;
+constexpr long long MAX_TOKENS = 1ll << 26;
+
+thread_local char error_buf[256] = {0};
+mlops_fbla_status fail(mlops_fbla_status st, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buf, sizeof(error_buf) - 1, fmt, ap);
+  va_end(ap);
+  return st;
+}
+mlops_fbla_status ok() { error_buf[0] = 0; return MLOPS_FBLA_OK; }
+bool aligned(const void *p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
+bool valid_format(const mlops_fbla_config *c) { return c->format == MLOPS_FBLA_3P3 || c->format == MLOPS_FBLA_4P2; }
+bool valid_strides(const mlops_fbla_config *c) {
+  return (c->head_stride == 0 && c->group_stride == 0) || (c->head_stride > 0 && c->group_stride > 0);
+}
+bool valid_out_layout(const mlops_fbla_config *c) {
+  if (c->out_head_stride == 0 && c->out_token_stride == 0) return true;
+  return c->out_head_stride > 0 && c->out_token_stride > 0 && c->out_token_stride < (1ll << 30) && c->out_head_stride % 8 == 0 &&
+         c->out_token_stride % 8 == 0 && c->batch == 1;
+}
+// queries served together per virtual KV head for r queries per KV head: r for 1, 2, 4, else the largest of 4, 2, 1 dividing r
+int decode_group(int r) { return r == 1 || r == 2 || r == 4 ? r : r % 4 == 0 ? 4 : r % 2 == 0 ? 2 : 1; }
+float scale_log2(const mlops_fbla_config *c) {
+  const float scale = c->scale == 0.f ? 1.f / sqrtf((float)D) : c->scale;
+  return scale * 1.4426950408889634f;
+}
+bool cache_complete(const mlops_fbla_cache *k) {
+  return k->coarse && k->fine && k->meta && k->exact_sink_k && k->exact_sink_v && k->exact_open_k && k->exact_open_v;
+}
+fbla_k_cache kcache(const mlops_fbla_cache *k) {
+  return fbla_k_cache{k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
+}
+
+// ---- decode scratch ------------------------------------------------------------------------------------------------
+struct Layout {
+  size_t lse, part, dpart, row_r, counts, items, item_off, status, bytes;
+  int nblocks, nslices;
+};
+// shape: the launch shape of the current device (fbla_k_decode_shape); tokens: the layout's token count
+bool decode_layout(const mlops_fbla_config *c, long long tokens, const fbla_k_decode &shape, Layout &L) {
+  const int r = c->q_heads / c->kv_heads, qg = decode_group(r), vg = r / qg;
+  const size_t vheads = (size_t)c->batch * c->kv_heads * vg;
+  const long long groups = (tokens + G - 1) / G;
+  L.nblocks = (int)(groups * SBG);
+  L.nslices = (int)((L.nblocks + FBLA_K_SLICE - 1) / FBLA_K_SLICE);
+  if (L.nslices < 1) L.nslices = 1;
+  const size_t tw = (size_t)shape.coarse_ctas * shape.coarse_warps, xw = (size_t)shape.coarse_ctas;
+  const size_t rw = (size_t)shape.refine_ctas * shape.refine_warps;
+  const size_t row = (size_t)qg * FBLA_K_PSTRIDE * sizeof(float);
+  L.lse = 0;
+  L.part = L.lse + up256(vheads * L.nblocks * qg * sizeof(float));
+  L.dpart = L.part + up256((tw + xw + 2 * vheads) * row);
+  L.row_r = L.dpart + up256((rw + vheads) * row);
+  L.counts = L.row_r + up256(vheads * qg * sizeof(float));
+  L.items = L.counts + up256(vheads * L.nslices * sizeof(int));
+  L.item_off = L.items + up256(vheads * L.nslices * FBLA_K_SLICE * sizeof(int));
+  L.status = L.item_off + up256((vheads + 1) * sizeof(int));
+  L.bytes = L.status + 256;
+  return true;
+}
+bool valid_decode_shape(const mlops_fbla_config *c) {  // c->tokens: the layout's
+  if (!c || c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->tokens <= 0 || !valid_strides(c)) return false;
+  if (c->q_heads % c->kv_heads) return false;
+  if (c->capacity != 0 && c->capacity < c->tokens) return false;
+  return c->tokens <= MAX_TOKENS;
+}
+size_t scratch_bytes_of(const mlops_fbla_config *lc) {
+  fbla_k_decode shape{};
+  shape.cb = lc->format == MLOPS_FBLA_3P3 ? 3 : 4;
+  if (fbla_k_decode_shape(&shape) != cudaSuccess) return 0;
+  Layout L;
+  decode_layout(lc, lc->tokens, shape, L);
+  return L.bytes;
+}
+
+mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                         uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  const bool by_capacity = length != nullptr;
+  if (!c || !k || !q || !out || !scratch) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  mlops_fbla_config lc = *c;
+  if (by_capacity) lc.tokens = c->capacity;
+  if (!valid_decode_shape(&lc) || (by_capacity && c->tokens < 0))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads and tokens must be positive (device length: capacity positive, tokens >= 0), "
+                "q_heads a multiple of kv_heads, tokens <= 2^26, capacity 0 or >= tokens, strides both 0 or both positive", fn);
+  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
+  if (!(c->scale >= 0.f) || !(c->tau >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scale and tau must be nonnegative", fn);
+  if (!cache_complete(k)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
+  const void *ptrs[] = {q, out, scratch, k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
+  for (const void *p : ptrs)
+    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: pointers must be 16-byte aligned", fn);
+  if (!aligned(length, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length must be 4-byte aligned", fn);
+  if ((c->length_stride != 0 && c->length_stride != 1) || (c->length_stride && !length))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0, or 1 with a device length", fn);
+
+  fbla_k_decode a{};
+  a.cb = c->format == MLOPS_FBLA_3P3 ? 3 : 4;
+  a.fb = c->format == MLOPS_FBLA_3P3 ? 3 : 2;
+  cudaError_t e = fbla_k_decode_shape(&a);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  Layout L;
+  decode_layout(&lc, lc.tokens, a, L);
+  if (scratch_bytes < L.bytes) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scratch has %zu bytes, need %zu", fn, scratch_bytes, L.bytes);
+  const int r = c->q_heads / c->kv_heads;
+  a.qg = decode_group(r);
+  a.vg = r / a.qg;
+  if ((long long)c->batch * c->kv_heads * a.vg * L.nslices > 40000)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch * kv_heads * virtual heads * slices of 16384 tokens exceeds 40000 (split the batch)", fn);
+  a.c = kcache(k);
+  a.q = q; a.out = out;
+  char *base = static_cast<char *>(scratch);
+  a.lse = reinterpret_cast<float *>(base + L.lse);
+  a.part = reinterpret_cast<float *>(base + L.part);
+  a.dpart = reinterpret_cast<float *>(base + L.dpart);
+  a.row_r = reinterpret_cast<float *>(base + L.row_r);
+  a.counts = reinterpret_cast<int *>(base + L.counts);
+  a.items = reinterpret_cast<int *>(base + L.items);
+  a.item_off = reinterpret_cast<int *>(base + L.item_off);
+  a.status = reinterpret_cast<int *>(base + L.status);
+  a.length = length;
+  a.lstride = c->length_stride;
+  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads; a.tokens = c->tokens;
+  a.nblocks = L.nblocks; a.nslices = L.nslices;
+  const long long cap = c->capacity ? c->capacity : c->tokens;
+  a.hs = c->head_stride ? c->head_stride : (int)((cap + G - 1) / G);
+  a.gs = c->group_stride ? c->group_stride : 1;
+  a.sl = scale_log2(c);
+  const float tau = c->tau != 0.f ? c->tau : c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f;
+  a.log2_tau = log2f(tau);
+  e = fbla_k_decode_launch(&a, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
+}
+
+// ---- prefill ------------------------------------------------------------------------------------------------------------
+mlops_fbla_status prefill_common(const char *fn, const mlops_fbla_config *c, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                 const mlops_fbla_cache *x, uint16_t *out) {
+  if (!valid_out_layout(c))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: out_head_stride and out_token_stride both positive multiples of 8 (batch 1) or both 0", fn);
+  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
+  if (!(c->scale >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scale must be nonnegative", fn);
+  if (!cache_complete(x)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
+  const void *ptrs[] = {k, v, q, out, x->coarse, x->fine, x->meta, x->exact_sink_k, x->exact_sink_v, x->exact_open_k, x->exact_open_v};
+  for (const void *p : ptrs)
+    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: pointers must be 16-byte aligned", fn);
+  if (!aligned(x->tc_images, 128)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: tc_images must be 128-byte aligned", fn);
+  return MLOPS_FBLA_OK;
+}
+void fill_prefill(const mlops_fbla_config *c, int count, long long capacity, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                  const mlops_fbla_cache *x, uint16_t *out, fbla_k_prefill &a) {
+  a.c = kcache(x);
+  a.q = q; a.k = k; a.v = v; a.out = out;
+  a.out_hs = c->out_head_stride ? c->out_head_stride : (int64_t)count * D;
+  a.out_ts = c->out_token_stride ? (int)c->out_token_stride : D;
+  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads;
+  a.n0 = c->tokens; a.count = count;
+  a.hs = c->head_stride ? c->head_stride : (int)((capacity + G - 1) / G);
+  a.gs = c->group_stride ? c->group_stride : 1;
+  a.cb = c->format == MLOPS_FBLA_3P3 ? 3 : 4;
+  a.fb = c->format == MLOPS_FBLA_3P3 ? 3 : 2;
+  a.sl = scale_log2(c);
+}
+mlops_fbla_status run_prefill(const char *fn, const fbla_k_prefill &a, int close_blocks, cudaStream_t stream) {
+  // order: close reads the old windows, the attention reads them too, finish overwrites them last
+  cudaError_t e = fbla_k_close_launch(&a, close_blocks, stream);
+  if (e == cudaSuccess && a.q) e = fbla_k_attend_launch(&a, stream);
+  if (e == cudaSuccess) e = fbla_k_finish_launch(&a, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
+}
+mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
+                             const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
+                             cudaStream_t stream) {
+  if (!c || !length || !cache || !k || !v) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  if (q && !out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q needs output", fn);
+  if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 ||
+      (long long)c->tokens + max_count > c->capacity || max_count <= 0 || c->capacity > MAX_TOKENS || !valid_strides(c))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads, max_count and capacity must be positive, tokens >= 0, tokens + max_count <= "
+                "capacity <= 2^26, q_heads a multiple of kv_heads, strides both 0 or both positive", fn);
+  if ((c->length_stride != 0 && c->length_stride != 1) || (c->length_stride && (q || dcount)))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0 (1 only for the one-token append)", fn);
+  const mlops_fbla_status st = prefill_common(fn, c, q, k, v, cache, out);
+  if (st != MLOPS_FBLA_OK) return st;
+  if (!aligned(length, 4) || !aligned(dcount, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length and count must be 4-byte aligned", fn);
+  fbla_k_prefill a{};
+  fill_prefill(c, max_count, c->capacity, q, k, v, cache, out, a);
+  a.length = length; a.dcount = dcount; a.lstride = c->length_stride;
+  // a chunk of at most max_count tokens starting anywhere closes at most max_count / 128 + 1 groups
+  return run_prefill(fn, a, max_count / G + 1, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t mlops_fbla_decode_scratch_bytes(const mlops_fbla_config *c) {
+  if (!valid_decode_shape(c) || !valid_format(c)) return 0;
+  return scratch_bytes_of(c);
+}
+
+size_t mlops_fbla_decode_scratch_bytes_for(const mlops_fbla_config *c, int per_head) {
+  if (!c || c->capacity <= 0 || per_head < 0) return 0;
+  mlops_fbla_config lc = *c;
+  lc.tokens = c->capacity;
+  if (!valid_decode_shape(&lc) || !valid_format(c)) return 0;
+  return scratch_bytes_of(&lc);
+}
+
+mlops_fbla_status mlops_fbla_decode(const mlops_fbla_config *c, const uint16_t *q, const mlops_fbla_cache *k, uint16_t *out,
+                                    void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  return decode("mlops_fbla_decode", c, nullptr, q, k, out, scratch, scratch_bytes, stream);
+}
+
+mlops_fbla_status mlops_fbla_decode_at(const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                                       uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  if (!length) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_decode_at: null length");
+  if (c && c->capacity <= 0) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_decode_at: capacity must be positive");
+  return decode("mlops_fbla_decode_at", c, length, q, k, out, scratch, scratch_bytes, stream);
+}
+
+size_t mlops_fbla_images_bytes(const mlops_fbla_config *) { return 0; }
+
+int mlops_fbla_cache_sizes(const mlops_fbla_config *c, mlops_fbla_sizes *out) {
+  if (!c || !out || c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->q_heads % c->kv_heads || !valid_strides(c)) return 0;
+  if (!valid_format(c)) return 0;
+  const long long tokens = c->capacity ? c->capacity : c->tokens;
+  if (tokens <= 0 || (c->capacity && c->capacity < c->tokens)) return 0;
+  const size_t heads = (size_t)c->batch * c->kv_heads, groups = (size_t)((tokens + G - 1) / G);
+  const size_t hs = c->head_stride ? (size_t)c->head_stride : groups, gs = c->group_stride ? (size_t)c->group_stride : 1;
+  const size_t units = (heads - 1) * hs + (groups - 1) * gs + 1;
+  const bool three = c->format == MLOPS_FBLA_3P3;
+  out->coarse = units * SBG * (three ? 1536 : 2048);
+  out->fine = units * SBG * (three ? 1536 : 1024);
+  out->meta = units * 1024;
+  out->exact = heads * G * D * sizeof(uint16_t);
+  out->images = 0;
+  return 1;
+}
+
+mlops_fbla_status mlops_fbla_prefill(const mlops_fbla_config *c, int count, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                     const mlops_fbla_cache *cache, uint16_t *out, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_prefill";
+  if (!c || !cache || !k || !v) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  if (q && !out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q needs output", fn);
+  const long long n1 = (long long)c->tokens + count;
+  if (c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->tokens < 0 || count <= 0 || !valid_strides(c) || c->q_heads % c->kv_heads ||
+      !(c->capacity == 0 || c->capacity >= n1) || n1 > MAX_TOKENS)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads and count must be positive, tokens >= 0, q_heads a multiple of kv_heads, "
+                "tokens + count <= capacity (0: tokens + count) and <= 2^26, strides both 0 or both positive", fn);
+  const mlops_fbla_status st = prefill_common(fn, c, q, k, v, cache, out);
+  if (st != MLOPS_FBLA_OK) return st;
+  fbla_k_prefill a{};
+  fill_prefill(c, count, c->capacity ? c->capacity : n1, q, k, v, cache, out, a);
+  const int g_first = c->tokens == 0 ? 0 : (c->tokens - 1) / G, g_end = (int)((n1 - 1) / G);
+  return run_prefill(fn, a, g_end - g_first, stream);
+}
+
+mlops_fbla_status mlops_fbla_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q,
+                                        const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
+                                        cudaStream_t stream) {
+  if (!count) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_prefill_at: null argument");
+  return prefill_at("mlops_fbla_prefill_at", c, length, count, max_count, q, k, v, cache, out, stream);
+}
+
+mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *c, const int *length, const uint16_t *k, const uint16_t *v,
+                                       const mlops_fbla_cache *cache, cudaStream_t stream) {
+  return prefill_at("mlops_fbla_append_at", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, stream);
+}
+
+const char *mlops_fbla_status_string(mlops_fbla_status status) {
+  switch (status) {
+    case MLOPS_FBLA_OK: return "ok";
+    case MLOPS_FBLA_INVALID_VALUE: return "invalid value";
+    case MLOPS_FBLA_CUDA_ERROR: return "CUDA error";
+  }
+  return "unknown status";
+}
+
+const char *mlops_fbla_last_error(void) { return error_buf; }
+
+}  // extern "C"

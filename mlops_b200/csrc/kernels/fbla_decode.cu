@@ -1,0 +1,878 @@
+// FBLA compressed-KV decode for sm_100a: coarse pass (+ the BF16 windows), select, refine, merge.
+//
+// Semantics follow the reference's decode (attention/fbla/src/fbla_kernels.cuh:315-359 qhat, :479-533 coarse blocks,
+// :866-920 select, :1036-1072 refine, :1270-1294 merge): per (query, group) int8 qhat, 16-token P blocks of integers
+// p = round(255 * 2^(s - max)), coarse cells decoded at their midpoint, blocks with 2^(lse_j - R) > tau corrected by
+// (full - coarse). The structure is new:
+//   * a persistent grid, one CTA per SM; every warp owns a contiguous range of the flattened list of closed
+//     (virtual head, group) units and a private 2-stage ring in shared memory that whole groups (8 records + 1 KiB
+//     metadata) are streamed into by 1-D bulk asynchronous copies completing on mbarriers (all waits bounded);
+//   * scores and values are integer tensor-core products taken straight from the packed records (fbla_frag.cuh):
+//     tokens on M for S^T = K_codes qhat^T, channels on M for O^T = V_codes^T P^T, both P blocks of a record pair
+//     in the 8 columns of one product; the instruction count per byte no longer grows with the GQA ratio;
+//   * one extra warp per CTA serves the BF16 sink / open windows with plain loads and FP32 FMAs.
+// Reduction orders are fixed by (warp, unit) ranges alone, so outputs are bit-reproducible run to run.
+#include "fbla_frag.cuh"
+#include "fbla_kernels.h"
+
+namespace fbla {
+
+constexpr int PSTRIDE = FBLA_K_PSTRIDE;  // floats of one partial row: o[128], m, l, 2 pad (coarse); o[128], dl, 3 pad (refine)
+constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
+
+template <int CB> struct CoarseShape {
+  static constexpr int WARPS = CB == 4 ? 6 : 8;  // streaming warps (the ring of each: 2 groups)
+  static constexpr int NST = 2;
+  static constexpr int GROUP_BYTES = SBG * record_bytes(CB);
+  static constexpr int STAGE = GROUP_BYTES + 1024;  // + the group's metadata
+};
+
+// ---- where a batch row's tokens put its units -----------------------------------------------------------------------
+struct Row { int tokens, groups, closed, exact; };
+__device__ __forceinline__ Row row_of(const fbla_k_decode &a, int b) {
+  Row r;
+  r.tokens = (a.length ? __ldg(a.length + (a.lstride ? b : 0)) : 0) + a.tokens;
+  r.groups = (r.tokens + G - 1) / G;
+  r.closed = r.groups >= 3 ? r.groups - 2 : 0;
+  const int na = r.groups == 1 ? (r.tokens + S - 1) / S : (r.groups >= 2 ? SBG : 0);
+  const int no = r.groups >= 2 ? (r.tokens - G * (r.groups - 1) + S - 1) / S : 0;
+  r.exact = na + no;  // BF16 sub-blocks: the sink's, then the open group's
+  return r;
+}
+// Flattened unit lists. Closed groups: row b contributes hpr * closed(b) units, head-major. BF16 sub-blocks likewise.
+// A cursor walks one list; every warp builds its own from the row lengths (no shared state, no limit on the batch).
+struct Cursor {
+  int b, hir, i, n;  // batch row, virtual head within the row, index within the head's n units
+};
+template <bool EXACT>
+__device__ __forceinline__ int units_of(const Row &r) { return EXACT ? r.exact : r.closed; }
+
+template <bool EXACT>
+__device__ __forceinline__ long long total_units(const fbla_k_decode &a, int hpr) {
+  long long t = 0;
+  for (int b = 0; b < a.batch; ++b) t += (long long)hpr * units_of<EXACT>(row_of(a, b));
+  return t;
+}
+// the cursor of flattened unit u (u < total)
+template <bool EXACT>
+__device__ __forceinline__ Cursor locate(const fbla_k_decode &a, int hpr, long long u) {
+  Cursor c{0, 0, 0, 0};
+  for (int b = 0; b < a.batch; ++b) {
+    const int n = units_of<EXACT>(row_of(a, b));
+    const long long span = (long long)hpr * n;
+    if (u < span) { c.b = b; c.hir = (int)(u / n); c.i = (int)(u % n); c.n = n; return c; }
+    u -= span;
+  }
+  c.b = a.batch;
+  return c;
+}
+template <bool EXACT>
+__device__ __forceinline__ void advance(const fbla_k_decode &a, int hpr, Cursor &c) {
+  if (++c.i < c.n) return;
+  c.i = 0;
+  if (++c.hir < hpr) return;
+  c.hir = 0;
+  for (++c.b; c.b < a.batch; ++c.b) {
+    c.n = units_of<EXACT>(row_of(a, c.b));
+    if (c.n) return;
+  }
+}
+// first flattened unit of virtual head vh, and the head's unit count
+template <bool EXACT>
+__device__ __forceinline__ long long head_offset(const fbla_k_decode &a, int hpr, int vh, int &n) {
+  const int bq = vh / hpr, hir = vh - bq * hpr;
+  long long off = 0;
+  for (int b = 0; b < bq; ++b) off += (long long)hpr * units_of<EXACT>(row_of(a, b));
+  n = units_of<EXACT>(row_of(a, bq));
+  return off + (long long)hir * n;
+}
+__device__ __forceinline__ long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
+
+// q row (batch b, virtual head hir = kh * vg + j, query qi) in q / out
+__device__ __forceinline__ int q_row(const fbla_k_decode &a, int b, int hir, int qi) {
+  const int kh = hir / a.vg, j = hir - kh * a.vg;
+  return b * a.q_heads + kh * (a.q_heads / a.kv_heads) + j * a.qg + qi;
+}
+
+// ---- per-group query quantization (the definition of include/mlops_fbla.h) --------------------------------------------
+// Lane l holds channels 4 l .. 4 l + 3: km = the lane's 16 metadata bytes of K (4 bases, 4 steps), q4 = its 4 q values.
+// Writes the lane's qhat word to qst_row[l]; returns through the references the warp-uniform sq, qb (= sl q . base),
+// qsum (= sum qhat).
+__device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, uint32_t *qst_row, int lane, float &sq, float &qb, float &qsum) {
+  const float kb[4] = {bf_lo(km.x), bf_hi(km.x), bf_lo(km.y), bf_hi(km.y)}, ks[4] = {bf_lo(km.z), bf_hi(km.z), bf_lo(km.w), bf_hi(km.w)};
+  const float qf[4] = {q4.x, q4.y, q4.z, q4.w};
+  float z[4], amax = 0.f, dot = 0.f;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) { z[x] = __fmul_rn(qf[x], ks[x]); amax = fmaxf(amax, fabsf(z[x])); dot = fmaf(qf[x], kb[x], dot); }
+  amax = warp_max(amax);
+  // r = fl(127 / amax), correctly rounded: reciprocal seed, one Newton step, quotient and its residual correction
+  float rc;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
+  rc = fmaf(fmaf(-amax, rc, 1.f), rc, rc);
+  const float q0 = __fmul_rn(127.f, rc);
+  const float r = amax > 0.f ? fmaf(fmaf(-amax, q0, 127.f), rc, q0) : 0.f;
+  uint32_t word = 0;
+  float s = 0.f;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const float t = fmaf(z[x], r, MAGICF);  // rint(z r) in the low mantissa bits: one rounding of the exact product
+    word |= (__float_as_uint(t) & 255u) << (8 * x);
+    s += t - MAGICF;
+  }
+  qst_row[lane] = word;
+  sq = __fmul_rn(amax, __fmul_rn(sl, 1.f / 127.f));
+  qb = __fmul_rn(warp_sum(dot), sl);
+  qsum = warp_sum(s);
+}
+
+// ---- shared memory of the coarse kernel ---------------------------------------------------------------------------------
+template <int CB> struct __align__(128) StreamWarp {
+  uint8_t stage[CoarseShape<CB>::NST][CoarseShape<CB>::STAGE];
+  uint8_t qst[8 * QST_ROW];  // qhat rows (rows >= QG stay zero)
+  uint8_t pst[128];          // P bytes of a record pair: [block parity][query 0..3][16 tokens]
+  uint64_t bar[CoarseShape<CB>::NST];
+};
+struct __align__(16) ExactWarp {
+  float q[4][D];
+  uint8_t pst[4][16];
+};
+template <int CB> struct CoarseSmem {
+  StreamWarp<CB> w[CoarseShape<CB>::WARPS];
+  ExactWarp x;
+};
+
+__device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
+  if (a.status) { atomicCAS(a.status, 0, pass); a.status[1] = blockIdx.x; }
+}
+
+// ---- the BF16 windows: one warp per CTA ----------------------------------------------------------------------------------
+// Unit = one 16-token sub-block of the sink (first) or the open window. Scores s = sl * (q . k) in FP32, the same
+// integer P block, values in FP32. Lane (t = lane % 16, h = lane / 16) scores token t over channels 64 h .. 64 h + 63;
+// for the values lane l owns channels 4 l .. 4 l + 3.
+template <int QG>
+__device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
+  const int hpr = a.kv_heads * a.vg;
+  const long long total = total_units<true>(a, hpr), per = ceil_div(total, nxw);
+  const long long lo = (long long)xw * per, hi = min(total, lo + per);
+  if (lo >= hi) return;
+  const int slot0 = a.coarse_ctas * a.coarse_warps + a.batch * hpr;  // after the coarse slots
+  Cursor c = locate<true>(a, hpr, lo);
+  int cur_vh = -1;
+  float m[QG], l[QG], o[QG][4];
+  auto flush = [&]() {
+    float *p = a.part + (size_t)(slot0 + xw + cur_vh) * QG * PSTRIDE;
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) {
+      *reinterpret_cast<float4 *>(p + qi * PSTRIDE + 4 * lane) = make_float4(o[qi][0], o[qi][1], o[qi][2], o[qi][3]);
+      if (!lane) { p[qi * PSTRIDE + D] = m[qi]; p[qi * PSTRIDE + D + 1] = l[qi]; }
+    }
+  };
+  for (long long u = lo; u < hi; ++u, advance<true>(a, hpr, c)) {
+    const int vh = c.b * hpr + c.hir, bh = vh / a.vg;
+    if (vh != cur_vh) {
+      if (cur_vh >= 0) flush();
+      cur_vh = vh;
+      __syncwarp();
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) {
+        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, c.b, c.hir, qi) * D) + lane);
+        *reinterpret_cast<float4 *>(&sm.q[qi][4 * lane]) = make_float4(bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y));
+        m[qi] = -INFINITY; l[qi] = 0.f;
+        o[qi][0] = o[qi][1] = o[qi][2] = o[qi][3] = 0.f;
+      }
+      __syncwarp();
+    }
+    const Row r = row_of(a, c.b);
+    const int na = r.groups == 1 ? (r.tokens + S - 1) / S : SBG;
+    const bool sink = c.i < na;
+    const int j = sink ? c.i : c.i - na;
+    const int count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
+    const size_t eh = (size_t)bh * G * D;
+    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh;
+    const int t = lane & 15, h = lane >> 4, tok = j * S + t;
+    float x[QG];
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) x[qi] = 0.f;
+    if (tok < count) {
+      const uint4 *kp = reinterpret_cast<const uint4 *>(ek + (size_t)tok * D + 64 * h);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 w = __ldcg(kp + i);
+        const float kv[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+#pragma unroll
+        for (int qi = 0; qi < QG; ++qi)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x[qi] = fmaf(sm.q[qi][64 * h + 8 * i + e], kv[e], x[qi]);
+      }
+    }
+    float al[QG], w[QG], sp[QG];
+    uint32_t P[QG][4];
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) {
+      x[qi] += __shfl_xor_sync(FULL, x[qi], 16);
+      const float s = tok < count ? __fmul_rn(x[qi], a.sl) : -INFINITY;
+      float mb = s;
+#pragma unroll
+      for (int off = 8; off; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(FULL, mb, off));
+      const float mn = fmaxf(m[qi], mb);
+      al[qi] = ex2(m[qi] - mn); w[qi] = ex2(mb - mn);  // (2^-inf = 0; mb is finite: token 0 of a unit always exists)
+      m[qi] = mn;
+      const uint32_t pbits = __float_as_uint(fmaf(ex2(s - mb), 255.f, MAGICF));
+      if (lane < 16) sm.pst[qi][t] = (uint8_t)pbits;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) {
+      const uint4 pw = *reinterpret_cast<const uint4 *>(sm.pst[qi]);
+      P[qi][0] = pw.x; P[qi][1] = pw.y; P[qi][2] = pw.z; P[qi][3] = pw.w;
+      sp[qi] = (float)(__dp4a(pw.x, 0x01010101u, 0u) + __dp4a(pw.y, 0x01010101u, 0u) + __dp4a(pw.z, 0x01010101u, 0u) + __dp4a(pw.w, 0x01010101u, 0u));
+    }
+    float y[QG][4];
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) y[qi][0] = y[qi][1] = y[qi][2] = y[qi][3] = 0.f;
+#pragma unroll
+    for (int tt = 0; tt < S; ++tt) {
+      const uint2 vw = j * S + tt < count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(j * S + tt) * D) + lane) : make_uint2(0u, 0u);
+      const float vv[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) {
+        const float p = (float)((P[qi][tt >> 2] >> (8 * (tt & 3))) & 255u);
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) y[qi][cc] = fmaf(p, vv[cc], y[qi][cc]);
+      }
+    }
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) {
+      l[qi] = fmaf(al[qi], l[qi], w[qi] * sp[qi]);
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) o[qi][cc] = fmaf(al[qi], o[qi][cc], w[qi] * y[qi][cc]);
+    }
+    __syncwarp();
+  }
+  flush();
+}
+
+// ---- one closed group on the tensor cores ----------------------------------------------------------------------------------
+// The warp's running softmax of its current virtual head. Thread (gid, tig): channels 4 (8 u + gid) + cc, u, cc = 0..3,
+// of queries qe = 2 (tig & 1) + e, e = 0, 1, summed over the sub-blocks of parity tig >> 1 only: the two parities'
+// threads are added when the partial is written.
+struct Run {
+  float m[2], l[2], o[4][4][2];
+};
+template <int QG> __device__ __forceinline__ bool query_valid(int tig, int e) { return 2 * (tig & 1) + e < QG; }
+
+template <int CB, int FB, int QG>
+__device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &sm, const float4 (&q4)[QG], float sl, int lane, Run &run,
+                                             float *lse_group /* [8 sub-blocks][QG] of this (virtual head, group) */) {
+  constexpr int RB = record_bytes(CB);
+  constexpr float HOFF = .5f * ((1 << FB) - 1);
+  const int gid = lane >> 2, tig = lane & 3;
+  const uint8_t *meta = st + CoarseShape<CB>::GROUP_BYTES;
+  // qhat of every query; c0 / sqc of the thread's two columns
+  float c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f};
+  {
+    const uint4 km = lds128(meta + 16 * lane);
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) {
+      float sq, qb, qsum;
+      quantize_query(km, q4[qi], sl, reinterpret_cast<uint32_t *>(sm.qst + QST_ROW * qi), lane, sq, qb, qsum);
+      const float c = fmaf(__fmul_rn(sq, HOFF), qsum, qb), s2 = __fmul_rn(sq, (float)(1 << FB));
+      if (qi == 2 * (tig & 1)) { c0[0] = c; sqc[0] = s2; }
+      if (qi == 2 * (tig & 1) + 1) { c0[1] = c; sqc[1] = s2; }
+    }
+  }
+  __syncwarp();
+  uint32_t B[8];
+  qhat_frag<CB>(sm.qst, gid, tig, B);
+  // scores of the 8 sub-blocks: s[j][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1);
+  // only columns < QG (threads tig < 2) are queries, the rest multiply zero rows of qst
+  float s[SBG][4], mb[SBG][2], mg[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int j = 0; j < SBG; ++j) {
+    float x[4];
+    qk_tile<CB>(st + j * RB, gid, tig, B, x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[j][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float v = fmaxf(s[j][e], s[j][2 + e]);
+      v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
+      v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
+      v = fmaxf(v, __shfl_xor_sync(FULL, v, 16));
+      mb[j][e] = v;
+      mg[e] = fmaxf(mg[e], v);
+    }
+  }
+  // Threads tig >= 2 accumulate the odd sub-blocks (columns 4..7 of the value products) of queries 2 (tig & 1) + e:
+  // their maxima live in thread tig - 2.
+  const bool odd = tig >> 1;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) { const float o2 = __shfl_xor_sync(FULL, mg[e], 2); if (odd) mg[e] = o2; }
+  float A[4][4][2], Bs[2] = {0.f, 0.f};
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) A[u][cc][0] = A[u][cc][1] = 0.f;
+#pragma unroll
+  for (int J = 0; J < SBG / 2; ++J) {
+    // P bytes of sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1): pst[parity][query][token]
+    if (tig < 2) {
+#pragma unroll
+      for (int par = 0; par < 2; ++par)
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (query_valid<QG>(tig, e)) {
+            const int j = 2 * J + par, qe = 2 * tig + e;
+            const uint32_t p0 = __float_as_uint(fmaf(ex2(s[j][e] - mb[j][e]), 255.f, MAGICF));
+            const uint32_t p8 = __float_as_uint(fmaf(ex2(s[j][2 + e] - mb[j][e]), 255.f, MAGICF));
+            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)p0;
+            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)p8;
+          }
+    }
+    __syncwarp();
+    // column gid of the value products: gid < 4: parity 0, query gid, k block = tokens 4 tig ..; gid >= 4: parity 1
+    const uint32_t pw = lds32(sm.pst + 4 * lane);
+    const uint32_t b0 = gid < 4 ? pw : 0u, b1 = gid < 4 ? 0u : pw;
+    const uint8_t *ra = st + (2 * J) * RB, *rb = ra + RB;
+    // the thread's sub-block 2 J + (tig >> 1), queries 2 (tig & 1) + e: its maximum and weight
+    float mbj[2], wj[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float other = __shfl_xor_sync(FULL, mb[2 * J + 1][e], 2);
+      mbj[e] = odd ? other : mb[2 * J][e];
+      wj[e] = ex2(mbj[e] - mg[e]);
+    }
+    {  // sum p of both sub-blocks, every column: a product with an all-ones A
+      uint32_t d[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+      mma_u8u8_k32(d, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float sp = isum(d[e]);
+        Bs[e] = fmaf(wj[e], sp, Bs[e]);
+        if (gid == 0 && query_valid<QG>(tig, e)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1) + e] = mbj[e] + lg2(sp);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      uint32_t va[4], vb[4];
+      v_slots<CB>(ra, 8 * u + gid, tig, va);
+      v_slots<CB>(rb, 8 * u + gid, tig, vb);
+      uint32_t d01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, d23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+      mma_u8u8_k32(d01, va[0], va[1], vb[0], vb[1], b0, b1);  // rows gid: channel cc 0, gid + 8: cc 1
+      mma_u8u8_k32(d23, va[2], va[3], vb[2], vb[3], b0, b1);  // cc 2, cc 3
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        A[u][0][e] = fmaf(wj[e], isum(d01[e]), A[u][0][e]);
+        A[u][1][e] = fmaf(wj[e], isum(d01[2 + e]), A[u][1][e]);
+        A[u][2][e] = fmaf(wj[e], isum(d23[e]), A[u][2][e]);
+        A[u][3][e] = fmaf(wj[e], isum(d23[2 + e]), A[u][3][e]);
+      }
+    }
+    __syncwarp();  // pst is rewritten by the next pair
+  }
+  // fold the group into the running softmax: o += 2^(mg - m) (vs' A + vb' B), coarse cell midpoints folded into vb'
+  float al[2], be[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float mn = fmaxf(run.m[e], mg[e]);
+    al[e] = ex2(run.m[e] - mn); be[e] = ex2(mg[e] - mn);
+    run.m[e] = mn;
+    run.l[e] = fmaf(al[e], run.l[e], be[e] * Bs[e]);
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
+    const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      const float vbp = fmaf(vs[cc], HOFF, vb[cc]), vsp = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc));
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        run.o[u][cc][e] = fmaf(al[e], run.o[u][cc][e], be[e] * fmaf(vsp, A[u][cc][e], vbp * Bs[e]));
+    }
+  }
+}
+
+
+// ---- the coarse kernel -------------------------------------------------------------------------------------------------
+template <int QG> __device__ __forceinline__ void reset(Run &r) {
+  r.m[0] = r.m[1] = -INFINITY; r.l[0] = r.l[1] = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) r.o[u][cc][0] = r.o[u][cc][1] = 0.f;
+}
+// one partial row set: threads tig and tig ^ 2 hold the two sub-block parities of the same (channel, query) sums
+template <int QG> __device__ __forceinline__ void write_partial(float *p, const Run &r, int lane, bool correction) {
+  const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    const float l = r.l[e] + __shfl_xor_sync(FULL, r.l[e], 2);
+    const int qe = 2 * tig + e;
+    float *row = p + qe * PSTRIDE;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float4 v;
+      v.x = r.o[u][0][e] + __shfl_xor_sync(FULL, r.o[u][0][e], 2);
+      v.y = r.o[u][1][e] + __shfl_xor_sync(FULL, r.o[u][1][e], 2);
+      v.z = r.o[u][2][e] + __shfl_xor_sync(FULL, r.o[u][2][e], 2);
+      v.w = r.o[u][3][e] + __shfl_xor_sync(FULL, r.o[u][3][e], 2);
+      if (tig < 2 && qe < QG) *reinterpret_cast<float4 *>(row + 4 * (8 * u + gid)) = v;
+    }
+    if (tig < 2 && qe < QG && gid == 0) {
+      if (correction) row[D] = l;
+      else { row[D] = r.m[e]; row[D + 1] = l; }
+    }
+  }
+}
+
+template <int CB, int FB, int QG>
+__global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + 1), 1) coarse_kernel(const fbla_k_decode a) {
+  using Sh = CoarseShape<CB>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (blockIdx.x == 0 && threadIdx.x == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
+  if (warp == Sh::WARPS) {
+    exact_warp<QG>(a, sm.x, lane, blockIdx.x, gridDim.x);
+    return;
+  }
+  StreamWarp<CB> &w = sm.w[warp];
+  for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
+  reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < Sh::NST; ++s) mbar_init(&w.bar[s], 1);
+    mbar_init_fence();
+  }
+  __syncwarp();
+
+  const int hpr = a.kv_heads * a.vg;
+  const long long total = total_units<false>(a, hpr), tw = (long long)gridDim.x * Sh::WARPS, per = ceil_div(total, tw);
+  const long long gw = (long long)blockIdx.x * Sh::WARPS + warp, lo = gw * per, hi = min(total, lo + per);
+  if (lo >= hi) return;
+  Cursor fc = locate<false>(a, hpr, lo), cc = fc;
+  auto issue = [&](const Cursor &c, int s) {  // lane 0: group 1 + c.i of the cursor's KV head into stage s
+    const int bh = (c.b * hpr + c.hir) / a.vg;
+    const size_t unit = (size_t)bh * a.hs + (size_t)(1 + c.i) * a.gs;
+    mbar_expect_tx(&w.bar[s], Sh::STAGE);
+    bulk_g2s(w.stage[s], a.c.coarse + unit * Sh::GROUP_BYTES, Sh::GROUP_BYTES, &w.bar[s]);
+    bulk_g2s(w.stage[s] + Sh::GROUP_BYTES, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
+  };
+#pragma unroll
+  for (int s = 0; s < Sh::NST; ++s)
+    if (lo + s < hi) {
+      if (lane == 0) issue(fc, s);
+      advance<false>(a, hpr, fc);
+    }
+  Run run;
+  float4 q4[QG];
+  int cur_vh = -1;
+  for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
+    const int k = (int)(u - lo), s = k % Sh::NST, vh = cc.b * hpr + cc.hir;
+    if (vh != cur_vh) {
+      if (cur_vh >= 0) write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
+      cur_vh = vh;
+      reset<QG>(run);
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) {
+        const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, cc.b, cc.hir, qi) * D) + lane);
+        q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
+      }
+    }
+    const bool ok = mbar_wait_bounded(&w.bar[s], (k / Sh::NST) & 1);
+    if (!__all_sync(FULL, ok)) {
+      if (lane == 0) report(a, 1);
+      return;
+    }
+    coarse_group<CB, FB, QG>(w.stage[s], w, q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)(1 + cc.i) * SBG) * QG);
+    __syncwarp();
+    if (u + Sh::NST < hi) {
+      if (lane == 0) { fence_async_smem(); issue(fc, s); }
+      advance<false>(a, hpr, fc);
+    }
+  }
+  write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
+}
+
+// ---- which partial slots belong to a virtual head ------------------------------------------------------------------------
+struct Slots { int c0, c1, x0, x1; };  // coarse warps c0..c1 (slot w + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
+__device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
+  const int hpr = a.kv_heads * a.vg;
+  Slots s{0, -1, 0, -1};
+  int n;
+  const long long tw = (long long)a.coarse_ctas * a.coarse_warps;
+  long long off = head_offset<false>(a, hpr, vh, n);
+  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), tw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
+  off = head_offset<true>(a, hpr, vh, n);
+  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), a.coarse_ctas); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
+  return s;
+}
+__device__ __forceinline__ const float *coarse_slot(const fbla_k_decode &a, int w, int vh, int qi) {
+  return a.part + ((size_t)(w + vh) * a.qg + qi) * PSTRIDE;
+}
+__device__ __forceinline__ const float *window_slot(const fbla_k_decode &a, int x, int vh, int qi) {
+  const int base = a.coarse_ctas * a.coarse_warps + a.batch * a.kv_heads * a.vg;
+  return a.part + ((size_t)(base + x + vh) * a.qg + qi) * PSTRIDE;
+}
+
+// ---- select: R = log2 of the row's coarse mass; the sub-blocks holding more than tau of it for some query ------------
+template <int QG>
+__global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
+  __shared__ float R[4];
+  __shared__ int wc[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, vh = blockIdx.y, slice = blockIdx.x;
+  const int hpr = a.kv_heads * a.vg;
+  if (warp < QG) {
+    const Slots s = slots_of(a, vh);
+    const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
+    float mx = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
+      mx = fmaxf(mx, __ldcg(p + D));
+    }
+    mx = warp_max(mx);
+    float ls = 0.f;
+    for (int i = lane; i < n; i += 32) {
+      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
+      const float m = __ldcg(p + D);
+      if (m != -INFINITY) ls = fmaf(__ldcg(p + D + 1), ex2(m - mx), ls);
+    }
+    const float r = mx + lg2(warp_sum(ls));
+    if (!lane) { R[warp] = r; if (!slice) a.row_r[vh * QG + warp] = r; }
+  }
+  __syncthreads();
+  const Row row = row_of(a, vh / hpr);
+  const int lo = SBG + slice * SLICE + warp * (SLICE / 8), hi = SBG * (row.groups - 1);
+  int qm[4], n = 0;
+  uint32_t bal[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int sb = lo + 32 * i + lane;
+    qm[i] = 0;
+    if (sb < hi) {
+      const float *p = a.lse + ((size_t)vh * a.nblocks + sb) * QG;
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) qm[i] |= (__ldcg(p + qi) - R[qi] > a.log2_tau) << qi;
+    }
+    bal[i] = __ballot_sync(FULL, qm[i] != 0);
+    n += __popc(bal[i]);
+  }
+  if (!lane) wc[warp] = n;
+  __syncthreads();
+  int off = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) { off += w < warp ? wc[w] : 0; total += wc[w]; }
+  int *items = a.items + ((size_t)vh * a.nslices + slice) * SLICE;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (qm[i]) items[off + __popc(bal[i] & ((1u << lane) - 1u))] = (lo + 32 * i + lane) << 4 | qm[i];
+    off += __popc(bal[i]);
+  }
+  if (!threadIdx.x) a.counts[(size_t)vh * a.nslices + slice] = total;
+}
+
+// ---- refine: full - coarse of every selected sub-block ----------------------------------------------------------------------
+template <int CB, int FB> struct RefineShape {
+  static constexpr int WARPS = 8, NST = 2;
+  static constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
+  static constexpr int STAGE = RC + RF + 1024;
+};
+template <int CB, int FB> struct __align__(128) RefineWarp {
+  uint8_t stage[RefineShape<CB, FB>::NST][RefineShape<CB, FB>::STAGE];
+  uint8_t qst[8 * QST_ROW];
+  uint8_t pst[128];  // rows 0..3: P under the full scores, rows 4..7: under the coarse scores; 16 tokens each
+  uint64_t bar[RefineShape<CB, FB>::NST];
+};
+
+template <int CB, int FB, int QG>
+__global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_kernel(const fbla_k_decode a) {
+  using Sh = RefineShape<CB, FB>;
+  constexpr float HOFF = .5f * ((1 << FB) - 1);
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  RefineWarp<CB, FB> *ws = reinterpret_cast<RefineWarp<CB, FB> *>(smem_raw);
+  int *pre = reinterpret_cast<int *>(smem_raw + sizeof(RefineWarp<CB, FB>) * Sh::WARPS);  // [entries + 1]
+  __shared__ int chunk_sum[256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
+  const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, entries = vheads * a.nslices;
+  // exclusive prefix of the slices' counts: pre[e], e = vh * nslices + slice
+  {
+    const int per = (entries + 255) / 256, e0 = threadIdx.x * per, e1 = min(entries, e0 + per);
+    int sum = 0;
+    for (int e = e0; e < e1; ++e) sum += __ldcg(a.counts + e);
+    chunk_sum[threadIdx.x] = sum;
+    __syncthreads();
+    if (warp == 0) {
+      int run = 0;
+      for (int i0 = 0; i0 < 256; i0 += 32) {
+        const int v = chunk_sum[i0 + lane];
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(FULL, x, o); x += lane >= o ? y : 0; }
+        chunk_sum[i0 + lane] = run + x - v;
+        run += __shfl_sync(FULL, x, 31);
+      }
+      if (!lane) pre[entries] = run;
+    }
+    __syncthreads();
+    int acc = chunk_sum[threadIdx.x];
+    for (int e = e0; e < e1; ++e) { pre[e] = acc; acc += __ldcg(a.counts + e); }
+    __syncthreads();
+    if (blockIdx.x == 0)  // for the merge: the first item of every virtual head, and the total
+      for (int v = threadIdx.x; v <= vheads; v += blockDim.x) a.item_off[v] = pre[v * a.nslices];
+  }
+  const int total = pre[entries];
+  const long long rw = (long long)gridDim.x * Sh::WARPS;
+  const int per = (int)ceil_div(total, rw), gw = blockIdx.x * Sh::WARPS + warp;
+  const int lo = gw * per, hi = min(total, lo + per);
+  if (lo >= hi) return;
+  RefineWarp<CB, FB> &w = ws[warp];
+  for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
+  reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < Sh::NST; ++s) mbar_init(&w.bar[s], 1);
+    mbar_init_fence();
+  }
+  __syncwarp();
+  // entry of item lo: the last e with pre[e] <= lo
+  int fe;
+  {
+    int l = 0, h = entries;  // pre[l] <= lo < pre[h]
+    while (h - l > 1) { const int mid = (l + h) >> 1; if (pre[mid] <= lo) l = mid; else h = mid; }
+    fe = l;
+  }
+  int ce = fe;
+  auto item_at = [&](int k, int &e) {  // item k (>= the previous k): its entry (advanced) and value
+    while (pre[e + 1] <= k) ++e;
+    return __ldcg(a.items + (size_t)e * SLICE + (k - pre[e]));
+  };
+  auto issue = [&](int it, int e, int s) {  // lane 0
+    const int vh = e / a.nslices, bh = vh / a.vg, sb = it >> 4;
+    const size_t unit = (size_t)bh * a.hs + (size_t)(sb / SBG) * a.gs, rec = unit * SBG + sb % SBG;
+    mbar_expect_tx(&w.bar[s], Sh::STAGE);
+    bulk_g2s(w.stage[s], a.c.coarse + rec * Sh::RC, Sh::RC, &w.bar[s]);
+    bulk_g2s(w.stage[s] + Sh::RC, a.c.fine + rec * Sh::RF, Sh::RF, &w.bar[s]);
+    bulk_g2s(w.stage[s] + Sh::RC + Sh::RF, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
+  };
+  int fit[Sh::NST];  // the items in flight (warp-uniform)
+#pragma unroll
+  for (int s = 0; s < Sh::NST; ++s)
+    if (lo + s < hi) {
+      fit[s] = item_at(lo + s, fe);
+      if (lane == 0) issue(fit[s], fe, s);
+    }
+  Run run;  // m unused: corrections are already in units of 2^-R
+  float4 q4[QG];
+  float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
+  uint32_t B[8];
+  int cur_vh = -1;
+  long long cur_unit = -1;
+  for (int k = lo; k < hi; ++k) {
+    const int s = (k - lo) % Sh::NST;
+    const int it = item_at(k, ce), vh = ce / a.nslices, sb = it >> 4;
+    if (vh != cur_vh) {
+      if (cur_vh >= 0) write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
+      cur_vh = vh; cur_unit = -1;
+      reset<QG>(run);
+      const int b = vh / hpr, hir = vh - b * hpr;
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) {
+        const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, b, hir, qi) * D) + lane);
+        q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) Rq[e] = query_valid<QG>(tig, e) ? __ldcg(a.row_r + vh * QG + 2 * (tig & 1) + e) : 0.f;
+    }
+    const bool ok = mbar_wait_bounded(&w.bar[s], ((k - lo) / Sh::NST) & 1);
+    if (!__all_sync(FULL, ok)) {
+      if (lane == 0) report(a, 3);
+      return;
+    }
+    const uint8_t *crec = w.stage[s], *frec = crec + Sh::RC, *meta = frec + Sh::RF;
+    const long long unit = (long long)vh * a.nblocks + sb / SBG;
+    if (unit != cur_unit) {  // the group's qhat: the same function of the same inputs as the coarse pass
+      cur_unit = unit;
+      __syncwarp();
+      const uint4 km = lds128(meta + 16 * lane);
+#pragma unroll
+      for (int qi = 0; qi < QG; ++qi) {
+        float sq, qb, qsum;
+        quantize_query(km, q4[qi], a.sl, reinterpret_cast<uint32_t *>(w.qst + QST_ROW * qi), lane, sq, qb, qsum);
+        const float c = fmaf(__fmul_rn(sq, HOFF), qsum, qb), s2 = __fmul_rn(sq, (float)(1 << FB));
+#pragma unroll
+        for (int e = 0; e < 2; ++e)
+          if (qi == 2 * (tig & 1) + e) { c0[e] = c; sqc[e] = s2; sqf[e] = sq; qbf[e] = qb; }
+      }
+      __syncwarp();
+      qhat_frag<CB>(w.qst, gid, tig, B);
+    }
+    float xh[4], xl[4];
+    qk_tile<CB>(crec, gid, tig, B, xh);
+    qk_tile<FB>(frec, gid, tig, B, xl);
+    // columns 2 tig + e (tig < 2: queries): coarse and full scores of tokens gid, gid + 8
+    float mc[2], mf[2], sc[2][2], sf[2][2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sc[e][r] = fmaf(sqc[e], xh[2 * r + e], c0[e]);
+        sf[e][r] = fmaf(sqf[e], fmaf((float)(1 << FB), xh[2 * r + e], xl[2 * r + e]), qbf[e]);
+      }
+      float vc = fmaxf(sc[e][0], sc[e][1]), vf = fmaxf(sf[e][0], sf[e][1]);
+#pragma unroll
+      for (int o = 4; o <= 16; o <<= 1) { vc = fmaxf(vc, __shfl_xor_sync(FULL, vc, o)); vf = fmaxf(vf, __shfl_xor_sync(FULL, vf, o)); }
+      mc[e] = vc; mf[e] = vf;
+    }
+    if (tig < 2) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e)
+        if (query_valid<QG>(tig, e)) {
+          const int qe = 2 * tig + e;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            w.pst[qe * 16 + gid + 8 * r] = (uint8_t)__float_as_uint(fmaf(ex2(sf[e][r] - mf[e]), 255.f, MAGICF));
+            w.pst[(4 + qe) * 16 + gid + 8 * r] = (uint8_t)__float_as_uint(fmaf(ex2(sc[e][r] - mc[e]), 255.f, MAGICF));
+          }
+        }
+    }
+    __syncwarp();
+    // Value products: column gid < 4: query gid under the full scores, gid >= 4: query gid - 4 under the coarse ones.
+    // Thread (gid, tig) reads columns 2 tig + e: tig < 2 holds the full-score sums of queries 2 tig + e, tig >= 2 the
+    // coarse-score sums of queries 2 (tig - 2) + e.
+    const bool cset = tig >> 1;
+    const uint32_t b0 = lds32(w.pst + 4 * lane);
+    float wgt[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float mco = __shfl_xor_sync(FULL, mc[e], 2);
+      const bool on = query_valid<QG>(tig, e) && ((it >> (2 * (tig & 1) + e)) & 1);
+      wgt[e] = on ? (cset ? -ex2(mco - Rq[e]) : ex2(mf[e] - Rq[e])) : 0.f;
+    }
+    {
+      float sp[2];  // sum p of the thread's two columns: a product with an all-ones A
+      {
+        uint32_t d[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+        mma_u8u8_k16(d, 0x01010101u, 0x01010101u, b0);
+        sp[0] = isum(d[0]); sp[1] = isum(d[1]);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) run.l[e] = fmaf(wgt[e], sp[e], run.l[e]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint32_t vh4[4], vl4[4];
+        v_slots<CB>(crec, 8 * u + gid, tig, vh4);
+        v_slots<FB>(frec, 8 * u + gid, tig, vl4);
+        uint32_t h01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, h23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+        uint32_t l01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, l23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
+        mma_u8u8_k16(h01, vh4[0], vh4[1], b0);
+        mma_u8u8_k16(h23, vh4[2], vh4[3], b0);
+        mma_u8u8_k16(l01, vl4[0], vl4[1], b0);
+        mma_u8u8_k16(l23, vl4[2], vl4[3], b0);
+        const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
+        const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const float vhi = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc)), vlo = __fmul_rn(vs[cc], v_unscale<FB>(cc));
+          const float vbc = fmaf(vs[cc], HOFF, vb[cc]);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float yh = isum(cc < 2 ? h01[2 * (cc & 1) + e] : h23[2 * (cc & 1) + e]);
+            const float yl = isum(cc < 2 ? l01[2 * (cc & 1) + e] : l23[2 * (cc & 1) + e]);
+            const float full = fmaf(vb[cc], sp[e], fmaf(vhi, yh, vlo * yl));
+            const float coarse = fmaf(vbc, sp[e], vhi * yh);
+            run.o[u][cc][e] = fmaf(wgt[e], cset ? coarse : full, run.o[u][cc][e]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (k + Sh::NST < hi) {
+      fit[s] = item_at(k + Sh::NST, fe);
+      if (lane == 0) { fence_async_smem(); issue(fit[s], fe, s); }
+    }
+  }
+  write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
+}
+
+// ---- merge: out = (sum 2^(m_c - R) o_c + sum do) / (sum 2^(m_c - R) l_c + sum dl), BF16 ---------------------------------
+template <int QG>
+__global__ void __launch_bounds__(128) merge_kernel(const fbla_k_decode a) {
+  const int vh = blockIdx.x / QG, qi = blockIdx.x % QG, ch = threadIdx.x;
+  const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, b = vh / hpr, hir = vh - b * hpr;
+  const Slots s = slots_of(a, vh);
+  const float Rq = __ldcg(a.row_r + vh * QG + qi);
+  float O = 0.f, L = 0.f;
+  for (int w = s.c0; w <= s.c1; ++w) {
+    const float *p = coarse_slot(a, w, vh, qi);
+    const float m = __ldcg(p + D), e = m == -INFINITY ? 0.f : ex2(m - Rq);
+    L = fmaf(e, __ldcg(p + D + 1), L); O = fmaf(e, __ldcg(p + ch), O);
+  }
+  for (int x = s.x0; x <= s.x1; ++x) {
+    const float *p = window_slot(a, x, vh, qi);
+    const float m = __ldcg(p + D), e = m == -INFINITY ? 0.f : ex2(m - Rq);
+    L = fmaf(e, __ldcg(p + D + 1), L); O = fmaf(e, __ldcg(p + ch), O);
+  }
+  const int i0 = __ldcg(a.item_off + vh), i1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
+  if (i1 > i0) {
+    const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
+    for (int w = i0 / per; w <= (i1 - 1) / per; ++w) {
+      const float *p = a.dpart + ((size_t)(w + vh) * QG + qi) * PSTRIDE;
+      L += __ldcg(p + D); O += __ldcg(p + ch);
+    }
+  }
+  a.out[(size_t)q_row(a, b, hir, qi) * D + ch] = f32_to_bf16(__fdividef(O, L));
+}
+
+template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a, cudaStream_t stream) {
+  const int vheads = a.batch * a.kv_heads * a.vg;
+  const size_t csm = sizeof(CoarseSmem<CB>);
+  const size_t rsm = sizeof(RefineWarp<CB, FB>) * RefineShape<CB, FB>::WARPS + sizeof(int) * ((size_t)vheads * a.nslices + 1);
+  static thread_local int configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(refine_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = 1;
+  }
+  if (rsm > 227 * 1024) return cudaErrorInvalidValue;
+  coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + 1), csm, stream>>>(a);
+  select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a);
+  refine_kernel<CB, FB, QG><<<a.refine_ctas, 32 * RefineShape<CB, FB>::WARPS, rsm, stream>>>(a);
+  merge_kernel<QG><<<vheads * QG, 128, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace fbla
+
+extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  a->coarse_ctas = sms;
+  a->coarse_warps = a->cb == 4 ? fbla::CoarseShape<4>::WARPS : fbla::CoarseShape<3>::WARPS;
+  a->refine_ctas = sms;
+  a->refine_warps = 8;
+  return cudaSuccess;
+}
+
+extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream) {
+  using namespace fbla;
+  if (a->cb == 3) {
+    switch (a->qg) {
+      case 1: return launch_all<3, 3, 1>(*a, stream);
+      case 2: return launch_all<3, 3, 2>(*a, stream);
+      default: return launch_all<3, 3, 4>(*a, stream);
+    }
+  }
+  switch (a->qg) {
+    case 1: return launch_all<4, 2, 1>(*a, stream);
+    case 2: return launch_all<4, 2, 2>(*a, stream);
+    default: return launch_all<4, 2, 4>(*a, stream);
+  }
+}

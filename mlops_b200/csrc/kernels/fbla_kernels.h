@@ -1,0 +1,77 @@
+// The thin C ABI between the C++ host layer (validation, geometry, dispatch) and the CUDA kernels: plain structs of
+// pointers and sizes, one launcher per pass. The host layer fills these; nothing here validates.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+  uint8_t *coarse, *fine;
+  uint16_t *meta, *sink_k, *sink_v, *open_k, *open_v;
+} fbla_k_cache;
+
+// ---- decode -------------------------------------------------------------------------------------------------------
+// Virtual heads: a KV head with r = q_heads / kv_heads queries is served as vg = r / qg virtual heads of qg in {1, 2, 4}
+// queries each (virtual head vh = kv_head_linear * vg + j owns queries j * qg .. j * qg + qg - 1 of its KV head).
+// Scratch arrays (all written before they are read; no initial contents needed):
+//   lse    [VH][nblocks][qg]  float  log2 mass of every closed sub-block under the coarse scores
+//   part   [TW + 2 VH][qg][130] float  (m, l, o[128]) partials: slot w + vh for coarse warp w, TW + VH + vh for the BF16 windows
+//   dpart  [RW + VH][qg][129] float  (dl, do[128]) corrections of refine warp w at slot w + vh
+//   row_r  [VH][qg]           float  log2 of the row's total coarse mass
+//   counts [VH][nslices]      int    selected sub-blocks per slice of 1024 sub-blocks
+//   items  [VH][nslices][1024] int   (sub-block << 4) | query mask, in sub-block order
+//   item_off [VH * nslices + 1] int  exclusive prefix of counts (written by the refine pass for the merge)
+//   status [4]                int    0 ok; nonzero: a bounded wait gave up (which pass, which CTA)
+typedef struct {
+  fbla_k_cache c;
+  const uint16_t *q;
+  uint16_t *out;
+  float *lse, *part, *dpart, *row_r;
+  int *counts, *items, *item_off, *status;
+  const int *length;  // NULL, or device lengths: tokens of batch row b = length[b * lstride] + tokens
+  int lstride;
+  int batch, q_heads, kv_heads, tokens;
+  int nblocks, nslices;  // layout of lse / items: sub-blocks and slices per head at the capacity
+  int hs, gs;            // units between KV heads and between groups
+  int qg, vg;            // queries per virtual head, virtual heads per KV head
+  int cb, fb;            // plane bits
+  int coarse_ctas, coarse_warps;  // persistent coarse CTAs and warps per CTA (TW = coarse_ctas * coarse_warps)
+  int refine_ctas, refine_warps;  // RW = refine_ctas * refine_warps
+  float sl, log2_tau;
+} fbla_k_decode;
+
+#define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
+#define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
+
+cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);
+// occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
+cudaError_t fbla_k_decode_shape(fbla_k_decode *a);
+
+// ---- prefill: close the chunk's groups, attention, update the BF16 windows --------------------------------------------
+typedef struct {
+  fbla_k_cache c;
+  const uint16_t *q, *k, *v;  // q NULL: append only
+  uint16_t *out;
+  int64_t out_hs;             // elements between q heads of out
+  int out_ts;                 // elements between positions of out
+  const int *length;          // NULL, or the chunk starts at length[row * lstride] + n0
+  const int *dcount;          // NULL, or the chunk's token count on the device (count is then its ceiling)
+  int lstride;
+  int batch, q_heads, kv_heads, n0, count;
+  int hs, gs;
+  int cb, fb;
+  float sl;
+} fbla_k_prefill;
+
+// close_blocks: grid x of the close pass (groups the chunk can close); 0 skips it
+cudaError_t fbla_k_close_launch(const fbla_k_prefill *a, int close_blocks, cudaStream_t stream);
+cudaError_t fbla_k_finish_launch(const fbla_k_prefill *a, cudaStream_t stream);
+cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,158 @@
+"""Helpers of the GPU parity tests: drive a library that exports the mlops_fbla C ABI (the product, or the reference
+build under oracle/_ref) on torch device tensors, and move caches between numpy (oracle side) and the device."""
+import ctypes
+import os
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+OURS = os.path.join(ROOT, "mlops_b200", "lib", "libmlops_attention.so")
+REF = os.path.join(ROOT, "oracle", "_ref", "libmlops_attention_ref.so")
+FORMATS = {"3+3": (3, 3, 0), "4+2": (4, 2, 1)}
+
+
+class Config(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int), ("q_heads", ctypes.c_int), ("kv_heads", ctypes.c_int), ("tokens", ctypes.c_int),
+                ("scale", ctypes.c_float), ("tau", ctypes.c_float), ("format", ctypes.c_int), ("capacity", ctypes.c_int),
+                ("head_stride", ctypes.c_int), ("group_stride", ctypes.c_int),
+                ("out_head_stride", ctypes.c_int64), ("out_token_stride", ctypes.c_int64), ("length_stride", ctypes.c_int)]
+
+
+class Cache(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("coarse", "fine", "meta", "sink_k", "sink_v", "open_k", "open_v", "images")]
+
+
+def bf16_tensor(bits, device="cuda"):
+    """numpy uint16 BF16 bit patterns -> torch bfloat16 tensor on the device"""
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(device).view(torch.bfloat16)
+
+
+def bits_of(t):
+    """torch bfloat16 tensor -> numpy uint16 bit patterns"""
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def bf16_ulp(x):
+    """spacing of BF16 numbers at |x| (numpy float64 array)"""
+    e = np.floor(np.log2(np.maximum(np.abs(x), 1e-38)))
+    return np.exp2(e - 7)
+
+
+class CLib:
+    """One loaded library exporting the mlops_fbla C ABI."""
+
+    def __init__(self, path):
+        self.path = path
+        self.lib = ctypes.CDLL(path)  # RTLD_LOCAL: the product and the reference export the same symbol names
+        L = self.lib
+        vp, cp, kp = ctypes.c_void_p, ctypes.POINTER(Config), ctypes.POINTER(Cache)
+        L.mlops_fbla_decode_scratch_bytes.restype = ctypes.c_size_t
+        L.mlops_fbla_decode_scratch_bytes.argtypes = [cp]
+        L.mlops_fbla_decode.restype = ctypes.c_int
+        L.mlops_fbla_decode.argtypes = [cp, vp, kp, vp, vp, ctypes.c_size_t, vp]
+        L.mlops_fbla_decode_at.restype = ctypes.c_int
+        L.mlops_fbla_decode_at.argtypes = [cp, vp, vp, kp, vp, vp, ctypes.c_size_t, vp]
+        L.mlops_fbla_prefill.restype = ctypes.c_int
+        L.mlops_fbla_prefill.argtypes = [cp, ctypes.c_int, vp, vp, vp, kp, vp, vp]
+        L.mlops_fbla_prefill_at.restype = ctypes.c_int
+        L.mlops_fbla_prefill_at.argtypes = [cp, vp, vp, ctypes.c_int, vp, vp, vp, kp, vp, vp]
+        L.mlops_fbla_append_at.restype = ctypes.c_int
+        L.mlops_fbla_append_at.argtypes = [cp, vp, vp, vp, kp, vp]
+        L.mlops_fbla_last_error.restype = ctypes.c_char_p
+
+    def error(self):
+        return self.lib.mlops_fbla_last_error().decode()
+
+    @staticmethod
+    def empty(batch, kv_heads, capacity, mode, device="cuda"):
+        cb, fb, fmt = FORMATS[mode]
+        cg = (capacity + 127) // 128
+        z = lambda shape, dt: torch.zeros(shape, dtype=dt, device=device)
+        c = dict(coarse=z((batch, kv_heads, cg * 8, 2 * cb * 256), torch.uint8), fine=z((batch, kv_heads, cg * 8, 2 * fb * 256), torch.uint8),
+                 meta=z((batch, kv_heads, cg, 512), torch.bfloat16), tokens=0, capacity=capacity, mode=mode, batch=batch, kv_heads=kv_heads)
+        for n in ("sink_k", "sink_v", "open_k", "open_v"):
+            c[n] = z((batch, kv_heads, 128, 128), torch.bfloat16)
+        return c
+
+    @staticmethod
+    def _cache(c):
+        return Cache(*[c[n].data_ptr() for n in ("coarse", "fine", "meta", "sink_k", "sink_v", "open_k", "open_v")], None)
+
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def prefill(self, c, k, v, q=None, scale=0.0, q_heads=None):
+        """k, v [B, Hkv, n, 128] bf16 device tensors appended in place; with q returns [B, Hq, n, 128] bf16."""
+        n = k.shape[2]
+        qh = q.shape[1] if q is not None else (q_heads or c["kv_heads"])
+        cfg = Config(c["batch"], qh, c["kv_heads"], c["tokens"], scale, 0.0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, 0)
+        out = torch.empty_like(q) if q is not None else None
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_prefill(ctypes.byref(cfg), n, q.data_ptr() if q is not None else None, k.data_ptr(), v.data_ptr(),
+                                         ctypes.byref(kc), out.data_ptr() if out is not None else None, self._stream())
+        if st:
+            raise RuntimeError(f"prefill status {st}: {self.error()}")
+        c["tokens"] += n
+        return out
+
+    def encode(self, k, v, mode, capacity=None):
+        B, H, N, _ = k.shape
+        c = self.empty(B, H, N if capacity is None else capacity, mode, k.device)
+        self.prefill(c, k, v)
+        return c
+
+    def scratch(self, c, q_heads, poison=0xFF):
+        cfg = Config(c["batch"], q_heads, c["kv_heads"], c["tokens"], 0, 0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, 0)
+        n = self.lib.mlops_fbla_decode_scratch_bytes(ctypes.byref(cfg))
+        assert n > 0, self.error()
+        return torch.full((n,), poison, dtype=torch.uint8, device=c["coarse"].device)
+
+    def decode(self, c, q, scale=0.0, tau=0.0, scratch=None):
+        """q [B, Hq, 128] bf16 -> [B, Hq, 128] bf16"""
+        cfg = Config(c["batch"], q.shape[1], c["kv_heads"], c["tokens"], scale, tau, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, 0)
+        if scratch is None:
+            scratch = self.scratch(c, q.shape[1])
+        out = torch.empty_like(q)
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_decode(ctypes.byref(cfg), q.data_ptr(), ctypes.byref(kc), out.data_ptr(), scratch.data_ptr(),
+                                        scratch.numel(), self._stream())
+        if st:
+            raise RuntimeError(f"decode status {st}: {self.error()}")
+        self.last_scratch = scratch
+        return out
+
+
+def cache_to_numpy(c):
+    """device cache -> the oracle's numpy layout (heads flattened)"""
+    B, H = c["batch"], c["kv_heads"]
+    out = dict(tokens=c["tokens"], capacity=c["capacity"], mode=c["mode"], batch=B, kv_heads=H)
+    out["coarse"] = c["coarse"].cpu().numpy().reshape(B * H, -1, c["coarse"].shape[-1])
+    out["fine"] = c["fine"].cpu().numpy().reshape(B * H, -1, c["fine"].shape[-1])
+    out["meta"] = bits_of(c["meta"]).reshape(B * H, -1, 512)
+    for n in ("sink_k", "sink_v", "open_k", "open_v"):
+        out[n] = bits_of(c[n]).reshape(B * H, 128, 128)
+    return out
+
+
+def assert_cache_equal(dev_cache, np_cache, what=""):
+    got = cache_to_numpy(dev_cache)
+    for key in ("meta", "coarse", "fine", "sink_k", "sink_v", "open_k", "open_v"):
+        a, b = got[key], np_cache[key].reshape(got[key].shape)
+        if not np.array_equal(a, b):
+            bad = np.argwhere(a != b)
+            raise AssertionError(f"{what} {key}: {len(bad)} differing elements, first at {bad[0].tolist()}: {a[tuple(bad[0])]} vs {b[tuple(bad[0])]}")
+
+
+def check_close(got_bf16_bits, want64, what="", tol=2e-3):
+    """The acceptance rule for attention outputs: |bf16(ours) - oracle| <= tol * max|oracle| + half a BF16 ulp of the
+    element (the output's own rounding), where the oracle value is the unrounded float64 model."""
+    from tests import datagen
+    got = datagen.bf16_to_f32(got_bf16_bits).astype(np.float64).reshape(want64.shape)
+    scale = np.abs(want64).max()
+    err = np.abs(got - want64)
+    bound = tol * scale + 0.5 * bf16_ulp(want64)
+    worst = (err - bound).max()
+    rel = err.max() / scale
+    assert worst <= 0, f"{what}: max|err| / max|ref| = {rel:.3e} exceeds {tol:g} (+ half ulp) by {worst:.3e}"
+    return rel
