@@ -122,8 +122,8 @@ mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *
   const int r = c->q_heads / c->kv_heads;
   a.qg = decode_group(r);
   a.vg = r / a.qg;
-  if ((long long)c->batch * c->kv_heads * a.vg * L.nslices > 40000)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch * kv_heads * virtual heads * slices of 16384 tokens exceeds 40000 (split the batch)", fn);
+  if ((long long)c->batch * c->kv_heads * a.vg * L.nslices > 36000)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch * kv_heads * virtual heads * slices of 16384 tokens exceeds 36000 (split the batch)", fn);
   a.c = kcache(k);
   a.q = q; a.out = out;
   char *base = static_cast<char *>(scratch);

@@ -824,6 +824,7 @@ __global__ void __launch_bounds__(128) merge_kernel(const fbla_k_decode a) {
   a.out[(size_t)q_row(a, b, hir, qi) * D + ch] = f32_to_bf16(__fdividef(O, L));
 }
 
+constexpr int REFINE_SMEM_MAX = 220 * 1024;  // dynamic shared memory of the refine pass (its ring + the slice prefix)
 template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a, cudaStream_t stream) {
   const int vheads = a.batch * a.kv_heads * a.vg;
   const size_t csm = sizeof(CoarseSmem<CB>);
@@ -834,11 +835,11 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(refine_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    e = cudaFuncSetAttribute(refine_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, REFINE_SMEM_MAX);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = 1;
   }
-  if (rsm > 227 * 1024) return cudaErrorInvalidValue;
+  if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + 1), csm, stream>>>(a);
   select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a);
   refine_kernel<CB, FB, QG><<<a.refine_ctas, 32 * RefineShape<CB, FB>::WARPS, rsm, stream>>>(a);

@@ -46,7 +46,7 @@ def uneven_case(seed, batch, q_heads, kv_heads, tokens, q_rows=None):
 
 def edge_group(seed):
     """[128, 128] BF16 group with hard quantizer channels: constant, all-negative, zero-minimum, huge range, tiny
-    range, +-0, subnormal-ish."""
+    range, all-zero, very small."""
     rng = np.random.default_rng(seed)
     x = rng.standard_normal((128, 128), dtype=np.float32)
     x[:, 0] = 1.25                      # constant: step 0
@@ -54,7 +54,7 @@ def edge_group(seed):
     x[:, 2] = np.abs(x[:, 2]); x[5, 2] = 0.0      # minimum exactly 0
     x[:, 3] *= 1e4                      # huge range
     x[:, 4] = 3.0 + 1e-3 * x[:, 4]      # tiny range relative to the offset
-    x[:, 5] = 0.0; x[7, 5] = -0.0       # zeros of both signs
+    x[:, 5] = 0.0                       # all zero
     x[:, 6] *= 1e-20                    # very small magnitudes (steps below 1e-30 are clamped by the reference's Python twin only)
     x[:, 7] = -x[:, 7] * 8.0            # outlier channel
     x[:, 8] = np.where(np.arange(128) % 2 == 0, 1.0, -1.0)  # two-valued

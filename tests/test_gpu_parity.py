@@ -61,15 +61,29 @@ def test_cache_bytes_bit_exact(ours, oracle, mode, B, H, N, cap, chunks, gen, se
         gu.assert_cache_equal(c, o, f"{mode} after {t} tokens")
 
 
+def _edge_kv(seed):
+    x = datagen.edge_group(seed).copy()
+    x[7, 5] = 0x8000                                          # a -0 among +0: the minimum is -0 on the GPU (min.f32 orders signed zeros)
+    k = np.concatenate([x, x[:1]])[None, None]                # 129 tokens: the group closes
+    v = np.concatenate([x[::-1], x[:1]])[None, None]
+    return k, v
+
+
 def test_quantizer_edge_channels(ours, oracle):
     """Constant, all-negative, zero-minimum, huge, tiny, signed-zero and two-valued channels."""
     for seed in (3, 4):
-        x = datagen.edge_group(seed)
-        k = np.concatenate([x, x[:1]])[None, None]            # 129 tokens: the group closes
-        v = np.concatenate([x[::-1], x[:1]])[None, None]
+        k, v = _edge_kv(seed)
         for mode in MODES:
             c = ours.encode(*_dev(k, v), mode)
             gu.assert_cache_equal(c, oracle.encode(k, v, mode), f"edge {seed} {mode}")
+
+
+def test_quantizer_edge_channels_reference_library(ours, ref):
+    for seed in (3, 4):
+        k, v = _edge_kv(seed)
+        for mode in MODES:
+            a, b = ours.encode(*_dev(k, v), mode), ref.encode(*_dev(k, v), mode)
+            gu.assert_cache_equal(a, gu.cache_to_numpy(b), f"edge {seed} {mode} vs reference library")
 
 
 @pytest.mark.parametrize("mode", MODES)
