@@ -1,0 +1,267 @@
+"""Headline benchmark of the FBLA hot path: batched compressed-KV decode.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): BASELINE configs[1] -- batch 8, 32 query heads / 8 KV heads, head_dim 128, context 16384 per
+sequence (131072 context tokens in all), 4+2 mode, seeded BF16 N(0,1) inputs with 4 outlier channels per KV head
+scaled x8, softmax scale 1/sqrt(128), default tau. One step = one decode call (one new token per sequence) over the
+resident compressed cache, which the library itself wrote (quantize-on-write).
+N > 1: one process per GPU (torchrun), each rank decodes its own batch of 8 sequences -- the path shards by batch row
+and KV head with no exchange -- so per-GPU work is fixed ("weak") and value = tokens of all ranks / max time.
+
+Prints ONE JSON line: metric decode tokens/s with the cache resident in HBM (`value`), the same through the Python
+interface with host q / output buffers (`e2e`), the roofline of the dominant kernel, a CPU baseline (the oracle's port
+of the reference's host-side model, a bounded sample), clocks sampled during the timed region.
+`--impl reference` times the reference's host-side path on the CPU cores of this machine (the oracle port).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+CFG = dict(batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002)
+METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+
+
+def make_inputs(rank=0):
+    from tests import datagen
+    return datagen.baseline_case(CFG["seed"] + 7919 * rank, CFG["batch"], CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=True)
+
+
+def algorithmic_bytes(share):
+    """Bytes one decode must move (the reference bench's accounting, attention/fbla/bench/bench_fbla.cu:136-141):
+    coarse records + 1 KiB metadata of every closed group, the BF16 sink and open tokens (K and V), and coarse + fine
+    records of the share of closed sub-blocks that some query of the KV head refines."""
+    cb, fb = (3, 3) if CFG["mode"] == "3+3" else (4, 2)
+    heads = CFG["batch"] * CFG["kv_heads"]
+    groups = (CFG["tokens"] + 127) // 128
+    closed = max(groups - 2, 0)
+    open_tokens = CFG["tokens"] - 128 * (groups - 1)
+    rc, rf = 2 * cb * 256, 2 * fb * 256
+    coarse = heads * closed * (8 * rc + 1024)
+    windows = heads * (128 + open_tokens) * 128 * 2 * 2
+    refine = share * heads * closed * 8 * (rc + rf)
+    return coarse + windows + refine, dict(coarse_and_meta=coarse, bf16_windows=windows, refine=refine)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.nv:
+            return
+        nv = self.nv
+        names = {nv.nvmlClocksEventReasonHwSlowdown: "hw_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                 nv.nvmlClocksEventReasonSwThermalSlowdown: "sw_thermal_slowdown", nv.nvmlClocksEventReasonSwPowerCap: "sw_power_cap"}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def result(self):
+        self.stop_flag = True
+        self.join(timeout=1.0)
+        return dict(sm_mhz=float(np.median(self.samples)) if self.samples else None, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                    samples=len(self.samples))
+
+
+def cpu_baseline(rows=8, repeats=3):
+    """The oracle's port of the reference's host-side decode model on `rows` of the workload's batch rows, `repeats` times."""
+    from oracle import fbla_oracle as orc
+    from tests import datagen
+    q, k, v = datagen.baseline_case(CFG["seed"], rows, CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=True)
+    cache = orc.encode(k, v, CFG["mode"])
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        _, stats = orc.decode(q, cache, stats=True)
+    dt = time.perf_counter() - t0
+    return dict(value=rows * repeats / dt, unit=UNIT, cores=orc.threads(), kind="port",
+                sample=f"{rows} of {CFG['batch']} batch rows of the workload x {repeats} (float64 decode model on the packed cache, cache prebuilt), {dt:.1f} s"), stats
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(max(1, min(args.warmup, 1))):
+        cpu_baseline(8, 1)
+    base = None
+    for _ in range(max(1, min(args.steps, 3))):
+        base, _ = cpu_baseline(8, 2)
+        vals.append(base["value"])
+    v = float(np.median(vals))
+    base["value"] = v
+    line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=len(vals), warmup=1, ms_per_step=1000.0 * CFG["batch"] / v,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64", data="synthetic", impl="reference",
+                config=dict(workload="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1])", **{k: CFG[k] for k in ("batch", "q_heads", "kv_heads", "tokens", "mode")}),
+                cpu_baseline=base, e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import ctypes
+
+    import torch
+    import torch.distributed as dist
+
+    from mlops_b200 import attention
+    from mlops_b200.attention import _C
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    q, k, v = make_inputs(rank)
+    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16)
+    q_host = bf(q).pin_memory()
+    qd = q_host.to(dev)
+    # two caches (the same tokens, separate memory), alternated step by step: the working set (2 x 210 MB) exceeds L2
+    copies = []
+    kd, vd = bf(k).to(dev), bf(v).to(dev)
+    for _ in range(2):
+        copies.append(attention.encode(kd, vd, CFG["mode"]))
+    del kd, vd
+    c0 = copies[0]
+    cfg = _C.Config(CFG["batch"], CFG["q_heads"], CFG["kv_heads"], c0.tokens, 0.0, 0.0, c0.format, c0.capacity, 0, 0, 0, 0, 0)
+    nbytes = _C.lib.mlops_fbla_decode_scratch_bytes(ctypes.byref(cfg))
+    scratch = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(qd)
+    caches = [_C.Cache(c.coarse.data_ptr(), c.fine.data_ptr(), c.meta.data_ptr(), c.sink_k.data_ptr(), c.sink_v.data_ptr(), c.open_k.data_ptr(),
+                       c.open_v.data_ptr(), None) for c in copies]
+
+    def step(i, stream):
+        st = _C.lib.mlops_fbla_decode(ctypes.byref(cfg), qd.data_ptr(), ctypes.byref(caches[i & 1]), out.data_ptr(), scratch.data_ptr(), nbytes,
+                                      ctypes.c_void_p(stream.cuda_stream))
+        if st:
+            raise RuntimeError(_C.last_error())
+
+    stream = torch.cuda.current_stream()
+    for i in range(max(args.warmup, 3)):
+        step(i, stream)
+    torch.cuda.synchronize()
+    status = scratch[-256:].view(torch.int32)[:2].tolist()
+    if status[0]:
+        raise RuntimeError(f"a bounded wait gave up: status {status}")
+    # refined share of (KV head, sub-block) pairs, from the device's own select pass
+    vheads, nsl = CFG["batch"] * CFG["kv_heads"], max(1, ((CFG["tokens"] + 127) // 128 * 8 + 1023) // 1024)
+    share = refine_share(scratch, cfg, _C, vheads, nsl)
+    abytes, parts = algorithmic_bytes(share)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: K steps between CUDA events on the launching stream ----------------------------
+    sampler = ClockSampler(local)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(i, stream)
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.result()
+    # ---- end to end through the Python interface: host q -> device, decode, output -> host, every step -----------------
+    light = os.environ.get("FBLA_BENCH_LIGHT") == "1"  # profiling runs: skip the end-to-end and CPU legs
+    out_host = torch.empty(q_host.shape, dtype=torch.bfloat16).pin_memory()
+    for i in range(3):
+        attention.decode(q_host.to(dev, non_blocking=True), copies[i & 1])
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(1 if light else args.steps):
+        o = attention.decode(q_host.to(dev, non_blocking=True), copies[i & 1])
+        out_host.copy_(o, non_blocking=True)
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) * (args.steps if light else 1)
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = t.tolist()
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak, peak_kind = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        per_step = ms / args.steps
+        achieved = abytes / (per_step * 1e-3) / 1e9
+        value = world * CFG["batch"] / (per_step * 1e-3)
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=per_step,
+                    higher_is_better=True, scaling="weak", vs_baseline=None, dtype="u8", data="synthetic",
+                    config=dict(workload="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1]); per rank", l2="two cache copies alternated, 2 x 210 MB > L2",
+                                refined_share=share, **{k: CFG[k] for k in ("batch", "q_heads", "kv_heads", "tokens", "mode")}),
+                    e2e=dict(value=world * CFG["batch"] / (ms_e2e / args.steps * 1e-3), unit=UNIT, h2d_bytes_per_step=q_host.numel() * 2,
+                             d2h_bytes_per_step=out_host.numel() * 2),
+                    gpu_launches=4 * args.steps,
+                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None, peak_kind=peak_kind,
+                                  kernel="decode call (coarse + select + refine + merge)", algorithmic_bytes=abytes, bytes_parts=parts),
+                    clocks=clocks)
+        if world == 1 and not light:
+            base, stats = cpu_baseline(8, 3)
+            line["cpu_baseline"] = base
+            line["config"]["oracle_refined_share"] = stats[3] / max(1, stats[2])
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def refine_share(scratch, cfg, _C, vheads, nsl):
+    """Fraction of closed (KV head, sub-block) pairs the select pass listed: total items / closed sub-blocks. The total is
+    the last word of the item_off array (offsets follow the scratch layout of mlops_b200/csrc/host/fbla_api.cpp)."""
+    import torch
+    up = lambda n: (n + 255) & ~255
+    items_total_off = scratch.numel() - 256 - up((vheads + 1) * 4) + vheads * 4
+    total = int(scratch[items_total_off:items_total_off + 4].view(torch.int32).item())
+    groups = (cfg.tokens + 127) // 128
+    closed_blocks = vheads * max(groups - 2, 0) * 8
+    return total / max(1, closed_blocks)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
