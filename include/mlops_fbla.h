@@ -160,6 +160,19 @@ mlops_fbla_status mlops_fbla_decode_at(const mlops_fbla_config *cfg, const int *
 mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *cfg, const int *length, const uint16_t *k, const uint16_t *v,
                                        const mlops_fbla_cache *cache, cudaStream_t stream);
 
+/* Decode without a caller-provided scratch, for callers that cannot allocate device memory (an engine whose allocator
+ * is closed after start-up, a plugin host that forbids cudaMalloc, a real-time loop): the scratch is a 32 MiB array
+ * inside the library image, held by every GPU that loads the library until the process exits. Same arguments and
+ * results as mlops_fbla_decode otherwise. Configurations whose scratch (mlops_fbla_decode_scratch_bytes) exceeds
+ * mlops_fbla_decode_static_scratch_limit() are rejected with MLOPS_FBLA_INVALID_VALUE. The first call on a device
+ * looks the array's device address up and should come before any stream capture; all calls on a device share the
+ * array, so calls that overlap on the GPU race (keep them on one stream). Error text: mlops_fbla_decode_static_error().
+ * This entry point has no counterpart in the reference interface. */
+mlops_fbla_status mlops_fbla_decode_static(const mlops_fbla_config *cfg, const uint16_t *q, const mlops_fbla_cache *cache,
+                                           uint16_t *output, cudaStream_t stream);
+size_t mlops_fbla_decode_static_scratch_limit(void);
+const char *mlops_fbla_decode_static_error(void);
+
 /* reference: mlops_fbla.h:185-186 */
 const char *mlops_fbla_status_string(mlops_fbla_status status);
 const char *mlops_fbla_last_error(void); /* thread-local; "" after a successful call */
