@@ -8,7 +8,8 @@ import os
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libmlops_attention.so")
+_LIB_PATH = os.environ.get("MLOPS_FBLA_LIBRARY") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                                                                  "libmlops_attention.so")
 if not os.path.exists(_LIB_PATH):
     raise ImportError(f"{_LIB_PATH} is missing: build it with `make -C mlops_b200/csrc` (or __graft_entry__.build()); "
                       "this package has no fallback path")

@@ -63,7 +63,7 @@ bool decode_layout(const mlops_fbla_config *c, long long tokens, const fbla_k_de
   L.nblocks = (int)(groups * SBG);
   L.nslices = (int)((L.nblocks + FBLA_K_SLICE - 1) / FBLA_K_SLICE);
   if (L.nslices < 1) L.nslices = 1;
-  const size_t tw = (size_t)shape.coarse_ctas * shape.coarse_warps, xw = (size_t)shape.coarse_ctas;
+  const size_t tw = (size_t)shape.coarse_ctas * shape.coarse_warps, xw = (size_t)shape.coarse_ctas * FBLA_K_WINDOW_WARPS;
   const size_t rw = (size_t)shape.refine_ctas * shape.refine_warps;
   const size_t row = (size_t)qg * FBLA_K_PSTRIDE * sizeof(float);
   L.lse = 0;

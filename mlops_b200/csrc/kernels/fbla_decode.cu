@@ -20,12 +20,24 @@ namespace fbla {
 constexpr int PSTRIDE = FBLA_K_PSTRIDE;  // floats of one partial row: o[128], m, l, 2 pad (coarse); o[128], dl, 3 pad (refine)
 constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 
+// Streaming warps per CTA and ring slots per warp, per coarse bit width. A slot holds one record pair (32 tokens);
+// the group's metadata has two slots of its own. NP <= 4 (one group of lookahead) keeps two metadata slots enough.
+#ifndef FBLA_CW4
+#define FBLA_CW4 10
+#endif
+#ifndef FBLA_CW3
+#define FBLA_CW3 10
+#endif
+#ifndef FBLA_NP
+#define FBLA_NP 4
+#endif
 template <int CB> struct CoarseShape {
-  static constexpr int WARPS = CB == 4 ? 6 : 8;  // streaming warps (the ring of each: 2 groups)
-  static constexpr int NST = 2;
+  static constexpr int WARPS = CB == 4 ? FBLA_CW4 : FBLA_CW3;
+  static constexpr int NP = FBLA_NP;
+  static constexpr int PAIR_BYTES = 2 * record_bytes(CB);
   static constexpr int GROUP_BYTES = SBG * record_bytes(CB);
-  static constexpr int STAGE = GROUP_BYTES + 1024;  // + the group's metadata
 };
+static_assert(FBLA_NP >= 2 && FBLA_NP <= 4, "ring slots per warp");
 
 // ---- where a batch row's tokens put its units -----------------------------------------------------------------------
 struct Row { int tokens, groups, closed, exact; };
@@ -47,8 +59,10 @@ struct Cursor {
 template <bool EXACT>
 __device__ __forceinline__ int units_of(const Row &r) { return EXACT ? r.exact : r.closed; }
 
+// (one length for every batch row: closed forms, no loop over the batch)
 template <bool EXACT>
 __device__ __forceinline__ long long total_units(const fbla_k_decode &a, int hpr) {
+  if (!a.lstride) return (long long)a.batch * hpr * units_of<EXACT>(row_of(a, 0));
   long long t = 0;
   for (int b = 0; b < a.batch; ++b) t += (long long)hpr * units_of<EXACT>(row_of(a, b));
   return t;
@@ -57,6 +71,11 @@ __device__ __forceinline__ long long total_units(const fbla_k_decode &a, int hpr
 template <bool EXACT>
 __device__ __forceinline__ Cursor locate(const fbla_k_decode &a, int hpr, long long u) {
   Cursor c{0, 0, 0, 0};
+  if (!a.lstride) {
+    const int n = units_of<EXACT>(row_of(a, 0)), h = (int)(u / n);
+    c.b = h / hpr; c.hir = h - c.b * hpr; c.i = (int)(u - (long long)h * n); c.n = n;
+    return c;
+  }
   for (int b = 0; b < a.batch; ++b) {
     const int n = units_of<EXACT>(row_of(a, b));
     const long long span = (long long)hpr * n;
@@ -80,6 +99,7 @@ __device__ __forceinline__ void advance(const fbla_k_decode &a, int hpr, Cursor 
 // first flattened unit of virtual head vh, and the head's unit count
 template <bool EXACT>
 __device__ __forceinline__ long long head_offset(const fbla_k_decode &a, int hpr, int vh, int &n) {
+  if (!a.lstride) { n = units_of<EXACT>(row_of(a, 0)); return (long long)vh * n; }
   const int bq = vh / hpr, hir = vh - bq * hpr;
   long long off = 0;
   for (int b = 0; b < bq; ++b) off += (long long)hpr * units_of<EXACT>(row_of(a, b));
@@ -104,7 +124,7 @@ __device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, ui
   float z[4], amax = 0.f, dot = 0.f;
 #pragma unroll
   for (int x = 0; x < 4; ++x) { z[x] = __fmul_rn(qf[x], ks[x]); amax = fmaxf(amax, fabsf(z[x])); dot = fmaf(qf[x], kb[x], dot); }
-  amax = warp_max(amax);
+  amax = __uint_as_float(__reduce_max_sync(FULL, __float_as_uint(amax)));  // amax >= 0: the bit patterns order as the values
   // r = fl(127 / amax), correctly rounded: reciprocal seed, one Newton step, quotient and its residual correction
   float rc;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
@@ -112,34 +132,37 @@ __device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, ui
   const float q0 = __fmul_rn(127.f, rc);
   const float r = amax > 0.f ? fmaf(fmaf(-amax, q0, 127.f), rc, q0) : 0.f;
   uint32_t word = 0;
-  float s = 0.f;
 #pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    const float t = fmaf(z[x], r, MAGICF);  // rint(z r) in the low mantissa bits: one rounding of the exact product
-    word |= (__float_as_uint(t) & 255u) << (8 * x);
-    s += t - MAGICF;
-  }
+  for (int x = 0; x < 4; ++x)  // rint(z r) in the low mantissa bits: one rounding of the exact product
+    word |= (__float_as_uint(fmaf(z[x], r, MAGICF)) & 255u) << (8 * x);
   qst_row[lane] = word;
   sq = __fmul_rn(amax, __fmul_rn(sl, 1.f / 127.f));
   qb = __fmul_rn(warp_sum(dot), sl);
-  qsum = warp_sum(s);
+  qsum = (float)__reduce_add_sync(FULL, __dp4a((int)word, 0x01010101, 0));  // the exact integer sum of the codes
 }
 
 // ---- shared memory of the coarse kernel ---------------------------------------------------------------------------------
 template <int CB> struct __align__(128) StreamWarp {
-  uint8_t stage[CoarseShape<CB>::NST][CoarseShape<CB>::STAGE];
+  uint8_t pair[CoarseShape<CB>::NP][CoarseShape<CB>::PAIR_BYTES];  // ring of record pairs
+  uint8_t meta[2][1024];                                           // metadata of the group in progress and of the next
   uint8_t qst[8 * QST_ROW];  // qhat rows (rows >= QG stay zero)
   uint8_t pst[128];          // P bytes of a record pair: [block parity][query 0..3][16 tokens]
-  uint64_t bar[CoarseShape<CB>::NST];
+  uint64_t bar_pair[CoarseShape<CB>::NP], bar_meta[2];
 };
 struct __align__(16) ExactWarp {
   float q[4][D];
   uint8_t pst[4][16];
 };
+constexpr int XWARPS = FBLA_K_WINDOW_WARPS;
 template <int CB> struct CoarseSmem {
   StreamWarp<CB> w[CoarseShape<CB>::WARPS];
-  ExactWarp x;
+  ExactWarp x[XWARPS];
 };
+
+// Programmatic dependent launch: the next pass of a decode is launched while this one still runs (hiding its launch
+// latency) and waits here until the previous pass has completed and its writes are visible.
+__device__ __forceinline__ void wait_previous_pass() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_next_pass() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
   if (a.status) { atomicCAS(a.status, 0, pass); a.status[1] = blockIdx.x; }
@@ -261,14 +284,55 @@ struct Run {
 };
 template <int QG> __device__ __forceinline__ bool query_valid(int tig, int e) { return 2 * (tig & 1) + e < QG; }
 
+// The warp's stream of record pairs: chunk p = 4 k + i is pair i of the k-th group of the warp's range, in ring slot
+// p % NP (its (p / NP)-th use); the group's metadata travels with pair 0 into metadata slot k & 1. All lanes carry the
+// (warp-uniform) state; lane 0 issues the copies.
+template <int CB> struct Ring {
+  using Sh = CoarseShape<CB>;
+  StreamWarp<CB> &w;
+  const fbla_k_decode &a;
+  int hpr, lane;
+  Cursor fc;                           // the group of the next chunk to issue
+  int issued, chunks;                  // chunks issued / in the warp's range
+  const uint8_t *src_pair, *src_meta;  // that group's records and metadata
+  __device__ __forceinline__ void point() {
+    const int bh = (fc.b * hpr + fc.hir) / a.vg;
+    const size_t unit = (size_t)bh * a.hs + (size_t)(1 + fc.i) * a.gs;
+    src_pair = a.c.coarse + unit * Sh::GROUP_BYTES;
+    src_meta = reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024;
+  }
+  __device__ __forceinline__ void issue_next() {
+    if (issued >= chunks) return;
+    const int i = issued & 3, slot = issued % Sh::NP, ms = (issued >> 2) & 1;
+    if (lane == 0) {
+      fence_async_smem();  // the slot's earlier reads (ordered before this point by __syncwarp) precede the copy's writes
+      if (i == 0) {
+        mbar_expect_tx(&w.bar_meta[ms], 1024);
+        bulk_g2s(w.meta[ms], src_meta, 1024, &w.bar_meta[ms]);
+      }
+      mbar_expect_tx(&w.bar_pair[slot], Sh::PAIR_BYTES);
+      bulk_g2s(w.pair[slot], src_pair + i * Sh::PAIR_BYTES, Sh::PAIR_BYTES, &w.bar_pair[slot]);
+    }
+    ++issued;
+    if (i == 3 && issued < chunks) { advance<false>(a, hpr, fc); point(); }
+  }
+  // false: a bounded wait gave up
+  __device__ __forceinline__ bool wait_meta(int k) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_meta[k & 1], (uint32_t)((k >> 1) & 1))); }
+  __device__ __forceinline__ bool wait_pair(int p) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_pair[p % Sh::NP], (uint32_t)((p / Sh::NP) & 1))); }
+};
+
+// Group k of the warp's range. Returns false if a bounded wait gave up.
 template <int CB, int FB, int QG>
-__device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &sm, const float4 (&q4)[QG], float sl, int lane, Run &run,
+__device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4 (&q4)[QG], float sl, int lane, Run &run,
                                              float *lse_group /* [8 sub-blocks][QG] of this (virtual head, group) */) {
   constexpr int RB = record_bytes(CB);
   constexpr float HOFF = .5f * ((1 << FB) - 1);
+  StreamWarp<CB> &sm = ring.w;
   const int gid = lane >> 2, tig = lane & 3;
-  const uint8_t *meta = st + CoarseShape<CB>::GROUP_BYTES;
-  // qhat of every query; c0 / sqc of the thread's two columns
+  const bool odd = tig >> 1;  // threads tig >= 2 accumulate the odd sub-block of every pair (columns 4..7 of the value products)
+  if (!ring.wait_meta(k)) return false;
+  const uint8_t *meta = sm.meta[k & 1];
+  // qhat of every query; c0 / sqc of the thread's two score columns
   float c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f};
   {
     const uint4 km = lds128(meta + 16 * lane);
@@ -284,67 +348,84 @@ __device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &
   __syncwarp();
   uint32_t B[8];
   qhat_frag<CB>(sm.qst, gid, tig, B);
-  // scores of the 8 sub-blocks: s[j][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1);
-  // only columns < QG (threads tig < 2) are queries, the rest multiply zero rows of qst
-  float s[SBG][4], mb[SBG][2], mg[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-  for (int j = 0; j < SBG; ++j) {
-    float x[4];
-    qk_tile<CB>(st + j * RB, gid, tig, B, x);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) s[j][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      float v = fmaxf(s[j][e], s[j][2 + e]);
-      v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
-      v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
-      v = fmaxf(v, __shfl_xor_sync(FULL, v, 16));
-      mb[j][e] = v;
-      mg[e] = fmaxf(mg[e], v);
-    }
-  }
-  // Threads tig >= 2 accumulate the odd sub-blocks (columns 4..7 of the value products) of queries 2 (tig & 1) + e:
-  // their maxima live in thread tig - 2.
-  const bool odd = tig >> 1;
-#pragma unroll
-  for (int e = 0; e < 2; ++e) { const float o2 = __shfl_xor_sync(FULL, mg[e], 2); if (odd) mg[e] = o2; }
+  // the group's sums in code units, relative to the running maximum run.m: A = sum w y, Bs = sum w sum p
   float A[4][4][2], Bs[2] = {0.f, 0.f};
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) A[u][cc][0] = A[u][cc][1] = 0.f;
+#pragma unroll 1
+  for (int J = 0; J < SBG / 2; ++J) {  // sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1)
+    const int p = 4 * k + J;
+    if (!ring.wait_pair(p)) return false;
+    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP], *rb = ra + RB;
+    // scores s[par][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1);
+    // only columns < QG (threads tig < 2) are queries, the others multiply zero rows of qst
+    float s[2][4], mb[2][2];
+    {
+      float x[4];
+      qk_tile<CB>(ra, gid, tig, B, x);
 #pragma unroll
-  for (int J = 0; J < SBG / 2; ++J) {
-    // P bytes of sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1): pst[parity][query][token]
-    if (tig < 2) {
+      for (int i = 0; i < 4; ++i) s[0][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
+      qk_tile<CB>(rb, gid, tig, B, x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[1][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
+    }
+#pragma unroll
+    for (int par = 0; par < 2; ++par)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float v = fmaxf(s[par][e], s[par][2 + e]);
+        v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
+        v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
+        v = fmaxf(v, __shfl_xor_sync(FULL, v, 16));
+        mb[par][e] = v;
+      }
+    // the thread's own sub-block 2 J + (tig >> 1) of queries 2 (tig & 1) + e, and the pair's maximum (the same value in
+    // both parities' threads, so their running maxima stay equal)
+    float mbj[2], mp[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float other = __shfl_xor_sync(FULL, mb[1][e], 2);
+      mbj[e] = odd ? other : mb[0][e];
+      const float pm = fmaxf(mb[0][e], mb[1][e]), pmo = __shfl_xor_sync(FULL, pm, 2);
+      mp[e] = odd ? pmo : pm;
+    }
+    // the running maximum moves only when a pair exceeds it by more than 2^8 (weights stay <= 2^8; the rescale is rare)
+    const bool grow = mp[0] > run.m[0] + 8.f || mp[1] > run.m[1] + 8.f;
+    if (__any_sync(FULL, grow)) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float mn = mp[e] > run.m[e] + 8.f ? mp[e] : run.m[e], al = ex2(run.m[e] - mn);  // (2^-inf = 0 on the first group)
+        run.m[e] = mn;
+        run.l[e] *= al; Bs[e] *= al;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) { run.o[u][cc][e] *= al; A[u][cc][e] *= al; }
+      }
+    }
+    if (tig < 2) {  // P bytes: pst[parity][query][token]
 #pragma unroll
       for (int par = 0; par < 2; ++par)
 #pragma unroll
         for (int e = 0; e < 2; ++e)
           if (query_valid<QG>(tig, e)) {
-            const int j = 2 * J + par, qe = 2 * tig + e;
-            const uint32_t p0 = __float_as_uint(fmaf(ex2(s[j][e] - mb[j][e]), 255.f, MAGICF));
-            const uint32_t p8 = __float_as_uint(fmaf(ex2(s[j][2 + e] - mb[j][e]), 255.f, MAGICF));
-            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)p0;
-            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)p8;
+            const int qe = 2 * tig + e;
+            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)__float_as_uint(fmaf(ex2(s[par][e] - mb[par][e]), 255.f, MAGICF));
+            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)__float_as_uint(fmaf(ex2(s[par][2 + e] - mb[par][e]), 255.f, MAGICF));
           }
     }
     __syncwarp();
     // column gid of the value products: gid < 4: parity 0, query gid, k block = tokens 4 tig ..; gid >= 4: parity 1
     const uint32_t pw = lds32(sm.pst + 4 * lane);
     const uint32_t b0 = gid < 4 ? pw : 0u, b1 = gid < 4 ? 0u : pw;
-    const uint8_t *ra = st + (2 * J) * RB, *rb = ra + RB;
-    // the thread's sub-block 2 J + (tig >> 1), queries 2 (tig & 1) + e: its maximum and weight
-    float mbj[2], wj[2];
+    float wj[2];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const float other = __shfl_xor_sync(FULL, mb[2 * J + 1][e], 2);
-      mbj[e] = odd ? other : mb[2 * J][e];
-      wj[e] = ex2(mbj[e] - mg[e]);
-    }
+    for (int e = 0; e < 2; ++e) wj[e] = ex2(mbj[e] - run.m[e]);
     {  // sum p of both sub-blocks, every column: a product with an all-ones A
-      uint32_t d[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-      mma_u8u8_k32(d, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1);
+      uint32_t d[4];
+      mma_u8u8_k32_from(d, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1, MAGIC);
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const float sp = isum(d[e]);
@@ -357,9 +438,9 @@ __device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &
       uint32_t va[4], vb[4];
       v_slots<CB>(ra, 8 * u + gid, tig, va);
       v_slots<CB>(rb, 8 * u + gid, tig, vb);
-      uint32_t d01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, d23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-      mma_u8u8_k32(d01, va[0], va[1], vb[0], vb[1], b0, b1);  // rows gid: channel cc 0, gid + 8: cc 1
-      mma_u8u8_k32(d23, va[2], va[3], vb[2], vb[3], b0, b1);  // cc 2, cc 3
+      uint32_t d01[4], d23[4];
+      mma_u8u8_k32_from(d01, va[0], va[1], vb[0], vb[1], b0, b1, MAGIC);  // rows gid: channel cc 0, gid + 8: cc 1
+      mma_u8u8_k32_from(d23, va[2], va[3], vb[2], vb[3], b0, b1, MAGIC);  // cc 2, cc 3
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         A[u][0][e] = fmaf(wj[e], isum(d01[e]), A[u][0][e]);
@@ -368,17 +449,12 @@ __device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &
         A[u][3][e] = fmaf(wj[e], isum(d23[2 + e]), A[u][3][e]);
       }
     }
-    __syncwarp();  // pst is rewritten by the next pair
+    __syncwarp();       // the pair's slot and pst are free
+    ring.issue_next();  // refill the slot with the chunk NP ahead
   }
-  // fold the group into the running softmax: o += 2^(mg - m) (vs' A + vb' B), coarse cell midpoints folded into vb'
-  float al[2], be[2];
+  // fold the group into the running softmax: o += vs' A + vb' B, coarse cell midpoints folded into vb'
 #pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const float mn = fmaxf(run.m[e], mg[e]);
-    al[e] = ex2(run.m[e] - mn); be[e] = ex2(mg[e] - mn);
-    run.m[e] = mn;
-    run.l[e] = fmaf(al[e], run.l[e], be[e] * Bs[e]);
-  }
+  for (int e = 0; e < 2; ++e) run.l[e] += Bs[e];
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
@@ -387,12 +463,11 @@ __device__ __forceinline__ void coarse_group(const uint8_t *st, StreamWarp<CB> &
     for (int cc = 0; cc < 4; ++cc) {
       const float vbp = fmaf(vs[cc], HOFF, vb[cc]), vsp = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc));
 #pragma unroll
-      for (int e = 0; e < 2; ++e)
-        run.o[u][cc][e] = fmaf(al[e], run.o[u][cc][e], be[e] * fmaf(vsp, A[u][cc][e], vbp * Bs[e]));
+      for (int e = 0; e < 2; ++e) run.o[u][cc][e] += fmaf(vsp, A[u][cc][e], vbp * Bs[e]);
     }
   }
+  return true;
 }
-
 
 // ---- the coarse kernel -------------------------------------------------------------------------------------------------
 template <int QG> __device__ __forceinline__ void reset(Run &r) {
@@ -426,15 +501,27 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
   }
 }
 
+#ifdef FBLA_TIMING  // tuning builds only: cycles every warp of the coarse kernel spent, read back by fbla_k_debug_read
+__device__ long long fbla_dbg[148 * 16];
+#define FBLA_T0 const long long t0_ = clock64();
+#define FBLA_T1 if ((threadIdx.x & 31) == 0) fbla_dbg[blockIdx.x * 16 + (threadIdx.x >> 5)] = clock64() - t0_;
+#else
+#define FBLA_T0
+#define FBLA_T1
+#endif
+
 template <int CB, int FB, int QG>
-__global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + 1), 1) coarse_kernel(const fbla_k_decode a) {
+__global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coarse_kernel(const fbla_k_decode a) {
   using Sh = CoarseShape<CB>;
+  FBLA_T0
+  allow_next_pass();
   extern __shared__ __align__(128) uint8_t smem_raw[];
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (blockIdx.x == 0 && threadIdx.x == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
-  if (warp == Sh::WARPS) {
-    exact_warp<QG>(a, sm.x, lane, blockIdx.x, gridDim.x);
+  if (warp >= Sh::WARPS) {
+    exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, blockIdx.x * XWARPS + (warp - Sh::WARPS), gridDim.x * XWARPS);
+    FBLA_T1
     return;
   }
   StreamWarp<CB> &w = sm.w[warp];
@@ -442,7 +529,9 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + 1), 1) coarse_k
   reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
   if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < Sh::NST; ++s) mbar_init(&w.bar[s], 1);
+    for (int s = 0; s < Sh::NP; ++s) mbar_init(&w.bar_pair[s], 1);
+    mbar_init(&w.bar_meta[0], 1);
+    mbar_init(&w.bar_meta[1], 1);
     mbar_init_fence();
   }
   __syncwarp();
@@ -451,25 +540,16 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + 1), 1) coarse_k
   const long long total = total_units<false>(a, hpr), tw = (long long)gridDim.x * Sh::WARPS, per = ceil_div(total, tw);
   const long long gw = (long long)blockIdx.x * Sh::WARPS + warp, lo = gw * per, hi = min(total, lo + per);
   if (lo >= hi) return;
-  Cursor fc = locate<false>(a, hpr, lo), cc = fc;
-  auto issue = [&](const Cursor &c, int s) {  // lane 0: group 1 + c.i of the cursor's KV head into stage s
-    const int bh = (c.b * hpr + c.hir) / a.vg;
-    const size_t unit = (size_t)bh * a.hs + (size_t)(1 + c.i) * a.gs;
-    mbar_expect_tx(&w.bar[s], Sh::STAGE);
-    bulk_g2s(w.stage[s], a.c.coarse + unit * Sh::GROUP_BYTES, Sh::GROUP_BYTES, &w.bar[s]);
-    bulk_g2s(w.stage[s] + Sh::GROUP_BYTES, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
-  };
+  Cursor cc = locate<false>(a, hpr, lo);
+  Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(4 * (hi - lo)), nullptr, nullptr};
+  ring.point();
 #pragma unroll
-  for (int s = 0; s < Sh::NST; ++s)
-    if (lo + s < hi) {
-      if (lane == 0) issue(fc, s);
-      advance<false>(a, hpr, fc);
-    }
+  for (int s = 0; s < Sh::NP; ++s) ring.issue_next();
   Run run;
   float4 q4[QG];
   int cur_vh = -1;
   for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
-    const int k = (int)(u - lo), s = k % Sh::NST, vh = cc.b * hpr + cc.hir;
+    const int vh = cc.b * hpr + cc.hir;
     if (vh != cur_vh) {
       if (cur_vh >= 0) write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
       cur_vh = vh;
@@ -480,19 +560,13 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + 1), 1) coarse_k
         q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
       }
     }
-    const bool ok = mbar_wait_bounded(&w.bar[s], (k / Sh::NST) & 1);
-    if (!__all_sync(FULL, ok)) {
+    if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)(1 + cc.i) * SBG) * QG)) {
       if (lane == 0) report(a, 1);
       return;
     }
-    coarse_group<CB, FB, QG>(w.stage[s], w, q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)(1 + cc.i) * SBG) * QG);
-    __syncwarp();
-    if (u + Sh::NST < hi) {
-      if (lane == 0) { fence_async_smem(); issue(fc, s); }
-      advance<false>(a, hpr, fc);
-    }
   }
   write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
+  FBLA_T1
 }
 
 // ---- which partial slots belong to a virtual head ------------------------------------------------------------------------
@@ -505,7 +579,7 @@ __device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
   long long off = head_offset<false>(a, hpr, vh, n);
   if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), tw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
   off = head_offset<true>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), a.coarse_ctas); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
+  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * XWARPS); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
   return s;
 }
 __device__ __forceinline__ const float *coarse_slot(const fbla_k_decode &a, int w, int vh, int qi) {
@@ -523,38 +597,52 @@ __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
   __shared__ int wc[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, vh = blockIdx.y, slice = blockIdx.x;
   const int hpr = a.kv_heads * a.vg;
-  if (warp < QG) {
-    const Slots s = slots_of(a, vh);
+  allow_next_pass();
+  const Row row = row_of(a, vh / hpr);
+  const Slots s = slots_of(a, vh);
+  wait_previous_pass();
+  // the slice's sub-block masses first (they do not depend on R): every load of the warp in flight together
+  const int lo = SBG + slice * SLICE + warp * (SLICE / 8), hi = SBG * (row.groups - 1);
+  float x[4][QG];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int sb = lo + 32 * i + lane;
+    const float *p = a.lse + ((size_t)vh * a.nblocks + min(sb, max(hi - 1, 0))) * QG;
+#pragma unroll
+    for (int qi = 0; qi < QG; ++qi) x[i][qi] = sb < hi ? __ldcg(p + qi) : -INFINITY;
+  }
+  if (warp < QG) {  // R of query `warp`: one pass over the head's partial (m, l), merged online, then across lanes
     const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
-    float mx = -INFINITY;
+    float mx = -INFINITY, ls = 0.f;
     for (int i = lane; i < n; i += 32) {
       const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
-      mx = fmaxf(mx, __ldcg(p + D));
+      const float m = __ldcg(p + D), l = __ldcg(p + D + 1);
+      if (m != -INFINITY) {
+        const float mn = fmaxf(mx, m);
+        ls = fmaf(ls, ex2(mx - mn), l * ex2(m - mn));
+        mx = mn;
+      }
     }
-    mx = warp_max(mx);
-    float ls = 0.f;
-    for (int i = lane; i < n; i += 32) {
-      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
-      const float m = __ldcg(p + D);
-      if (m != -INFINITY) ls = fmaf(__ldcg(p + D + 1), ex2(m - mx), ls);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+      const float m2 = __shfl_xor_sync(FULL, mx, o), l2 = __shfl_xor_sync(FULL, ls, o);
+      const float mn = fmaxf(mx, m2);
+      // (lanes pair up symmetrically: both compute the same sum in the same order of magnitudes)
+      const float a1 = mx == -INFINITY ? 0.f : ls * ex2(mx - mn), a2 = m2 == -INFINITY ? 0.f : l2 * ex2(m2 - mn);
+      ls = (lane & o) ? a2 + a1 : a1 + a2;
+      mx = mn;
     }
-    const float r = mx + lg2(warp_sum(ls));
+    const float r = mx + lg2(ls);
     if (!lane) { R[warp] = r; if (!slice) a.row_r[vh * QG + warp] = r; }
   }
   __syncthreads();
-  const Row row = row_of(a, vh / hpr);
-  const int lo = SBG + slice * SLICE + warp * (SLICE / 8), hi = SBG * (row.groups - 1);
   int qm[4], n = 0;
   uint32_t bal[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int sb = lo + 32 * i + lane;
     qm[i] = 0;
-    if (sb < hi) {
-      const float *p = a.lse + ((size_t)vh * a.nblocks + sb) * QG;
 #pragma unroll
-      for (int qi = 0; qi < QG; ++qi) qm[i] |= (__ldcg(p + qi) - R[qi] > a.log2_tau) << qi;
-    }
+    for (int qi = 0; qi < QG; ++qi) qm[i] |= (x[i][qi] - R[qi] > a.log2_tau) << qi;
     bal[i] = __ballot_sync(FULL, qm[i] != 0);
     n += __popc(bal[i]);
   }
@@ -574,7 +662,7 @@ __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
 
 // ---- refine: full - coarse of every selected sub-block ----------------------------------------------------------------------
 template <int CB, int FB> struct RefineShape {
-  static constexpr int WARPS = 8, NST = 2;
+  static constexpr int WARPS = 12, NST = 2;
   static constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
   static constexpr int STAGE = RC + RF + 1024;
 };
@@ -595,6 +683,8 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
   __shared__ int chunk_sum[256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
   const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, entries = vheads * a.nslices;
+  allow_next_pass();
+  wait_previous_pass();
   // exclusive prefix of the slices' counts: pre[e], e = vh * nslices + slice
   {
     const int per = (entries + 255) / 256, e0 = threadIdx.x * per, e1 = min(entries, e0 + per);
@@ -663,6 +753,12 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
       if (lane == 0) issue(fit[s], fe, s);
     }
   Run run;  // m unused: corrections are already in units of 2^-R
+  float Ag[4][4][2], Bg[2] = {0.f, 0.f};  // the current group's sums in code units
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) Ag[u][cc][0] = Ag[u][cc][1] = 0.f;
+  int pe = fe;  // entry cursor for peeking at the next item
   float4 q4[QG];
   float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
   uint32_t B[8];
@@ -752,38 +848,58 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
     {
       float sp[2];  // sum p of the thread's two columns: a product with an all-ones A
       {
-        uint32_t d[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-        mma_u8u8_k16(d, 0x01010101u, 0x01010101u, b0);
+        uint32_t d[4];
+        mma_u8u8_k16_from(d, 0x01010101u, 0x01010101u, b0, MAGIC);
         sp[0] = isum(d[0]); sp[1] = isum(d[1]);
       }
 #pragma unroll
-      for (int e = 0; e < 2; ++e) run.l[e] = fmaf(wgt[e], sp[e], run.l[e]);
+      for (int e = 0; e < 2; ++e) Bg[e] = fmaf(wgt[e], sp[e], Bg[e]);
+      // the group's weighted code sums: full-score threads add w (2^FB h + f), coarse-score threads -w 2^FB h
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         uint32_t vh4[4], vl4[4];
         v_slots<CB>(crec, 8 * u + gid, tig, vh4);
         v_slots<FB>(frec, 8 * u + gid, tig, vl4);
-        uint32_t h01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, h23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-        uint32_t l01[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, l23[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-        mma_u8u8_k16(h01, vh4[0], vh4[1], b0);
-        mma_u8u8_k16(h23, vh4[2], vh4[3], b0);
-        mma_u8u8_k16(l01, vl4[0], vl4[1], b0);
-        mma_u8u8_k16(l23, vl4[2], vl4[3], b0);
-        const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
-        const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+        uint32_t h01[4], h23[4], l01[4], l23[4];
+        mma_u8u8_k16_from(h01, vh4[0], vh4[1], b0, MAGIC);
+        mma_u8u8_k16_from(h23, vh4[2], vh4[3], b0, MAGIC);
+        mma_u8u8_k16_from(l01, vl4[0], vl4[1], b0, MAGIC);
+        mma_u8u8_k16_from(l23, vl4[2], vl4[3], b0, MAGIC);
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
-          const float vhi = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc)), vlo = __fmul_rn(vs[cc], v_unscale<FB>(cc));
-          const float vbc = fmaf(vs[cc], HOFF, vb[cc]);
+          const float ch_ = (float)(1 << FB) * v_unscale<CB>(cc), cl_ = cset ? 0.f : v_unscale<FB>(cc);
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const float yh = isum(cc < 2 ? h01[2 * (cc & 1) + e] : h23[2 * (cc & 1) + e]);
             const float yl = isum(cc < 2 ? l01[2 * (cc & 1) + e] : l23[2 * (cc & 1) + e]);
-            const float full = fmaf(vb[cc], sp[e], fmaf(vhi, yh, vlo * yl));
-            const float coarse = fmaf(vbc, sp[e], vhi * yh);
-            run.o[u][cc][e] = fmaf(wgt[e], cset ? coarse : full, run.o[u][cc][e]);
+            Ag[u][cc][e] = fmaf(wgt[e], fmaf(ch_, yh, cl_ * yl), Ag[u][cc][e]);
           }
         }
+      }
+      // the group's last item of this warp: apply the V affine once (coarse cells at their midpoint)
+      bool last = k + 1 >= hi;
+      if (!last) {
+        const int nx = item_at(k + 1, pe);
+        last = pe / a.nslices != vh || (nx >> 4) / SBG != sb / SBG;
+      }
+      if (last) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) { run.l[e] += Bg[e]; }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
+          const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            const float vbx = cset ? fmaf(vs[cc], HOFF, vb[cc]) : vb[cc];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              run.o[u][cc][e] += fmaf(vs[cc], Ag[u][cc][e], vbx * Bg[e]);
+              Ag[u][cc][e] = 0.f;
+            }
+          }
+        }
+        Bg[0] = Bg[1] = 0.f;
       }
     }
     __syncwarp();
@@ -796,32 +912,76 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
 }
 
 // ---- merge: out = (sum 2^(m_c - R) o_c + sum do) / (sum 2^(m_c - R) l_c + sum dl), BF16 ---------------------------------
+// One CTA per output row (virtual head, query): thread (ch, sl) sums the partial rows sl, sl + 4, ... of its channel,
+// the four lanes of a channel are then added in a fixed order.
 template <int QG>
-__global__ void __launch_bounds__(128) merge_kernel(const fbla_k_decode a) {
-  const int vh = blockIdx.x / QG, qi = blockIdx.x % QG, ch = threadIdx.x;
+__global__ void __launch_bounds__(512) merge_kernel(const fbla_k_decode a) {
+  __shared__ float so[4][D], sl_[4];
+  __shared__ Slots ss;
+  __shared__ int rr[3];
+  const int vh = blockIdx.x / QG, qi = blockIdx.x % QG, ch = threadIdx.x & 127, sl = threadIdx.x >> 7;
   const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, b = vh / hpr, hir = vh - b * hpr;
-  const Slots s = slots_of(a, vh);
-  const float Rq = __ldcg(a.row_r + vh * QG + qi);
-  float O = 0.f, L = 0.f;
-  for (int w = s.c0; w <= s.c1; ++w) {
-    const float *p = coarse_slot(a, w, vh, qi);
-    const float m = __ldcg(p + D), e = m == -INFINITY ? 0.f : ex2(m - Rq);
-    L = fmaf(e, __ldcg(p + D + 1), L); O = fmaf(e, __ldcg(p + ch), O);
-  }
-  for (int x = s.x0; x <= s.x1; ++x) {
-    const float *p = window_slot(a, x, vh, qi);
-    const float m = __ldcg(p + D), e = m == -INFINITY ? 0.f : ex2(m - Rq);
-    L = fmaf(e, __ldcg(p + D + 1), L); O = fmaf(e, __ldcg(p + ch), O);
-  }
-  const int i0 = __ldcg(a.item_off + vh), i1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
-  if (i1 > i0) {
-    const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
-    for (int w = i0 / per; w <= (i1 - 1) / per; ++w) {
-      const float *p = a.dpart + ((size_t)(w + vh) * QG + qi) * PSTRIDE;
-      L += __ldcg(p + D); O += __ldcg(p + ch);
+  if (threadIdx.x == 0) ss = slots_of(a, vh);
+  wait_previous_pass();
+  if (threadIdx.x == 0) {
+    const int it0 = __ldcg(a.item_off + vh), it1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
+    rr[0] = 0; rr[1] = -1;
+    if (it1 > it0) {
+      const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
+      rr[0] = it0 / per; rr[1] = (it1 - 1) / per;
     }
   }
-  a.out[(size_t)q_row(a, b, hir, qi) * D + ch] = f32_to_bf16(__fdividef(O, L));
+  __syncthreads();
+  const Slots s = ss;
+  const float Rq = __ldcg(a.row_r + vh * QG + qi);
+  float O = 0.f, L = 0.f;
+  const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
+  for (int i0 = sl; i0 < n; i0 += 16) {
+    float m[4], l[4], o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = min(i0 + 4 * j, n - 1);
+      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, qi) : window_slot(a, s.x0 + i - nc, vh, qi);
+      m[j] = __ldcg(p + D); l[j] = __ldcg(p + D + 1); o[j] = __ldcg(p + ch);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i0 + 4 * j < n) {
+        const float e = m[j] == -INFINITY ? 0.f : ex2(m[j] - Rq);
+        L = fmaf(e, l[j], L); O = fmaf(e, o[j], O);
+      }
+  }
+  const int w0 = rr[0], w1 = rr[1];
+  for (int i0 = w0 + sl; i0 <= w1; i0 += 16) {
+    float l[4], o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float *p = a.dpart + ((size_t)(min(i0 + 4 * j, w1) + vh) * QG + qi) * PSTRIDE;
+      l[j] = __ldcg(p + D); o[j] = __ldcg(p + ch);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i0 + 4 * j <= w1) { L += l[j]; O += o[j]; }
+  }
+  so[sl][ch] = O;
+  if (ch == 0) sl_[sl] = L;
+  __syncthreads();
+  if (sl == 0) {
+    const float Os = (so[0][ch] + so[1][ch]) + (so[2][ch] + so[3][ch]), Ls = (sl_[0] + sl_[1]) + (sl_[2] + sl_[3]);
+    a.out[(size_t)q_row(a, b, hir, qi) * D + ch] = f32_to_bf16(__fdividef(Os, Ls));
+  }
+}
+
+// a launch that may begin while the previous kernel of the stream still runs (the kernel calls wait_previous_pass)
+template <class... P, class... A>
+cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 constexpr int REFINE_SMEM_MAX = 220 * 1024;  // dynamic shared memory of the refine pass (its ring + the slice prefix)
@@ -840,14 +1000,19 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
     if (dev >= 0 && dev < 64) configured[dev] = 1;
   }
   if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
-  coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + 1), csm, stream>>>(a);
-  select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a);
-  refine_kernel<CB, FB, QG><<<a.refine_ctas, 32 * RefineShape<CB, FB>::WARPS, rsm, stream>>>(a);
-  merge_kernel<QG><<<vheads * QG, 128, 0, stream>>>(a);
-  return cudaGetLastError();
+  coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, stream>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = launch_dependent(select_kernel<QG>, dim3(a.nslices, vheads), dim3(256), 0, stream, a);
+  if (e == cudaSuccess) e = launch_dependent(refine_kernel<CB, FB, QG>, dim3(a.refine_ctas), dim3(32 * RefineShape<CB, FB>::WARPS), rsm, stream, a);
+  if (e == cudaSuccess) e = launch_dependent(merge_kernel<QG>, dim3(vheads * QG), dim3(512), 0, stream, a);
+  return e;
 }
 
 }  // namespace fbla
+
+#ifdef FBLA_TIMING
+extern "C" cudaError_t fbla_k_debug_read(long long *host) { return cudaMemcpyFromSymbol(host, fbla::fbla_dbg, sizeof(fbla::fbla_dbg)); }
+#endif
 
 extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   int dev = 0, sms = 0;
@@ -858,7 +1023,7 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   a->coarse_ctas = sms;
   a->coarse_warps = a->cb == 4 ? fbla::CoarseShape<4>::WARPS : fbla::CoarseShape<3>::WARPS;
   a->refine_ctas = sms;
-  a->refine_warps = 8;
+  a->refine_warps = fbla::RefineShape<4, 2>::WARPS;
   return cudaSuccess;
 }
 

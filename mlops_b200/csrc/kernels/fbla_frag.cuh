@@ -15,8 +15,12 @@
 
 namespace fbla {
 
+__device__ __forceinline__ void mma_u8u8_k16_from(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, uint32_t c) {
+  asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]) : "r"(a0), "r"(a1), "r"(b0), "r"(c));
+}
 __device__ __forceinline__ void mma_u8u8_k16(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+  asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(b0));
 }
 
@@ -47,9 +51,9 @@ template <int BITS> __device__ __forceinline__ void qk_tile(const uint8_t *rec, 
     const uint32_t a = lds32(p0), a8 = lds32(p1), b = lds32(p0 + 512), b8 = lds32(p1 + 512);          // half 0: W[tig], W[4 + tig]
     const uint32_t c = lds32(p0 + 256), c8 = lds32(p1 + 256), d = lds32(p0 + 768), d8 = lds32(p1 + 768);  // half 1
     constexpr uint32_t L = 0x0f0f0f0fu, H = 0xf0f0f0f0u;
-    uint32_t lo[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, hi[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-    mma_u8s8_k32(lo, a & L, a8 & L, b & L, b8 & L, B[0], B[1]);
-    mma_u8s8_k32(hi, a & H, a8 & H, b & H, b8 & H, B[2], B[3]);
+    uint32_t lo[4], hi[4];
+    mma_u8s8_k32_from(lo, a & L, a8 & L, b & L, b8 & L, B[0], B[1], MAGIC);
+    mma_u8s8_k32_from(hi, a & H, a8 & H, b & H, b8 & H, B[2], B[3], MAGIC);
     mma_u8s8_k32(lo, c & L, c8 & L, d & L, d8 & L, B[4], B[5]);
     mma_u8s8_k32(hi, c & H, c8 & H, d & H, d8 & H, B[6], B[7]);
 #pragma unroll
@@ -60,8 +64,7 @@ template <int BITS> __device__ __forceinline__ void qk_tile(const uint8_t *rec, 
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const uint32_t M = 0x03030303u << (2 * m);
-      acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = MAGIC;
-      mma_u8s8_k32(acc[m], a & M, a8 & M, c & M, c8 & M, B[m], B[4 + m]);
+      mma_u8s8_k32_from(acc[m], a & M, a8 & M, c & M, c8 & M, B[m], B[4 + m], MAGIC);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -72,9 +75,9 @@ template <int BITS> __device__ __forceinline__ void qk_tile(const uint8_t *rec, 
     const uint32_t a = lds32(p0), a8 = lds32(p1), c = lds32(p0 + 256), c8 = lds32(p1 + 256);
     const uint32_t e = lds32(q0), e8 = lds32(q1), f = lds32(q0 + 8), f8 = lds32(q1 + 8);
     constexpr uint32_t L = 0x07070707u, M = 0x38383838u, T2 = 0x03030303u, T1 = 0x04040404u;
-    uint32_t lo[4] = {MAGIC, MAGIC, MAGIC, MAGIC}, mid[4] = {MAGIC, MAGIC, MAGIC, MAGIC};
-    mma_u8s8_k32(lo, a & L, a8 & L, c & L, c8 & L, B[0], B[1]);
-    mma_u8s8_k32(mid, a & M, a8 & M, c & M, c8 & M, B[2], B[3]);
+    uint32_t lo[4], mid[4];
+    mma_u8s8_k32_from(lo, a & L, a8 & L, c & L, c8 & L, B[0], B[1], MAGIC);
+    mma_u8s8_k32_from(mid, a & M, a8 & M, c & M, c8 & M, B[2], B[3], MAGIC);
     mma_u8s8_k32(lo, ((a >> 6) & T2) | ((e >> sh) & T1), ((a8 >> 6) & T2) | ((e8 >> sh) & T1),
                  ((c >> 6) & T2) | ((f >> sh) & T1), ((c8 >> 6) & T2) | ((f8 >> sh) & T1), B[4], B[5]);
     mma_u8s8_k32(lo, (e >> se) & L, (e8 >> se) & L, (f >> se) & L, (f8 >> se) & L, B[6], B[7]);

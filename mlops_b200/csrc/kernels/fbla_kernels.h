@@ -19,7 +19,8 @@ typedef struct {
 // queries each (virtual head vh = kv_head_linear * vg + j owns queries j * qg .. j * qg + qg - 1 of its KV head).
 // Scratch arrays (all written before they are read; no initial contents needed):
 //   lse    [VH][nblocks][qg]  float  log2 mass of every closed sub-block under the coarse scores
-//   part   [TW + 2 VH][qg][130] float  (m, l, o[128]) partials: slot w + vh for coarse warp w, TW + VH + vh for the BF16 windows
+//   part   [TW + XW + 2 VH][qg][132] float  (o[128], m, l) partials: slot w + vh for coarse warp w, TW + VH + x + vh for window warp x
+//          (XW = coarse_ctas * FBLA_K_WINDOW_WARPS)
 //   dpart  [RW + VH][qg][129] float  (dl, do[128]) corrections of refine warp w at slot w + vh
 //   row_r  [VH][qg]           float  log2 of the row's total coarse mass
 //   counts [VH][nslices]      int    selected sub-blocks per slice of 1024 sub-blocks
@@ -46,6 +47,7 @@ typedef struct {
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
+#define FBLA_K_WINDOW_WARPS 2 /* warps per coarse CTA that serve the BF16 sink / open windows */
 
 cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);
 // occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
