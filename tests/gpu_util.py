@@ -123,6 +123,47 @@ class CLib:
         return out
 
 
+    # ---- device-length calls ----------------------------------------------------------------------------------------
+    def decode_at(self, c, q, length, tokens_offset=0, scale=0.0, tau=0.0, scratch=None, length_stride=0, out=None):
+        """length: int32 device tensor (one entry, or one per batch row with length_stride 1); the cache length is
+        length + tokens_offset; c['capacity'] sets the layout."""
+        cfg = Config(c["batch"], q.shape[1], c["kv_heads"], tokens_offset, scale, tau, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, length_stride)
+        if scratch is None:
+            cap = Config(c["batch"], q.shape[1], c["kv_heads"], c["capacity"], 0, 0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, 0)
+            n = self.lib.mlops_fbla_decode_scratch_bytes(ctypes.byref(cap))
+            scratch = torch.full((n,), 0xFF, dtype=torch.uint8, device=q.device)
+        out = torch.empty_like(q) if out is None else out
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_decode_at(ctypes.byref(cfg), length.data_ptr(), q.data_ptr(), ctypes.byref(kc), out.data_ptr(),
+                                           scratch.data_ptr(), scratch.numel(), self._stream())
+        if st:
+            raise RuntimeError(f"decode_at status {st}: {self.error()}")
+        self.last_scratch = scratch
+        return out
+
+    def append_at(self, c, k, v, length, tokens_offset=0, length_stride=0):
+        """k, v [B, Hkv, 128]: one token per KV head at position length + tokens_offset (the caller advances length)."""
+        cfg = Config(c["batch"], c["kv_heads"], c["kv_heads"], tokens_offset, 0, 0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, length_stride)
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_append_at(ctypes.byref(cfg), length.data_ptr(), k.data_ptr(), v.data_ptr(), ctypes.byref(kc), self._stream())
+        if st:
+            raise RuntimeError(f"append_at status {st}: {self.error()}")
+
+    def prefill_at(self, c, k, v, q, length, count, max_count, tokens_offset=0, out=None):
+        """k, v [B, Hkv, max_count, 128], q [B, Hq, max_count, 128] or None; the chunk is their first *count positions."""
+        qh = q.shape[1] if q is not None else c["kv_heads"]
+        cfg = Config(c["batch"], qh, c["kv_heads"], tokens_offset, 0, 0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, 0)
+        if q is not None and out is None:
+            out = torch.empty_like(q)
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_prefill_at(ctypes.byref(cfg), length.data_ptr(), count.data_ptr(), max_count,
+                                            q.data_ptr() if q is not None else None, k.data_ptr(), v.data_ptr(), ctypes.byref(kc),
+                                            out.data_ptr() if out is not None else None, self._stream())
+        if st:
+            raise RuntimeError(f"prefill_at status {st}: {self.error()}")
+        return out
+
+
 def cache_to_numpy(c):
     """device cache -> the oracle's numpy layout (heads flattened)"""
     B, H = c["batch"], c["kv_heads"]
