@@ -5,6 +5,7 @@
 // synchronises, and keeps only per-thread state (last error, device attribute cache), so calls may come from many
 // host threads at once.
 #include "../../../include/mlops_fbla.h"
+#include "../../../include/mlops_fbla_shard.h"
 #include "../kernels/fbla_kernels.h"
 
 #include <cmath>
@@ -92,10 +93,11 @@ size_t scratch_bytes_of(const mlops_fbla_config *lc) {
   return L.bytes;
 }
 
-mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
-                         uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+// validates a decode and fills the kernels' arguments (out may be null when need_out is false: the shard passes)
+mlops_fbla_status prepare_decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                                 uint16_t *out, bool need_out, void *scratch, size_t scratch_bytes, fbla_k_decode &a) {
   const bool by_capacity = length != nullptr;
-  if (!c || !k || !q || !out || !scratch) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  if (!c || !k || !q || (need_out && !out) || !scratch) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
   mlops_fbla_config lc = *c;
   if (by_capacity) lc.tokens = c->capacity;
   if (!valid_decode_shape(&lc) || (by_capacity && c->tokens < 0))
@@ -111,7 +113,7 @@ mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *
   if ((c->length_stride != 0 && c->length_stride != 1) || (c->length_stride && !length))
     return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0, or 1 with a device length", fn);
 
-  fbla_k_decode a{};
+  a = fbla_k_decode{};
   a.cb = c->format == MLOPS_FBLA_3P3 ? 3 : 4;
   a.fb = c->format == MLOPS_FBLA_3P3 ? 3 : 2;
   cudaError_t e = fbla_k_decode_shape(&a);
@@ -145,9 +147,18 @@ mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *
   a.sl = scale_log2(c);
   const float tau = c->tau != 0.f ? c->tau : c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f;
   a.log2_tau = log2f(tau);
-  e = fbla_k_decode_launch(&a, stream);
+  return MLOPS_FBLA_OK;
+}
+mlops_fbla_status launch_decode(const char *fn, const fbla_k_decode &a, cudaStream_t stream) {
+  const cudaError_t e = fbla_k_decode_launch(&a, stream);
   if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
   return ok();
+}
+mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                         uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  fbla_k_decode a;
+  const mlops_fbla_status st = prepare_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a);
+  return st != MLOPS_FBLA_OK ? st : launch_decode(fn, a, stream);
 }
 
 // ---- prefill ------------------------------------------------------------------------------------------------------------
@@ -283,6 +294,60 @@ mlops_fbla_status mlops_fbla_prefill_at(const mlops_fbla_config *c, const int *l
 mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *c, const int *length, const uint16_t *k, const uint16_t *v,
                                        const mlops_fbla_cache *cache, cudaStream_t stream) {
   return prefill_at("mlops_fbla_append_at", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, stream);
+}
+
+// ---- sequence shards (include/mlops_fbla_shard.h) ------------------------------------------------------------------------
+static mlops_fbla_status shard_args(const char *fn, const mlops_fbla_shard *sh, fbla_k_decode &a) {
+  if (!sh || sh->group_first < 0 || sh->group_count < 0 || (sh->windows & ~3))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: shard needs group_first >= 0, group_count >= 0, windows in 0..3", fn);
+  a.shard_on = 1; a.sh_first = sh->group_first; a.sh_count = sh->group_count; a.sh_windows = sh->windows;
+  return MLOPS_FBLA_OK;
+}
+
+mlops_fbla_status mlops_fbla_shard_mass(const mlops_fbla_config *c, const mlops_fbla_shard *sh, const uint16_t *q, const mlops_fbla_cache *k,
+                                        float *row_mass, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_shard_mass";
+  if (!row_mass || !aligned(row_mass, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: row_mass must be a 16-byte aligned device pointer", fn);
+  fbla_k_decode a;
+  mlops_fbla_status st = prepare_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
+  if (st == MLOPS_FBLA_OK) st = shard_args(fn, sh, a);
+  if (st != MLOPS_FBLA_OK) return st;
+  a.phase = 1;
+  a.row_r = row_mass;
+  return launch_decode(fn, a, stream);
+}
+
+mlops_fbla_status mlops_fbla_shard_partial(const mlops_fbla_config *c, const mlops_fbla_shard *sh, const uint16_t *q, const mlops_fbla_cache *k,
+                                           const float *row_mass_total, float *partial, void *scratch, size_t scratch_bytes,
+                                           cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_shard_partial";
+  if (!row_mass_total || !partial || !aligned(row_mass_total, 16) || !aligned(partial, 16))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: row_mass_total and partial must be 16-byte aligned device pointers", fn);
+  fbla_k_decode a;
+  mlops_fbla_status st = prepare_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
+  if (st == MLOPS_FBLA_OK) st = shard_args(fn, sh, a);
+  if (st != MLOPS_FBLA_OK) return st;
+  a.phase = 2;
+  a.row_r = const_cast<float *>(row_mass_total);
+  a.out_partial = partial;
+  return launch_decode(fn, a, stream);
+}
+
+mlops_fbla_status mlops_fbla_shard_total_mass(int shards, int rows, const float *gathered, float *row_mass_total, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_shard_total_mass";
+  if (shards <= 0 || rows <= 0 || !gathered || !row_mass_total) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: shards and rows must be positive, pointers non-null", fn);
+  const cudaError_t e = fbla_k_total_mass_launch(gathered, row_mass_total, shards, rows, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
+}
+
+mlops_fbla_status mlops_fbla_shard_combine(int rows, const float *partial_sum, uint16_t *output, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_shard_combine";
+  if (rows <= 0 || !partial_sum || !output || !aligned(partial_sum, 16) || !aligned(output, 16))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: rows must be positive, pointers 16-byte aligned", fn);
+  const cudaError_t e = fbla_k_combine_launch(partial_sum, output, rows, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
 }
 
 const char *mlops_fbla_status_string(mlops_fbla_status status) {

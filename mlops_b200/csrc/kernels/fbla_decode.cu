@@ -40,15 +40,19 @@ template <int CB> struct CoarseShape {
 static_assert(FBLA_NP >= 2 && FBLA_NP <= 4, "ring slots per warp");
 
 // ---- where a batch row's tokens put its units -----------------------------------------------------------------------
-struct Row { int tokens, groups, closed, exact; };
+struct Row { int tokens, groups, g0, closed, na, exact; };  // g0: the first closed group processed; na: sink sub-blocks
 __device__ __forceinline__ Row row_of(const fbla_k_decode &a, int b) {
   Row r;
   r.tokens = (a.length ? __ldg(a.length + (a.lstride ? b : 0)) : 0) + a.tokens;
   r.groups = (r.tokens + G - 1) / G;
-  r.closed = r.groups >= 3 ? r.groups - 2 : 0;
-  const int na = r.groups == 1 ? (r.tokens + S - 1) / S : (r.groups >= 2 ? SBG : 0);
-  const int no = r.groups >= 2 ? (r.tokens - G * (r.groups - 1) + S - 1) / S : 0;
-  r.exact = na + no;  // BF16 sub-blocks: the sink's, then the open group's
+  int first = 1, last = r.groups - 1, win = 3;  // closed groups [first, last); the whole cache: 1 .. groups - 2
+  if (a.shard_on) { first = a.sh_first; last = min(last, a.sh_first + a.sh_count); win = a.sh_windows; }
+  r.g0 = first;
+  r.closed = max(last - first, 0);
+  r.na = !(win & 1) ? 0 : r.groups == 1 ? (r.tokens + S - 1) / S : (r.groups >= 2 ? SBG : 0);
+  // the open window: the last group's tokens; a cache of one group is read through its sink window unless only the open one is asked for
+  const int no = !(win & 2) ? 0 : r.groups >= 2 ? (r.tokens - G * (r.groups - 1) + S - 1) / S : (win & 1) ? 0 : (r.tokens + S - 1) / S;
+  r.exact = r.na + no;  // BF16 sub-blocks: the sink's, then the open group's
   return r;
 }
 // Flattened unit lists. Closed groups: row b contributes hpr * closed(b) units, head-major. BF16 sub-blocks likewise.
@@ -56,6 +60,8 @@ __device__ __forceinline__ Row row_of(const fbla_k_decode &a, int b) {
 struct Cursor {
   int b, hir, i, n;  // batch row, virtual head within the row, index within the head's n units
 };
+// the group of closed-group cursor c
+__device__ __forceinline__ int group_of(const fbla_k_decode &a, const Cursor &c) { return row_of(a, c.b).g0 + c.i; }
 template <bool EXACT>
 __device__ __forceinline__ int units_of(const Row &r) { return EXACT ? r.exact : r.closed; }
 
@@ -206,7 +212,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       __syncwarp();
     }
     const Row r = row_of(a, c.b);
-    const int na = r.groups == 1 ? (r.tokens + S - 1) / S : SBG;
+    const int na = r.na;
     const bool sink = c.i < na;
     const int j = sink ? c.i : c.i - na;
     const int count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
@@ -297,7 +303,7 @@ template <int CB> struct Ring {
   const uint8_t *src_pair, *src_meta;  // that group's records and metadata
   __device__ __forceinline__ void point() {
     const int bh = (fc.b * hpr + fc.hir) / a.vg;
-    const size_t unit = (size_t)bh * a.hs + (size_t)(1 + fc.i) * a.gs;
+    const size_t unit = (size_t)bh * a.hs + (size_t)group_of(a, fc) * a.gs;
     src_pair = a.c.coarse + unit * Sh::GROUP_BYTES;
     src_meta = reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024;
   }
@@ -560,7 +566,7 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coa
         q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
       }
     }
-    if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)(1 + cc.i) * SBG) * QG)) {
+    if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)group_of(a, cc) * SBG) * QG)) {
       if (lane == 0) report(a, 1);
       return;
     }
@@ -602,16 +608,19 @@ __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
   const Slots s = slots_of(a, vh);
   wait_previous_pass();
   // the slice's sub-block masses first (they do not depend on R): every load of the warp in flight together
-  const int lo = SBG + slice * SLICE + warp * (SLICE / 8), hi = SBG * (row.groups - 1);
+  const int lo = slice * SLICE + warp * (SLICE / 8), first = SBG * row.g0, hi = SBG * (row.g0 + row.closed);
   float x[4][QG];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int sb = lo + 32 * i + lane;
-    const float *p = a.lse + ((size_t)vh * a.nblocks + min(sb, max(hi - 1, 0))) * QG;
+    const bool closed = a.phase != 1 && sb >= first && sb < hi;
+    const float *p = a.lse + ((size_t)vh * a.nblocks + (closed ? sb : 0)) * QG;
 #pragma unroll
-    for (int qi = 0; qi < QG; ++qi) x[i][qi] = sb < hi ? __ldcg(p + qi) : -INFINITY;
+    for (int qi = 0; qi < QG; ++qi) x[i][qi] = closed ? __ldcg(p + qi) : -INFINITY;
   }
-  if (warp < QG) {  // R of query `warp`: one pass over the head's partial (m, l), merged online, then across lanes
+  if (a.phase == 2) {  // the rows' (global) log2 mass is given
+    if (threadIdx.x < QG) R[threadIdx.x] = __ldcg(a.row_r + vh * QG + threadIdx.x);
+  } else if (warp < QG) {  // R of query `warp`: one pass over the head's partial (m, l), merged online, then across lanes
     const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
     float mx = -INFINITY, ls = 0.f;
     for (int i = lane; i < n; i += 32) {
@@ -632,9 +641,10 @@ __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
       ls = (lane & o) ? a2 + a1 : a1 + a2;
       mx = mn;
     }
-    const float r = mx + lg2(ls);
+    const float r = mx + lg2(ls);  // (-inf for a shard that holds nothing of this row)
     if (!lane) { R[warp] = r; if (!slice) a.row_r[vh * QG + warp] = r; }
   }
+  if (a.phase == 1) return;  // only the local mass was asked for
   __syncthreads();
   int qm[4], n = 0;
   uint32_t bal[4];
@@ -968,7 +978,13 @@ __global__ void __launch_bounds__(512) merge_kernel(const fbla_k_decode a) {
   __syncthreads();
   if (sl == 0) {
     const float Os = (so[0][ch] + so[1][ch]) + (so[2][ch] + so[3][ch]), Ls = (sl_[0] + sl_[1]) + (sl_[2] + sl_[3]);
-    a.out[(size_t)q_row(a, b, hir, qi) * D + ch] = f32_to_bf16(__fdividef(Os, Ls));
+    const size_t row = (size_t)q_row(a, b, hir, qi);
+    if (a.out_partial) {  // a shard's share of the row, in units of 2^-R: summed over the shards before the division
+      a.out_partial[row * PSTRIDE + ch] = Os;
+      if (ch == 0) a.out_partial[row * PSTRIDE + D] = Ls;
+    } else {
+      a.out[row * D + ch] = f32_to_bf16(__fdividef(Os, Ls));
+    }
   }
 }
 
@@ -1000,15 +1016,49 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
     if (dev >= 0 && dev < 64) configured[dev] = 1;
   }
   if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
-  coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, stream>>>(a);
-  cudaError_t e = cudaGetLastError();
-  if (e == cudaSuccess) e = launch_dependent(select_kernel<QG>, dim3(a.nslices, vheads), dim3(256), 0, stream, a);
+  cudaError_t e = cudaSuccess;
+  if (a.phase != 2) {
+    coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, stream>>>(a);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = launch_dependent(select_kernel<QG>, dim3(a.phase == 1 ? 1 : a.nslices, vheads), dim3(256), 0, stream, a);
+    if (a.phase == 1) return e;
+  } else {
+    select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a);
+    e = cudaGetLastError();
+  }
   if (e == cudaSuccess) e = launch_dependent(refine_kernel<CB, FB, QG>, dim3(a.refine_ctas), dim3(32 * RefineShape<CB, FB>::WARPS), rsm, stream, a);
   if (e == cudaSuccess) e = launch_dependent(merge_kernel<QG>, dim3(vheads * QG), dim3(512), 0, stream, a);
   return e;
 }
 
+// a row's shares summed over the shards -> the BF16 output
+__global__ void __launch_bounds__(128) combine_kernel(const float *partial, uint16_t *out) {
+  const float *p = partial + (size_t)blockIdx.x * PSTRIDE;
+  out[(size_t)blockIdx.x * D + threadIdx.x] = f32_to_bf16(__fdividef(p[threadIdx.x], p[D]));
+}
+
+// R_total[i] = log2 sum_s 2^(mass[s][i]) over the shards (masses of -inf contribute nothing)
+__global__ void __launch_bounds__(128) total_mass_kernel(const float *mass, float *total, int shards, int rows) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  float mx = -INFINITY;
+  for (int s = 0; s < shards; ++s) mx = fmaxf(mx, mass[(size_t)s * rows + i]);
+  float sum = 0.f;
+  for (int s = 0; s < shards; ++s) { const float m = mass[(size_t)s * rows + i]; if (m != -INFINITY) sum += ex2(m - mx); }
+  total[i] = mx + lg2(sum);
+}
+
 }  // namespace fbla
+
+extern "C" cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream) {
+  fbla::total_mass_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(mass, total, shards, rows);
+  return cudaGetLastError();
+}
+
+extern "C" cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out, int rows, cudaStream_t stream) {
+  fbla::combine_kernel<<<rows, 128, 0, stream>>>(partial, out);
+  return cudaGetLastError();
+}
 
 #ifdef FBLA_TIMING
 extern "C" cudaError_t fbla_k_debug_read(long long *host) { return cudaMemcpyFromSymbol(host, fbla::fbla_dbg, sizeof(fbla::fbla_dbg)); }

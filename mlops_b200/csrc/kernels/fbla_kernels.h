@@ -43,6 +43,12 @@ typedef struct {
   int coarse_ctas, coarse_warps;  // persistent coarse CTAs and warps per CTA (TW = coarse_ctas * coarse_warps)
   int refine_ctas, refine_warps;  // RW = refine_ctas * refine_warps
   float sl, log2_tau;
+  // Sequence shards (one GPU's part of a long context); shard_on 0: the whole cache. A shard processes the closed groups
+  // [sh_first, sh_first + sh_count) of its local cache, the BF16 sink window if sh_windows & 1, the open window if & 2.
+  // phase 0: a whole decode. phase 1: coarse pass, then only the rows' local log2 mass into row_r. phase 2: select with
+  // the given (global) row_r, refine, and the rows' unnormalised sums (o[128], l, relative to row_r) into out_partial.
+  int shard_on, sh_first, sh_count, sh_windows, phase;
+  float *out_partial;  // [rows][FBLA_K_PSTRIDE] floats (phase 2)
 } fbla_k_decode;
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
@@ -50,6 +56,10 @@ typedef struct {
 #define FBLA_K_WINDOW_WARPS 2 /* warps per coarse CTA that serve the BF16 sink / open windows */
 
 cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);
+// out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
+// total[i] = log2 sum over shards of 2^mass[s][i]
+cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);
+cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out, int rows, cudaStream_t stream);
 // occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
 cudaError_t fbla_k_decode_shape(fbla_k_decode *a);
 
