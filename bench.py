@@ -250,13 +250,107 @@ def refine_share(scratch, cfg, _C, vheads, nsl):
     return total / max(1, closed_blocks)
 
 
+def run_seqsplit(args):
+    """BASELINE configs[2]: one sequence (batch 1, 32q/8kv, 3+3, plain N(0,1)) of 256K or 1M tokens split over the
+    ranks by whole groups; every decode step = two local passes + two NCCL exchanges (mass, partial sums)."""
+    import torch
+    import torch.distributed as dist
+
+    from mlops_b200.attention import sharded
+    from tests import datagen
+
+    tokens = 262144 if args.workload == "seqsplit_256k" else 1 << 20
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    plan = sharded.plan_shards(tokens, world)[rank]
+    n = plan.token_end - plan.token_first + plan.extra
+    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16)
+    q, _, _ = datagen.baseline_case(1003, 1, 32, 8, 1, outliers=False)
+    qd = bf(q).to(dev)
+    chunks_k, chunks_v = [], []
+    for c0 in range(0, n, 65536):  # the rank's tokens, generated in chunks to bound host memory
+        _, k, v = datagen.baseline_case(1003 + 977 * rank + c0, 1, 32, 8, min(65536, n - c0), outliers=False)
+        chunks_k.append(bf(k).to(dev)); chunks_v.append(bf(v).to(dev))
+    shard = sharded.encode_shard(torch.cat(chunks_k, 2), torch.cat(chunks_v, 2), "3+3", plan)
+    del chunks_k, chunks_v
+    group = dist.group.WORLD if world > 1 else None
+    for _ in range(max(args.warmup, 3)):
+        out = sharded.decode(qd, shard, group)
+    torch.cuda.synchronize()
+    # one decode step (both passes and both exchanges) as a CUDA graph: the step is a handful of ~30 us kernels, so
+    # host launch overhead would otherwise be what is measured
+    graph, mode_ = None, "eager"
+    try:
+        if world > 1:  # the exchanges are NCCL calls: left out of graphs here (a rank that failed to capture would desynchronise the others)
+            raise RuntimeError("multi-rank steps are launched eagerly")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                out = sharded.decode(qd, shard, group)
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()
+        torch.cuda.synchronize()
+        graph, mode_ = g, "cuda graph"
+    except Exception as exc:  # noqa: BLE001
+        print(f"graph capture unavailable ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+    if world > 1:
+        dist.barrier()
+    stream = torch.cuda.current_stream()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            out = sharded.decode(qd, shard, group)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    clocks = sampler.result()
+    if rank == 0:
+        groups = tokens // 128
+        coarse = 8 * ((groups - 2) * (8 * 1536 + 1024) + (128 + 128) * 512)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak = peaks.get("hbm_gbs", 6650.0)
+        ach = coarse / (ms * 1e-3) / 1e9
+        print(json.dumps(dict(metric=METRIC, value=1000.0 / ms, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms,
+                              higher_is_better=True, scaling="strong", vs_baseline=None, dtype="u8", data="synthetic",
+                              config=dict(workload=f"sequence-split decode B1 32q/8kv ctx{tokens} 3+3 (BASELINE configs[2])", tokens=tokens, l2="cache larger than L2", launch=mode_),
+                              gpu_launches=(2 + 3 + 2) * args.steps,
+                              roofline=dict(bound="hbm", achieved=ach, peak=peak * world, unit="GB/s", frac=ach / (peak * world), traffic=None,
+                                            algorithmic_bytes=coarse, note="coarse planes + metadata + BF16 windows only (refined share not counted)"),
+                              clocks=clocks)))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m"],
+                    help="decode_b8: the headline (BASELINE configs[1]); seqsplit_*: one long sequence split over the ranks (configs[2])")
     args = ap.parse_args()
+    if args.workload != "decode_b8" and args.impl == "ours":
+        return run_seqsplit(args)
     if args.impl == "reference":
         run_reference(args)
     else:

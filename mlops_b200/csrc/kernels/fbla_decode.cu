@@ -29,15 +29,19 @@ constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 #define FBLA_CW3 10
 #endif
 #ifndef FBLA_NP
-#define FBLA_NP 4
+#define FBLA_NP 2
+#endif
+#ifndef FBLA_PPC
+#define FBLA_PPC 2  // record pairs per chunk (one bulk copy, one barrier wait)
 #endif
 template <int CB> struct CoarseShape {
   static constexpr int WARPS = CB == 4 ? FBLA_CW4 : FBLA_CW3;
   static constexpr int NP = FBLA_NP;
-  static constexpr int PAIR_BYTES = 2 * record_bytes(CB);
+  static constexpr int PPC = FBLA_PPC, CPG = 4 / FBLA_PPC;  // pairs per chunk, chunks per group
+  static constexpr int PAIR_BYTES = 2 * record_bytes(CB), CHUNK_BYTES = FBLA_PPC * PAIR_BYTES;
   static constexpr int GROUP_BYTES = SBG * record_bytes(CB);
 };
-static_assert(FBLA_NP >= 2 && FBLA_NP <= 4, "ring slots per warp");
+static_assert(FBLA_NP >= 2 && FBLA_NP * FBLA_PPC <= 4 && 4 % FBLA_PPC == 0, "ring slots per warp: at most one group of lookahead");
 
 // ---- where a batch row's tokens put its units -----------------------------------------------------------------------
 struct Row { int tokens, groups, g0, closed, na, exact; };  // g0: the first closed group processed; na: sink sub-blocks
@@ -149,7 +153,7 @@ __device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, ui
 
 // ---- shared memory of the coarse kernel ---------------------------------------------------------------------------------
 template <int CB> struct __align__(128) StreamWarp {
-  uint8_t pair[CoarseShape<CB>::NP][CoarseShape<CB>::PAIR_BYTES];  // ring of record pairs
+  uint8_t pair[CoarseShape<CB>::NP][CoarseShape<CB>::CHUNK_BYTES];  // ring of chunks (PPC record pairs each)
   uint8_t meta[2][1024];                                           // metadata of the group in progress and of the next
   uint8_t qst[8 * QST_ROW];  // qhat rows (rows >= QG stay zero)
   uint8_t pst[128];          // P bytes of a record pair: [block parity][query 0..3][16 tokens]
@@ -178,6 +182,12 @@ __device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
 // Unit = one 16-token sub-block of the sink (first) or the open window. Scores s = sl * (q . k) in FP32, the same
 // integer P block, values in FP32. Lane (t = lane % 16, h = lane / 16) scores token t over channels 64 h .. 64 h + 63;
 // for the values lane l owns channels 4 l .. 4 l + 3.
+// one window sub-block's rows in registers: the lane's 64 channels of its token's K row, and its 4 channels of all 16 V rows
+struct WindowTile {
+  uint4 k[8];
+  uint2 v[16];
+  int j, count;  // sub-block within its window, the window's token count
+};
 template <int QG>
 __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
   const int hpr = a.kv_heads * a.vg;
@@ -185,6 +195,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
   const long long lo = (long long)xw * per, hi = min(total, lo + per);
   if (lo >= hi) return;
   const int slot0 = a.coarse_ctas * a.coarse_warps + a.batch * hpr;  // after the coarse slots
+  const int t = lane & 15, h = lane >> 4;
   Cursor c = locate<true>(a, hpr, lo);
   int cur_vh = -1;
   float m[QG], l[QG], o[QG][4];
@@ -196,8 +207,26 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       if (!lane) { p[qi * PSTRIDE + D] = m[qi]; p[qi * PSTRIDE + D + 1] = l[qi]; }
     }
   };
-  for (long long u = lo; u < hi; ++u, advance<true>(a, hpr, c)) {
-    const int vh = c.b * hpr + c.hir, bh = vh / a.vg;
+  // all loads of a sub-block at once (the next sub-block's are issued before the current one is computed)
+  auto load = [&](const Cursor &cu, WindowTile &w) {
+    const Row r = row_of(a, cu.b);
+    const bool sink = cu.i < r.na;
+    w.j = sink ? cu.i : cu.i - r.na;
+    w.count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
+    const size_t eh = (size_t)((cu.b * hpr + cu.hir) / a.vg) * G * D;
+    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh;
+    const int tok = w.j * S + t;
+    const uint4 *kp = reinterpret_cast<const uint4 *>(ek + (size_t)min(tok, G - 1) * D + 64 * h);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w.k[i] = tok < w.count ? __ldcg(kp + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int tt = 0; tt < S; ++tt)
+      w.v[tt] = w.j * S + tt < w.count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(w.j * S + tt) * D) + lane) : make_uint2(0u, 0u);
+  };
+  WindowTile cur, nxt;
+  load(c, cur);
+  for (long long u = lo; u < hi; ++u) {
+    const int vh = c.b * hpr + c.hir;
     if (vh != cur_vh) {
       if (cur_vh >= 0) flush();
       cur_vh = vh;
@@ -211,27 +240,21 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       }
       __syncwarp();
     }
-    const Row r = row_of(a, c.b);
-    const int na = r.na;
-    const bool sink = c.i < na;
-    const int j = sink ? c.i : c.i - na;
-    const int count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
-    const size_t eh = (size_t)bh * G * D;
-    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh;
-    const int t = lane & 15, h = lane >> 4, tok = j * S + t;
+    advance<true>(a, hpr, c);
+    if (u + 1 < hi) load(c, nxt);
+    const int tok = cur.j * S + t;
     float x[QG];
 #pragma unroll
     for (int qi = 0; qi < QG; ++qi) x[qi] = 0.f;
-    if (tok < count) {
-      const uint4 *kp = reinterpret_cast<const uint4 *>(ek + (size_t)tok * D + 64 * h);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint4 w = __ldcg(kp + i);
-        const float kv[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+    for (int i = 0; i < 8; ++i) {
+      const uint4 w = cur.k[i];
+      const float kv[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
 #pragma unroll
-        for (int qi = 0; qi < QG; ++qi)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) x[qi] = fmaf(sm.q[qi][64 * h + 8 * i + e], kv[e], x[qi]);
+      for (int qi = 0; qi < QG; ++qi) {
+        const float4 qa = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i]), qb = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i + 4]);
+        x[qi] = fmaf(qa.x, kv[0], x[qi]); x[qi] = fmaf(qa.y, kv[1], x[qi]); x[qi] = fmaf(qa.z, kv[2], x[qi]); x[qi] = fmaf(qa.w, kv[3], x[qi]);
+        x[qi] = fmaf(qb.x, kv[4], x[qi]); x[qi] = fmaf(qb.y, kv[5], x[qi]); x[qi] = fmaf(qb.z, kv[6], x[qi]); x[qi] = fmaf(qb.w, kv[7], x[qi]);
       }
     }
     float al[QG], w[QG], sp[QG];
@@ -239,7 +262,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
 #pragma unroll
     for (int qi = 0; qi < QG; ++qi) {
       x[qi] += __shfl_xor_sync(FULL, x[qi], 16);
-      const float s = tok < count ? __fmul_rn(x[qi], a.sl) : -INFINITY;
+      const float s = tok < cur.count ? __fmul_rn(x[qi], a.sl) : -INFINITY;
       float mb = s;
 #pragma unroll
       for (int off = 8; off; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(FULL, mb, off));
@@ -261,11 +284,12 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
     for (int qi = 0; qi < QG; ++qi) y[qi][0] = y[qi][1] = y[qi][2] = y[qi][3] = 0.f;
 #pragma unroll
     for (int tt = 0; tt < S; ++tt) {
-      const uint2 vw = j * S + tt < count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(j * S + tt) * D) + lane) : make_uint2(0u, 0u);
+      const uint2 vw = cur.v[tt];
       const float vv[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
 #pragma unroll
       for (int qi = 0; qi < QG; ++qi) {
-        const float p = (float)((P[qi][tt >> 2] >> (8 * (tt & 3))) & 255u);
+        // the byte as a float without a conversion instruction: the bits of 2^23 + p, minus 2^23
+        const float p = __uint_as_float(0x4B000000u | ((P[qi][tt >> 2] >> (8 * (tt & 3))) & 255u)) - 8388608.f;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) y[qi][cc] = fmaf(p, vv[cc], y[qi][cc]);
       }
@@ -277,6 +301,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       for (int cc = 0; cc < 4; ++cc) o[qi][cc] = fmaf(al[qi], o[qi][cc], w[qi] * y[qi][cc]);
     }
     __syncwarp();
+    cur = nxt;
   }
   flush();
 }
@@ -286,12 +311,13 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
 // of queries qe = 2 (tig & 1) + e, e = 0, 1, summed over the sub-blocks of parity tig >> 1 only: the two parities'
 // threads are added when the partial is written.
 struct Run {
-  float m[2], l[2], o[4][4][2];
+  float m[2], l[2];
+  float2 o[4][4];  // (.x, .y) = queries e = 0, 1
 };
 template <int QG> __device__ __forceinline__ bool query_valid(int tig, int e) { return 2 * (tig & 1) + e < QG; }
 
-// The warp's stream of record pairs: chunk p = 4 k + i is pair i of the k-th group of the warp's range, in ring slot
-// p % NP (its (p / NP)-th use); the group's metadata travels with pair 0 into metadata slot k & 1. All lanes carry the
+// The warp's stream of record pairs: chunk p = CPG k + i holds pairs PPC i .. of the k-th group of the warp's range, in ring
+// slot p % NP (its (p / NP)-th use); the group's metadata travels with chunk 0 into metadata slot k & 1. All lanes carry the
 // (warp-uniform) state; lane 0 issues the copies.
 template <int CB> struct Ring {
   using Sh = CoarseShape<CB>;
@@ -309,24 +335,32 @@ template <int CB> struct Ring {
   }
   __device__ __forceinline__ void issue_next() {
     if (issued >= chunks) return;
-    const int i = issued & 3, slot = issued % Sh::NP, ms = (issued >> 2) & 1;
-    if (lane == 0) {
-      fence_async_smem();  // the slot's earlier reads (ordered before this point by __syncwarp) precede the copy's writes
+    const int i = issued % Sh::CPG, slot = issued % Sh::NP, ms = (issued / Sh::CPG) & 1;
+    if (lane == 0) {  // (the slot's earlier reads have completed: their values were consumed before the __syncwarp above)
       if (i == 0) {
         mbar_expect_tx(&w.bar_meta[ms], 1024);
         bulk_g2s(w.meta[ms], src_meta, 1024, &w.bar_meta[ms]);
       }
-      mbar_expect_tx(&w.bar_pair[slot], Sh::PAIR_BYTES);
-      bulk_g2s(w.pair[slot], src_pair + i * Sh::PAIR_BYTES, Sh::PAIR_BYTES, &w.bar_pair[slot]);
+      mbar_expect_tx(&w.bar_pair[slot], Sh::CHUNK_BYTES);
+      bulk_g2s(w.pair[slot], src_pair + i * Sh::CHUNK_BYTES, Sh::CHUNK_BYTES, &w.bar_pair[slot]);
     }
     ++issued;
-    if (i == 3 && issued < chunks) { advance<false>(a, hpr, fc); point(); }
+    if (i == Sh::CPG - 1 && issued < chunks) { advance<false>(a, hpr, fc); point(); }
   }
   // false: a bounded wait gave up
   __device__ __forceinline__ bool wait_meta(int k) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_meta[k & 1], (uint32_t)((k >> 1) & 1))); }
   __device__ __forceinline__ bool wait_pair(int p) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_pair[p % Sh::NP], (uint32_t)((p / Sh::NP) & 1))); }
 };
 
+#ifdef FBLA_TIMING
+__device__ long long fbla_sec[148 * 16 * 8];
+__shared__ long long fbla_sec_sm[16 * 8];
+#define SEC(i) { const long long t_ = clock64(); if ((threadIdx.x & 31) == 0) fbla_sec_sm[(threadIdx.x >> 5) * 8 + (i)] += t_ - tsec_; tsec_ = clock64(); }
+#define SEC0 long long tsec_ = clock64();
+#else
+#define SEC(i)
+#define SEC0
+#endif
 // Group k of the warp's range. Returns false if a bounded wait gave up.
 template <int CB, int FB, int QG>
 __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4 (&q4)[QG], float sl, int lane, Run &run,
@@ -355,61 +389,72 @@ __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4
   uint32_t B[8];
   qhat_frag<CB>(sm.qst, gid, tig, B);
   // the group's sums in code units, relative to the running maximum run.m: A = sum w y, Bs = sum w sum p
-  float A[4][4][2], Bs[2] = {0.f, 0.f};
+  float2 A[4][4], Bs = make_float2(0.f, 0.f);
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) A[u][cc][0] = A[u][cc][1] = 0.f;
-#pragma unroll 1
-  for (int J = 0; J < SBG / 2; ++J) {  // sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1)
-    const int p = 4 * k + J;
-    if (!ring.wait_pair(p)) return false;
-    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP], *rb = ra + RB;
-    // scores s[par][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1);
-    // only columns < QG (threads tig < 2) are queries, the others multiply zero rows of qst
-    float s[2][4], mb[2][2];
-    {
+    for (int cc = 0; cc < 4; ++cc) A[u][cc] = make_float2(0.f, 0.f);
+  const float2 sqc2 = make_float2(sqc[0], sqc[1]), c02 = make_float2(c0[0], c0[1]);
+  // Software pipeline over the group's four record pairs: the scores of pair J + 1 (stage A: shared loads, score products,
+  // sub-block maxima) are issued before the softmax and value products of pair J (stage B), so that each stage's
+  // latencies are covered by the other's instructions.
+  struct Scores { float s[2][4], mb[2][2]; };
+  // stage A of pair J: scores s[par][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1)
+  // (only columns < QG, i.e. threads tig < 2, are queries; the others multiply zero rows of qst), and their maxima
+  auto stage_a = [&](int J, Scores &sc) -> bool {
+    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;  // the pair's chunk
+    if (J % CoarseShape<CB>::PPC == 0 && !ring.wait_pair(p)) return false;
+    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP] + (J % CoarseShape<CB>::PPC) * CoarseShape<CB>::PAIR_BYTES, *rb = ra + RB;
+#pragma unroll
+    for (int par = 0; par < 2; ++par) {
       float x[4];
-      qk_tile<CB>(ra, gid, tig, B, x);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s[0][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
-      qk_tile<CB>(rb, gid, tig, B, x);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s[1][i] = fmaf(sqc[i & 1], x[i], c0[i & 1]);
+      qk_tile<CB>(par ? rb : ra, gid, tig, B, x);
+      const float2 s01 = __ffma2_rn(sqc2, make_float2(x[0], x[1]), c02), s23 = __ffma2_rn(sqc2, make_float2(x[2], x[3]), c02);
+      sc.s[par][0] = s01.x; sc.s[par][1] = s01.y; sc.s[par][2] = s23.x; sc.s[par][3] = s23.y;
     }
 #pragma unroll
     for (int par = 0; par < 2; ++par)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        float v = fmaxf(s[par][e], s[par][2 + e]);
+        float v = fmaxf(sc.s[par][e], sc.s[par][2 + e]);
         v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
         v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
         v = fmaxf(v, __shfl_xor_sync(FULL, v, 16));
-        mb[par][e] = v;
+        sc.mb[par][e] = v;
       }
+    return true;
+  };
+  // stage B of pair J: sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1)
+  auto stage_b = [&](int J, const Scores &sc) {
+    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;
+    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP] + (J % CoarseShape<CB>::PPC) * CoarseShape<CB>::PAIR_BYTES, *rb = ra + RB;
     // the thread's own sub-block 2 J + (tig >> 1) of queries 2 (tig & 1) + e, and the pair's maximum (the same value in
     // both parities' threads, so their running maxima stay equal)
     float mbj[2], mp[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const float other = __shfl_xor_sync(FULL, mb[1][e], 2);
-      mbj[e] = odd ? other : mb[0][e];
-      const float pm = fmaxf(mb[0][e], mb[1][e]), pmo = __shfl_xor_sync(FULL, pm, 2);
+      const float other = __shfl_xor_sync(FULL, sc.mb[1][e], 2);
+      mbj[e] = odd ? other : sc.mb[0][e];
+      const float pm = fmaxf(sc.mb[0][e], sc.mb[1][e]), pmo = __shfl_xor_sync(FULL, pm, 2);
       mp[e] = odd ? pmo : pm;
     }
     // the running maximum moves only when a pair exceeds it by more than 2^8 (weights stay <= 2^8; the rescale is rare)
     const bool grow = mp[0] > run.m[0] + 8.f || mp[1] > run.m[1] + 8.f;
     if (__any_sync(FULL, grow)) {
+      float alv[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const float mn = mp[e] > run.m[e] + 8.f ? mp[e] : run.m[e], al = ex2(run.m[e] - mn);  // (2^-inf = 0 on the first group)
         run.m[e] = mn;
-        run.l[e] *= al; Bs[e] *= al;
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) { run.o[u][cc][e] *= al; A[u][cc][e] *= al; }
+        run.l[e] *= al;
+        alv[e] = al;
       }
+      const float2 al2 = make_float2(alv[0], alv[1]);
+      Bs = __fmul2_rn(Bs, al2);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) { run.o[u][cc] = __fmul2_rn(run.o[u][cc], al2); A[u][cc] = __fmul2_rn(A[u][cc], al2); }
     }
     if (tig < 2) {  // P bytes: pst[parity][query][token]
 #pragma unroll
@@ -418,25 +463,23 @@ __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4
         for (int e = 0; e < 2; ++e)
           if (query_valid<QG>(tig, e)) {
             const int qe = 2 * tig + e;
-            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)__float_as_uint(fmaf(ex2(s[par][e] - mb[par][e]), 255.f, MAGICF));
-            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)__float_as_uint(fmaf(ex2(s[par][2 + e] - mb[par][e]), 255.f, MAGICF));
+            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)__float_as_uint(fmaf(ex2(sc.s[par][e] - sc.mb[par][e]), 255.f, MAGICF));
+            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)__float_as_uint(fmaf(ex2(sc.s[par][2 + e] - sc.mb[par][e]), 255.f, MAGICF));
           }
     }
     __syncwarp();
     // column gid of the value products: gid < 4: parity 0, query gid, k block = tokens 4 tig ..; gid >= 4: parity 1
     const uint32_t pw = lds32(sm.pst + 4 * lane);
     const uint32_t b0 = gid < 4 ? pw : 0u, b1 = gid < 4 ? 0u : pw;
-    float wj[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) wj[e] = ex2(mbj[e] - run.m[e]);
+    const float2 wj = make_float2(ex2(mbj[0] - run.m[0]), ex2(mbj[1] - run.m[1]));
     {  // sum p of both sub-blocks, every column: a product with an all-ones A
       uint32_t d[4];
       mma_u8u8_k32_from(d, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1, MAGIC);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float sp = isum(d[e]);
-        Bs[e] = fmaf(wj[e], sp, Bs[e]);
-        if (gid == 0 && query_valid<QG>(tig, e)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1) + e] = mbj[e] + lg2(sp);
+      const float2 sp = isum2(d[0], d[1]);
+      Bs = __ffma2_rn(wj, sp, Bs);
+      if (gid == 0) {
+        if (query_valid<QG>(tig, 0)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1)] = mbj[0] + lg2(sp.x);
+        if (query_valid<QG>(tig, 1)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1) + 1] = mbj[1] + lg2(sp.y);
       }
     }
 #pragma unroll
@@ -447,20 +490,32 @@ __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4
       uint32_t d01[4], d23[4];
       mma_u8u8_k32_from(d01, va[0], va[1], vb[0], vb[1], b0, b1, MAGIC);  // rows gid: channel cc 0, gid + 8: cc 1
       mma_u8u8_k32_from(d23, va[2], va[3], vb[2], vb[3], b0, b1, MAGIC);  // cc 2, cc 3
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        A[u][0][e] = fmaf(wj[e], isum(d01[e]), A[u][0][e]);
-        A[u][1][e] = fmaf(wj[e], isum(d01[2 + e]), A[u][1][e]);
-        A[u][2][e] = fmaf(wj[e], isum(d23[e]), A[u][2][e]);
-        A[u][3][e] = fmaf(wj[e], isum(d23[2 + e]), A[u][3][e]);
-      }
+      A[u][0] = __ffma2_rn(wj, isum2(d01[0], d01[1]), A[u][0]);
+      A[u][1] = __ffma2_rn(wj, isum2(d01[2], d01[3]), A[u][1]);
+      A[u][2] = __ffma2_rn(wj, isum2(d23[0], d23[1]), A[u][2]);
+      A[u][3] = __ffma2_rn(wj, isum2(d23[2], d23[3]), A[u][3]);
     }
-    __syncwarp();       // the pair's slot and pst are free
-    ring.issue_next();  // refill the slot with the chunk NP ahead
+    __syncwarp();  // pst is free; after a chunk's last pair its slot is too
+    if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();  // refill the slot with the chunk NP ahead
+  };
+#ifdef FBLA_NOCOMPUTE  // tuning builds only: stream the chunks without touching them
+#pragma unroll 1
+  for (int J = 0; J < SBG / 2; ++J) {
+    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;
+    if (J % CoarseShape<CB>::PPC == 0 && !ring.wait_pair(p)) return false;
+    __syncwarp();
+    if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();
   }
+#else
+#pragma unroll 1
+  for (int J = 0; J < SBG / 2; ++J) {
+    Scores sc;
+    if (!stage_a(J, sc)) return false;
+    stage_b(J, sc);
+  }
+#endif
   // fold the group into the running softmax: o += vs' A + vb' B, coarse cell midpoints folded into vb'
-#pragma unroll
-  for (int e = 0; e < 2; ++e) run.l[e] += Bs[e];
+  run.l[0] += Bs.x; run.l[1] += Bs.y;
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
@@ -468,8 +523,7 @@ __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) {
       const float vbp = fmaf(vs[cc], HOFF, vb[cc]), vsp = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc));
-#pragma unroll
-      for (int e = 0; e < 2; ++e) run.o[u][cc][e] += fmaf(vsp, A[u][cc][e], vbp * Bs[e]);
+      run.o[u][cc] = __fadd2_rn(run.o[u][cc], __ffma2_rn(splat(vsp), A[u][cc], __fmul2_rn(splat(vbp), Bs)));
     }
   }
   return true;
@@ -481,7 +535,7 @@ template <int QG> __device__ __forceinline__ void reset(Run &r) {
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) r.o[u][cc][0] = r.o[u][cc][1] = 0.f;
+    for (int cc = 0; cc < 4; ++cc) r.o[u][cc] = make_float2(0.f, 0.f);
 }
 // one partial row set: threads tig and tig ^ 2 hold the two sub-block parities of the same (channel, query) sums
 template <int QG> __device__ __forceinline__ void write_partial(float *p, const Run &r, int lane, bool correction) {
@@ -494,10 +548,12 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       float4 v;
-      v.x = r.o[u][0][e] + __shfl_xor_sync(FULL, r.o[u][0][e], 2);
-      v.y = r.o[u][1][e] + __shfl_xor_sync(FULL, r.o[u][1][e], 2);
-      v.z = r.o[u][2][e] + __shfl_xor_sync(FULL, r.o[u][2][e], 2);
-      v.w = r.o[u][3][e] + __shfl_xor_sync(FULL, r.o[u][3][e], 2);
+      const float o0 = e ? r.o[u][0].y : r.o[u][0].x, o1 = e ? r.o[u][1].y : r.o[u][1].x;
+      const float o2 = e ? r.o[u][2].y : r.o[u][2].x, o3 = e ? r.o[u][3].y : r.o[u][3].x;
+      v.x = o0 + __shfl_xor_sync(FULL, o0, 2);
+      v.y = o1 + __shfl_xor_sync(FULL, o1, 2);
+      v.z = o2 + __shfl_xor_sync(FULL, o2, 2);
+      v.w = o3 + __shfl_xor_sync(FULL, o3, 2);
       if (tig < 2 && qe < QG) *reinterpret_cast<float4 *>(row + 4 * (8 * u + gid)) = v;
     }
     if (tig < 2 && qe < QG && gid == 0) {
@@ -509,8 +565,8 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
 
 #ifdef FBLA_TIMING  // tuning builds only: cycles every warp of the coarse kernel spent, read back by fbla_k_debug_read
 __device__ long long fbla_dbg[148 * 16];
-#define FBLA_T0 const long long t0_ = clock64();
-#define FBLA_T1 if ((threadIdx.x & 31) == 0) fbla_dbg[blockIdx.x * 16 + (threadIdx.x >> 5)] = clock64() - t0_;
+#define FBLA_T0 const long long t0_ = clock64(); if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) fbla_sec_sm[(threadIdx.x >> 5) * 8 + i_] = 0;
+#define FBLA_T1 if ((threadIdx.x & 31) == 0) { fbla_dbg[blockIdx.x * 16 + (threadIdx.x >> 5)] = clock64() - t0_; for (int i_ = 0; i_ < 8; ++i_) fbla_sec[(blockIdx.x * 16 + (threadIdx.x >> 5)) * 8 + i_] = fbla_sec_sm[(threadIdx.x >> 5) * 8 + i_]; }
 #else
 #define FBLA_T0
 #define FBLA_T1
@@ -526,10 +582,16 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coa
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (blockIdx.x == 0 && threadIdx.x == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
   if (warp >= Sh::WARPS) {
+#ifdef FBLA_NOWINDOW  // tuning builds only
+    return;
+#endif
     exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, blockIdx.x * XWARPS + (warp - Sh::WARPS), gridDim.x * XWARPS);
     FBLA_T1
     return;
   }
+#ifdef FBLA_NOSTREAM  // tuning builds only
+  return;
+#endif
   StreamWarp<CB> &w = sm.w[warp];
   for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
   reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
@@ -547,7 +609,7 @@ __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coa
   const long long gw = (long long)blockIdx.x * Sh::WARPS + warp, lo = gw * per, hi = min(total, lo + per);
   if (lo >= hi) return;
   Cursor cc = locate<false>(a, hpr, lo);
-  Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(4 * (hi - lo)), nullptr, nullptr};
+  Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(Sh::CPG * (hi - lo)), nullptr, nullptr};
   ring.point();
 #pragma unroll
   for (int s = 0; s < Sh::NP; ++s) ring.issue_next();
@@ -763,11 +825,11 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
       if (lane == 0) issue(fit[s], fe, s);
     }
   Run run;  // m unused: corrections are already in units of 2^-R
-  float Ag[4][4][2], Bg[2] = {0.f, 0.f};  // the current group's sums in code units
+  float2 Ag[4][4], Bg = make_float2(0.f, 0.f);  // the current group's sums in code units, (.x, .y) = queries e = 0, 1
 #pragma unroll
   for (int u = 0; u < 4; ++u)
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) Ag[u][cc][0] = Ag[u][cc][1] = 0.f;
+    for (int cc = 0; cc < 4; ++cc) Ag[u][cc] = make_float2(0.f, 0.f);
   int pe = fe;  // entry cursor for peeking at the next item
   float4 q4[QG];
   float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
@@ -856,14 +918,12 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
       wgt[e] = on ? (cset ? -ex2(mco - Rq[e]) : ex2(mf[e] - Rq[e])) : 0.f;
     }
     {
-      float sp[2];  // sum p of the thread's two columns: a product with an all-ones A
-      {
+      const float2 wgt2 = make_float2(wgt[0], wgt[1]);
+      {  // sum p of the thread's two columns: a product with an all-ones A
         uint32_t d[4];
         mma_u8u8_k16_from(d, 0x01010101u, 0x01010101u, b0, MAGIC);
-        sp[0] = isum(d[0]); sp[1] = isum(d[1]);
+        Bg = __ffma2_rn(wgt2, isum2(d[0], d[1]), Bg);
       }
-#pragma unroll
-      for (int e = 0; e < 2; ++e) Bg[e] = fmaf(wgt[e], sp[e], Bg[e]);
       // the group's weighted code sums: full-score threads add w (2^FB h + f), coarse-score threads -w 2^FB h
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -878,12 +938,9 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
           const float ch_ = (float)(1 << FB) * v_unscale<CB>(cc), cl_ = cset ? 0.f : v_unscale<FB>(cc);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float yh = isum(cc < 2 ? h01[2 * (cc & 1) + e] : h23[2 * (cc & 1) + e]);
-            const float yl = isum(cc < 2 ? l01[2 * (cc & 1) + e] : l23[2 * (cc & 1) + e]);
-            Ag[u][cc][e] = fmaf(wgt[e], fmaf(ch_, yh, cl_ * yl), Ag[u][cc][e]);
-          }
+          const uint32_t *hh = cc < 2 ? h01 : h23, *ll = cc < 2 ? l01 : l23;
+          const float2 yh = isum2(hh[2 * (cc & 1)], hh[2 * (cc & 1) + 1]), yl = isum2(ll[2 * (cc & 1)], ll[2 * (cc & 1) + 1]);
+          Ag[u][cc] = __ffma2_rn(wgt2, __ffma2_rn(splat(ch_), yh, __fmul2_rn(splat(cl_), yl)), Ag[u][cc]);
         }
       }
       // the group's last item of this warp: apply the V affine once (coarse cells at their midpoint)
@@ -893,8 +950,7 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
         last = pe / a.nslices != vh || (nx >> 4) / SBG != sb / SBG;
       }
       if (last) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) { run.l[e] += Bg[e]; }
+        run.l[0] += Bg.x; run.l[1] += Bg.y;
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
@@ -902,14 +958,11 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
             const float vbx = cset ? fmaf(vs[cc], HOFF, vb[cc]) : vb[cc];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              run.o[u][cc][e] += fmaf(vs[cc], Ag[u][cc][e], vbx * Bg[e]);
-              Ag[u][cc][e] = 0.f;
-            }
+            run.o[u][cc] = __fadd2_rn(run.o[u][cc], __ffma2_rn(splat(vs[cc]), Ag[u][cc], __fmul2_rn(splat(vbx), Bg)));
+            Ag[u][cc] = make_float2(0.f, 0.f);
           }
         }
-        Bg[0] = Bg[1] = 0.f;
+        Bg = make_float2(0.f, 0.f);
       }
     }
     __syncwarp();
@@ -1062,6 +1115,11 @@ extern "C" cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out
 
 #ifdef FBLA_TIMING
 extern "C" cudaError_t fbla_k_debug_read(long long *host) { return cudaMemcpyFromSymbol(host, fbla::fbla_dbg, sizeof(fbla::fbla_dbg)); }
+extern "C" cudaError_t fbla_k_debug_sections(long long *host, int clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(host, fbla::fbla_sec, sizeof(fbla::fbla_sec));
+  if (clear) { static long long zero[148 * 16 * 8]; cudaMemcpyToSymbol(fbla::fbla_sec, zero, sizeof(zero)); }
+  return e;
+}
 #endif
 
 extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {

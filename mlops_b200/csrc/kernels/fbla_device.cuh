@@ -32,6 +32,12 @@ __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32
 __device__ __forceinline__ float lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float isum(uint32_t acc) { return __uint_as_float(acc) - MAGICF; }  // exact for |sum| < 2^22
 
+// packed pairs of FP32 (FADD2 / FMUL2 / FFMA2 of sm_100: two lanes of arithmetic per instruction)
+__device__ __forceinline__ float2 isum2(uint32_t a, uint32_t b) {
+  return __fadd2_rn(make_float2(__uint_as_float(a), __uint_as_float(b)), make_float2(-MAGICF, -MAGICF));
+}
+__device__ __forceinline__ float2 splat(float x) { return make_float2(x, x); }
+
 __device__ __forceinline__ float warp_max(float x) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) x = fmaxf(x, __shfl_xor_sync(FULL, x, o));

@@ -56,8 +56,9 @@ template <int BITS> __device__ __forceinline__ void qk_tile(const uint8_t *rec, 
     mma_u8s8_k32_from(hi, a & H, a8 & H, b & H, b8 & H, B[2], B[3], MAGIC);
     mma_u8s8_k32(lo, c & L, c8 & L, d & L, d8 & L, B[4], B[5]);
     mma_u8s8_k32(hi, c & H, c8 & H, d & H, d8 & H, B[6], B[7]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = fmaf(isum(hi[i]), 1.f / 16, isum(lo[i]));
+    const float2 x01 = __ffma2_rn(isum2(hi[0], hi[1]), splat(1.f / 16), isum2(lo[0], lo[1]));
+    const float2 x23 = __ffma2_rn(isum2(hi[2], hi[3]), splat(1.f / 16), isum2(lo[2], lo[3]));
+    x[0] = x01.x; x[1] = x01.y; x[2] = x23.x; x[3] = x23.y;
   } else if (BITS == 2) {
     const uint32_t a = lds32(p0), a8 = lds32(p1), c = lds32(p0 + 256), c8 = lds32(p1 + 256);
     uint32_t acc[4][4];
@@ -81,8 +82,9 @@ template <int BITS> __device__ __forceinline__ void qk_tile(const uint8_t *rec, 
     mma_u8s8_k32(lo, ((a >> 6) & T2) | ((e >> sh) & T1), ((a8 >> 6) & T2) | ((e8 >> sh) & T1),
                  ((c >> 6) & T2) | ((f >> sh) & T1), ((c8 >> 6) & T2) | ((f8 >> sh) & T1), B[4], B[5]);
     mma_u8s8_k32(lo, (e >> se) & L, (e8 >> se) & L, (f >> se) & L, (f8 >> se) & L, B[6], B[7]);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) x[i] = fmaf(isum(mid[i]), 1.f / 8, isum(lo[i]));
+    const float2 x01 = __ffma2_rn(isum2(mid[0], mid[1]), splat(1.f / 8), isum2(lo[0], lo[1]));
+    const float2 x23 = __ffma2_rn(isum2(mid[2], mid[3]), splat(1.f / 8), isum2(lo[2], lo[3]));
+    x[0] = x01.x; x[1] = x01.y; x[2] = x23.x; x[3] = x23.y;
   }
 }
 
