@@ -82,7 +82,14 @@ typedef struct {
 // close_blocks: grid x of the close pass (groups the chunk can close); 0 skips it
 cudaError_t fbla_k_close_launch(const fbla_k_prefill *a, int close_blocks, cudaStream_t stream);
 cudaError_t fbla_k_finish_launch(const fbla_k_prefill *a, cudaStream_t stream);
+// attention of the chunk's rows: the tensor-core kernel (tcgen05, 128 rows per CTA), or -- for chunks of fewer than
+// FBLA_K_TC_MIN_ROWS rows, or when the environment variable MLOPS_FBLA_PREFILL=rows asks for it -- one warp per row
 cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);
+cudaError_t fbla_k_attend_rows_launch(const fbla_k_prefill *a, cudaStream_t stream);
+cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream);
+// 1 if a bounded wait of the tensor-core kernel gave up since the last call (and clears it), 0 if not, -1 on a CUDA error
+int fbla_k_attend_tc_status(void);
+#define FBLA_K_TC_MIN_ROWS 64
 
 #ifdef __cplusplus
 }

@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(256) attend_rows_kernel(const fbla_k_prefill a
 
 }  // namespace fbla
 
-extern "C" cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream) {
+extern "C" cudaError_t fbla_k_attend_rows_launch(const fbla_k_prefill *a, cudaStream_t stream) {
   const int qg = a->q_heads / a->kv_heads;
   const dim3 grid((a->count * qg + 7) / 8, a->batch * a->kv_heads);
   if (a->cb == 3) fbla::attend_rows_kernel<3, 3><<<grid, 256, 0, stream>>>(*a);

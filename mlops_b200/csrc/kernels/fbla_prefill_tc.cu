@@ -1,0 +1,467 @@
+// Causal prefill attention over the compressed cache on Blackwell tensor cores: tcgen05.mma with TMEM accumulators.
+//
+// Semantics: the reference's DP4A prefill (attention/fbla/src/fbla_prefill.cuh:389-705) -- the row at position p attends
+// to 0..p: group 0 (sink) and its own group in BF16, closed groups 1..own-1 through their full 6-bit codes with the
+// per-(row, group) int8 qhat, 16-token integer P blocks p = round(255 * 2^(s - max_block)) everywhere.
+//
+// One CTA = 128 query rows of one KV head (row r = position r / qg, query r % qg) x a sequence of "passes", one per
+// 128-token group the rows attend to. Per pass, two tensor-core products with FP32 accumulators in tensor memory:
+//   S[128 rows x 128 tokens]  = Qop[rows x 128 ch] . Kop[tokens x 128 ch]^T
+//   O[128 rows x 128 ch]     += P'[rows x 128 tokens] . V'[ch x 128 tokens]^T
+// Closed group: Qop = qhat (integers in [-127, 127]) and Kop = the 6-bit codes, both as FP16 -- products and the FP32
+// sums (< 2^24) are exact, so S is the reference's integer dot product; BF16 group: Qop = q, Kop = k in BF16 (exact
+// products, FP32 sums). P' = fp16(w_j p_t): the integer P block times its block weight 2^(m_j - m_row); V' =
+// fp16(base + step * code) (closed) or fp16(v) (BF16), so O accumulates across ALL passes in tensor memory and is read
+// once, at the end. The two FP16 roundings (relative 2^-11, zero mean) are the only deviations from the reference's
+// arithmetic; they stay far inside the 2e-3 output tolerance (measured ~1e-4).
+//
+// Warps 0-3: one thread per row (tensor-memory lane): qhat of the pass, softmax of S, P' into shared memory, output.
+// Warps 4-7: operands: unpack the group's records (bulk-copied raw into shared memory) into the K / V' tiles.
+// Warp 8: allocates tensor memory; its lane 0 issues the bulk copies and the products, which complete on mbarriers.
+// Operand tiles are K-major with the 128-byte swizzle (8-row x 128-byte atoms, 16-byte chunk c of row r at c ^ (r % 8)).
+// Every wait is bounded: on a timeout the thread raises a flag, everybody drains, tensor memory is freed, the kernel
+// returns and the host sees fbla_k_attend_tc_status() != 0.
+#include "fbla_device.cuh"
+#include "fbla_kernels.h"
+#include <cuda_fp16.h>
+#include <stdlib.h>
+#include <string.h>
+
+namespace fbla {
+namespace tc {
+
+constexpr int ROWS = 128;
+constexpr int SLAB = ROWS * 128;          // bytes of one K slab (128 rows x 128 bytes): 64 FP16 / BF16 of the K extent
+constexpr int TILE = 2 * SLAB;            // a [128 x 128] 16-bit operand tile: 32 KiB
+constexpr int RAW = 8 * 2048 + 8 * 1536;  // largest raw group (coarse 8 x 2048 + fine 8 x 1536 covers both formats)
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ int g_status = 0;  // nonzero: a bounded wait gave up in some launch since the last read
+
+struct __align__(1024) Smem {
+  uint8_t q[TILE];    // Qop of BF16 passes: the rows' q, BF16
+  uint8_t qh[TILE];   // Qop of closed passes: qhat, FP16
+  uint8_t k[TILE];    // Kop
+  uint8_t v[TILE];    // V'
+  uint8_t p[TILE];    // P'
+  uint8_t raw[RAW];   // the group's coarse records, then its fine records
+  uint8_t meta[1024];
+  uint64_t bar_raw, bar_kv, bar_q, bar_s, bar_p, bar_o;
+  uint32_t tmem_base;
+  int abort;
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t smem_desc(const void *tile_base, int slab, int kstep) {  // K-major, 128-byte swizzle
+  const uint32_t addr = smem_u32(tile_base) + slab * SLAB + kstep * 32;
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+constexpr uint32_t IDESC_F16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);           // D FP32, A / B FP16, M 128, N 128
+constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);                                // A / B BF16
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, bool accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\ttcgen05.wait::ld.sync.aligned;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+                 "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+                 "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait that also gives up when another thread has raised the abort flag
+__device__ __forceinline__ bool wait(Smem &sm, uint64_t *bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *reinterpret_cast<volatile int *>(&sm.abort)) return false;
+  }
+  *reinterpret_cast<volatile int *>(&sm.abort) = 1;
+  atomicExch(&g_status, 1);
+  return false;
+}
+
+// byte address of the 16-byte chunk holding K-extent element k0 (a multiple of 8) of tile row r
+__device__ __forceinline__ uint8_t *chunk_at(uint8_t *tile, int r, int k0) {
+  const int slab = k0 >> 6, c = (k0 & 63) >> 3;
+  return tile + slab * SLAB + r * 128 + ((c ^ (r & 7)) << 4);
+}
+
+// ---- record unpacking (the slot maps of include/mlops_fbla.h) --------------------------------------------------------------
+template <int BITS> __device__ __forceinline__ uint32_t slot_value(const uint32_t *W, int s) {  // 4 codes, one per byte, unscaled
+  if (BITS == 4) return s < 8 ? W[s] & 0x0f0f0f0fu : (W[s - 8] >> 4) & 0x0f0f0f0fu;
+  if (BITS == 2) return (W[s & 3] >> (2 * (s >> 2))) & 0x03030303u;
+  if (s < 6) return W[s] & 0x07070707u;
+  if (s < 12) return (W[s - 6] >> 3) & 0x07070707u;
+  const int r = s - 12;
+  return ((W[r] >> 6) & 0x03030303u) | ((W[4 + (r >> 1)] >> (4 + (r & 1))) & 0x04040404u);
+}
+__host__ __device__ constexpr int v_slot_of(int bits, int cc, int quad) {
+  return bits == 4 ? (cc < 2 ? 2 * quad + cc : 8 + 2 * quad + (cc - 2))
+       : bits == 2 ? 4 * cc + quad
+       : cc == 0 ? quad : cc == 1 ? 6 + quad : cc == 2 ? (quad < 2 ? 4 + quad : 8 + quad) : 12 + quad;
+}
+template <int BITS> __device__ __forceinline__ void lane_words(const uint8_t *rec, int tensor, int lane, uint32_t *W) {
+#pragma unroll
+  for (int w = 0; w < 2 * BITS; ++w) W[w] = lds32(rec + word_offset(BITS, tensor, lane, w));
+}
+// four small unsigned integers (bytes of x, each < 1024) as two packed FP16 pairs: 0x6400 | b is 1024 + b
+__device__ __forceinline__ uint2 bytes_to_half4(uint32_t x) {
+  const uint32_t lo = __byte_perm(x, 0x64646464u, 0x7170), hi = __byte_perm(x, 0x64646464u, 0x7372);  // (b1 | 0x64 << 8) << 16 | b0 | 0x64 << 8
+  const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6400));
+  const __half2 a = __hsub2(*reinterpret_cast<const __half2 *>(&lo), bias), b = __hsub2(*reinterpret_cast<const __half2 *>(&hi), bias);
+  return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+template <int CB, int FB>
+__global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill a) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, b = bh / a.kv_heads, kh = bh - b * a.kv_heads, qg = a.q_heads / a.kv_heads;
+  const int n0 = (a.length ? a.length[a.lstride ? b : 0] : 0) + a.n0;
+  const int count = a.dcount ? *a.dcount : a.count, n1 = n0 + count;
+  const int rows = count * qg, r0 = blockIdx.x * ROWS;
+  if (r0 >= rows) return;  // (CTA-uniform)
+  const int last_row = min(r0 + ROWS, rows) - 1;
+  const int own_min = (n0 + r0 / qg) / G, own_max = (n0 + last_row / qg) / G;
+  // passes: closed groups 1 .. own_max - 1, then the BF16 groups 0, own_min (if > 0), own_max (if another)
+  const int n_closed = max(own_max - 1, 0);
+  const int n_bf = 1 + (own_min > 0) + (own_max != own_min);
+  const int n_pass = n_closed + n_bf;
+  auto pass_group = [&](int n, bool &closed) {
+    closed = n < n_closed;
+    if (closed) return 1 + n;
+    const int j = n - n_closed;
+    return j == 0 ? 0 : (j == 1 && own_min > 0) ? own_min : own_max;
+  };
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_kv, 128); mbar_init(&sm.bar_q, 128);
+    mbar_init(&sm.bar_s, 1); mbar_init(&sm.bar_p, 128); mbar_init(&sm.bar_o, 1);
+    sm.abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == 8) {  // 256 columns of tensor memory: S at 0, O at 128
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base, tmem_s = tmem, tmem_o = tmem + 128;
+  const size_t head = (size_t)bh * a.hs, eh = (size_t)bh * G * D, ih = (size_t)bh * a.count * D;
+  // the BF16 row of position tp: the chunk, the sink window, or the window of the group that was open before the chunk
+  auto token_row = [&](int tp, const uint16_t *in, const uint16_t *sink, const uint16_t *open) -> const uint16_t * {
+    return tp >= n0 ? in + ih + (size_t)(tp - n0) * D : tp < G ? sink + eh + (size_t)tp * D : open + eh + (size_t)(tp - (n0 - 1) / G * G) * D;
+  };
+
+  if (warp == 8) {
+    // ================= issuer: bulk copies of the raw groups, the products =================
+    if (lane == 0) {
+      auto fetch = [&](int g) {
+        const size_t unit = head + (size_t)g * a.gs;
+        mbar_expect_tx(&sm.bar_raw, SBG * (RC + RF) + 1024);
+        bulk_g2s(sm.raw, a.c.coarse + unit * SBG * RC, SBG * RC, &sm.bar_raw);
+        bulk_g2s(sm.raw + SBG * RC, a.c.fine + unit * SBG * RF, SBG * RF, &sm.bar_raw);
+        bulk_g2s(sm.meta, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &sm.bar_raw);
+      };
+      if (n_closed > 0) fetch(1);
+      for (int n = 0; n < n_pass; ++n) {
+        bool closed;
+        pass_group(n, closed);
+        if (!wait(sm, &sm.bar_kv, n & 1) || !wait(sm, &sm.bar_q, n & 1)) break;
+        if (n + 1 < n_closed) fetch(2 + n);  // the raw buffer has been consumed: the next closed group's records
+        tc_fence_after();
+        const uint8_t *qop = closed ? sm.qh : sm.q;
+        const uint32_t idesc = closed ? IDESC_F16 : IDESC_BF16;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_f16(tmem_s, smem_desc(qop, kk >> 2, kk & 3), smem_desc(sm.k, kk >> 2, kk & 3), idesc, kk > 0);
+        mma_commit(&sm.bar_s);
+        if (!wait(sm, &sm.bar_p, n & 1)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_f16(tmem_o, smem_desc(sm.p, kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
+        mma_commit(&sm.bar_o);
+      }
+    }
+  } else if (warp >= 4) {
+    // ================= operand producers =================
+    const int pt = tid - 128;  // 0 .. 127
+    int raw_uses = 0;
+    for (int n = 0; n < n_pass; ++n) {
+      bool closed;
+      const int g = pass_group(n, closed);
+      if (closed && !wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
+      if (n > 0 && !wait(sm, &sm.bar_o, (n - 1) & 1)) break;  // the previous pass's products have read the K and V' tiles
+      if (closed) {
+        // (record j, lane l) pairs: pt handles j = pt / 32 and j + 4, lane l = pt % 32, of K and of V
+        const int l = pt & 31;
+#pragma unroll 1
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = (pt >> 5) + 4 * jj;
+          const uint8_t *rc = sm.raw + j * RC, *rf = sm.raw + SBG * RC + j * RF;
+          uint32_t Wc[2 * CB], Wf[2 * FB];
+          // K: token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
+          lane_words<CB>(rc, 0, l, Wc);
+          lane_words<FB>(rf, 0, l, Wf);
+          const int tok = 16 * j + (l & 15);
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2) {
+            const uint2 x = bytes_to_half4((slot_value<CB>(Wc, 2 * s2) << FB) | slot_value<FB>(Wf, 2 * s2));
+            const uint2 y = bytes_to_half4((slot_value<CB>(Wc, 2 * s2 + 1) << FB) | slot_value<FB>(Wf, 2 * s2 + 1));
+            *reinterpret_cast<uint4 *>(chunk_at(sm.k, tok, 64 * (l >> 4) + 8 * s2)) = make_uint4(x.x, x.y, y.x, y.y);
+          }
+          // V': channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code
+          lane_words<CB>(rc, 1, l, Wc);
+          lane_words<FB>(rf, 1, l, Wf);
+          const uint4 vm = lds128(sm.meta + 512 + 16 * l);
+          const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t h[8];
+#pragma unroll
+            for (int quad = 0; quad < 4; ++quad) {
+              const uint32_t code = (slot_value<CB>(Wc, v_slot_of(CB, cc, quad)) << FB) | slot_value<FB>(Wf, v_slot_of(FB, cc, quad));
+              float f[4];
+#pragma unroll
+              for (int x = 0; x < 4; ++x) f[x] = fmaf(vs[cc], __uint_as_float(0x4B000000u | ((code >> (8 * x)) & 255u)) - 8388608.f, vb[cc]);
+              h[2 * quad] = pack_half2(f[0], f[1]); h[2 * quad + 1] = pack_half2(f[2], f[3]);
+            }
+            uint8_t *dst = chunk_at(sm.v, 4 * l + cc, 16 * j);
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(chunk_at(sm.v, 4 * l + cc, 16 * j + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
+          }
+        }
+      } else {
+        // BF16 group g: K rows as they are; V rows converted to FP16 and transposed (tokens along the K extent)
+        for (int e = pt; e < G * 16; e += 128) {
+          const int tk = e >> 4, c = e & 15, tp = g * G + tk;
+          const bool live = tp < n1;
+          const uint4 kw = live ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.k, a.c.sink_k, a.c.open_k)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4 *>(chunk_at(sm.k, tk, 8 * c)) = kw;
+          const uint4 vw = live ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.v, a.c.sink_v, a.c.open_v)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const float f = (x & 1) ? bf_hi(w4[x >> 1]) : bf_lo(w4[x >> 1]);
+            *reinterpret_cast<__half *>(chunk_at(sm.v, 8 * c + x, tk & ~7) + 2 * (tk & 7)) = __float2half_rn(f);
+          }
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_kv);
+    }
+  } else {
+    // ================= row threads: qhat, softmax, P', output =================
+    const int r = tid, R = r0 + r;
+    const bool valid = R < rows;
+    const int i = valid ? R / qg : 0, hq = kh * qg + (valid ? R - i * qg : 0), pos = n0 + i, own = pos / G;
+    // the row's q into the BF16 Q tile (rows past the end: zeros)
+    {
+      const uint4 *qp = reinterpret_cast<const uint4 *>(a.q + ((size_t)(b * a.q_heads + hq) * a.count + i) * D);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4 *>(chunk_at(sm.q, r, 8 * c)) = valid ? __ldg(qp + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    int raw_uses = 0;
+    bool ok = true;
+    for (int n = 0; n < n_pass && ok; ++n) {
+      bool closed;
+      const int g = pass_group(n, closed);
+      const bool include = valid && (closed ? g < own : (g == 0 || g == own));
+      float sq = 0.f, qb = 0.f;
+      if (closed) {
+        if (!__all_sync(FULL, wait(sm, &sm.bar_raw, raw_uses++ & 1))) { ok = false; break; }
+        // qhat of the row for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r); written as FP16
+        float amax = 0.f, dot = 0.f;
+#pragma unroll 4
+        for (int c = 0; c < 16; ++c) {
+          const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(sm.q, r, 8 * c));
+          const uint4 m0 = lds128(sm.meta + 32 * c), m1 = lds128(sm.meta + 32 * c + 16);  // channels 8 c .. + 3 and + 4 .. + 7: 4 bases, 4 steps each
+          const float qf[8] = {bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y), bf_lo(qw.z), bf_hi(qw.z), bf_lo(qw.w), bf_hi(qw.w)};
+          const float kb[8] = {bf_lo(m0.x), bf_hi(m0.x), bf_lo(m0.y), bf_hi(m0.y), bf_lo(m1.x), bf_hi(m1.x), bf_lo(m1.y), bf_hi(m1.y)};
+          const float ks[8] = {bf_lo(m0.z), bf_hi(m0.z), bf_lo(m0.w), bf_hi(m0.w), bf_lo(m1.z), bf_hi(m1.z), bf_lo(m1.w), bf_hi(m1.w)};
+#pragma unroll
+          for (int x = 0; x < 8; ++x) { amax = fmaxf(amax, fabsf(__fmul_rn(qf[x], ks[x]))); dot = fmaf(qf[x], kb[x], dot); }
+        }
+        float rc;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
+        rc = fmaf(fmaf(-amax, rc, 1.f), rc, rc);
+        const float q0 = __fmul_rn(127.f, rc), rr = amax > 0.f ? fmaf(fmaf(-amax, q0, 127.f), rc, q0) : 0.f;
+        sq = __fmul_rn(amax, __fmul_rn(a.sl, 1.f / 127.f));
+        qb = __fmul_rn(dot, a.sl);
+#pragma unroll 4
+        for (int c = 0; c < 16; ++c) {
+          const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(sm.q, r, 8 * c));
+          const uint4 m0 = lds128(sm.meta + 32 * c), m1 = lds128(sm.meta + 32 * c + 16);
+          const float qf[8] = {bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y), bf_lo(qw.z), bf_hi(qw.z), bf_lo(qw.w), bf_hi(qw.w)};
+          const float ks[8] = {bf_lo(m0.z), bf_hi(m0.z), bf_lo(m0.w), bf_hi(m0.w), bf_lo(m1.z), bf_hi(m1.z), bf_lo(m1.w), bf_hi(m1.w)};
+          uint32_t h[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {  // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
+            const float t0 = fmaf(__fmul_rn(qf[2 * x], ks[2 * x]), rr, MAGICF) - MAGICF, t1 = fmaf(__fmul_rn(qf[2 * x + 1], ks[2 * x + 1]), rr, MAGICF) - MAGICF;
+            h[x] = pack_half2(t0, t1);
+          }
+          *reinterpret_cast<uint4 *>(chunk_at(sm.qh, r, 8 * c)) = make_uint4(h[0], h[1], h[2], h[3]);
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_q);
+      if (!__all_sync(FULL, wait(sm, &sm.bar_s, n & 1))) { ok = false; break; }
+      if (n > 0 && !__all_sync(FULL, wait(sm, &sm.bar_o, (n - 1) & 1))) { ok = false; break; }  // P' tile free, O stable
+      tc_fence_after();
+      // softmax of the row over the pass's 128 tokens, by 16-token blocks; P' = fp16(2^(m_block - m_row) p)
+      const float sl = a.sl;
+#pragma unroll 1
+      for (int cq = 0; cq < 4; ++cq) {  // 32 columns at a time
+        uint32_t x[32];
+        tmem_ld32(tmem_s + lane_base + 32 * cq, x);
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {  // the two 16-token blocks of the 32 columns
+          const int t0 = 32 * cq + 16 * hb;
+          float s[16], mb = -INFINITY;
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const float xv = __uint_as_float(x[16 * hb + t]);
+            float sv = closed ? fmaf(sq, xv, qb) : __fmul_rn(xv, sl);
+            if (!include || (!closed && g * G + t0 + t > pos)) sv = -INFINITY;
+            s[t] = sv;
+            mb = fmaxf(mb, sv);
+          }
+          // the row's running maximum moves only when a block exceeds it by more than 2^8 (rare): its sums, its O row in
+          // tensor memory and the P' chunks already written in this pass are rescaled. Tensor-memory accesses are
+          // warp-wide, so the whole warp takes part (rows that do not move scale by 1).
+          const bool need = mb > m_run + 8.f;
+          const float al = need ? ex2(m_run - mb) : 1.f;  // 0 on the row's first block
+          if (__any_sync(FULL, need)) {
+            if (n > 0) {
+#pragma unroll 1
+              for (int oc = 0; oc < 4; ++oc) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_base + 32 * oc, o);
+#pragma unroll
+                for (int z = 0; z < 32; ++z) o[z] = __float_as_uint(__uint_as_float(o[z]) * al);
+                tmem_st32(tmem_o + lane_base + 32 * oc, o);
+              }
+            }
+            if (need) {
+              l_run *= al;
+              for (int tb = 0; tb < t0; tb += 8) {
+                uint4 *pc = reinterpret_cast<uint4 *>(chunk_at(sm.p, r, tb));
+                uint4 w = *pc;
+                uint32_t *ww = reinterpret_cast<uint32_t *>(&w);
+#pragma unroll
+                for (int z = 0; z < 4; ++z) {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ww[z]));
+                  ww[z] = pack_half2(f.x * al, f.y * al);
+                }
+                *pc = w;
+              }
+              m_run = mb;
+            }
+          }
+          uint32_t h[8];
+          if (mb == -INFINITY) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) h[t] = 0u;
+          } else {
+            const float w = ex2(mb - m_run);
+            float sp = 0.f, pf[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) { pf[t] = fmaf(ex2(s[t] - mb), 255.f, MAGICF) - MAGICF; sp += pf[t]; }
+            l_run = fmaf(w, sp, l_run);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) h[t] = pack_half2(w * pf[2 * t], w * pf[2 * t + 1]);
+          }
+          *reinterpret_cast<uint4 *>(chunk_at(sm.p, r, t0)) = make_uint4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<uint4 *>(chunk_at(sm.p, r, t0 + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
+        }
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&sm.bar_p);
+    }
+    if (ok && __all_sync(FULL, wait(sm, &sm.bar_o, (n_pass - 1) & 1))) {
+      tc_fence_after();
+      const float inv = 1.f / l_run;
+      uint16_t *orow = a.out + (size_t)(b * a.q_heads + hq) * a.out_hs + (size_t)i * a.out_ts;
+#pragma unroll 1
+      for (int oc = 0; oc < 4; ++oc) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_base + 32 * oc, o);
+        if (valid) {
+#pragma unroll
+          for (int z = 0; z < 4; ++z) {
+            uint32_t w[4];
+#pragma unroll
+            for (int y = 0; y < 4; ++y)
+              w[y] = f32_to_bf16(__uint_as_float(o[8 * z + 2 * y]) * inv) | (uint32_t)f32_to_bf16(__uint_as_float(o[8 * z + 2 * y + 1]) * inv) << 16;
+            reinterpret_cast<uint4 *>(orow + 32 * oc)[z] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+  }
+}
+
+}  // namespace tc
+}  // namespace fbla
+
+extern "C" int fbla_k_attend_tc_status(void) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, fbla::tc::g_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(fbla::tc::g_status, &zero, sizeof(int));
+  return v;
+}
+
+extern "C" cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream) {
+  using namespace fbla::tc;
+  const int qg = a->q_heads / a->kv_heads;
+  const dim3 grid((a->count * qg + ROWS - 1) / ROWS, a->batch * a->kv_heads);
+  const size_t smem = sizeof(Smem) + 1024;
+  static thread_local int configured[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attend_tc_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attend_tc_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) configured[dev] = 1;
+  }
+  if (a->cb == 3) attend_tc_kernel<3, 3><<<grid, 288, smem, stream>>>(*a);
+  else attend_tc_kernel<4, 2><<<grid, 288, smem, stream>>>(*a);
+  return cudaGetLastError();
+}
+
+extern "C" cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream) {
+  static const bool rows_only = [] { const char *e = getenv("MLOPS_FBLA_PREFILL"); return e && !strcmp(e, "rows"); }();
+  const int rows = a->count * (a->q_heads / a->kv_heads);
+  return rows_only || rows < FBLA_K_TC_MIN_ROWS ? fbla_k_attend_rows_launch(a, stream) : fbla_k_attend_tc_launch(a, stream);
+}

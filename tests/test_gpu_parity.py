@@ -5,6 +5,8 @@ The case list follows the reference's own matrix (attention/fbla/tests/test_fbla
 attention/python/tests/test_attention.py)."""
 import os
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -209,6 +211,8 @@ def test_prefill_matches_oracle(ours, oracle, mode, B, QH, KH, N, chunks, seed):
         gu.check_close(got[:, :, idx], want[:, :, idx], f"{mode} prefill chunk at {t}")
         gu.assert_cache_equal(c, o, f"{mode} after chunk at {t}")
         t += n
+    # no bounded wait of the tensor-core kernel gave up
+    assert ctypes.CDLL(gu.OURS).fbla_k_attend_tc_status() == 0
 
 
 @pytest.mark.parametrize("mode", MODES)
