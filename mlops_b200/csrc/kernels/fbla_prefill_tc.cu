@@ -4,8 +4,9 @@
 // to 0..p: group 0 (sink) and its own group in BF16, closed groups 1..own-1 through their full 6-bit codes with the
 // per-(row, group) int8 qhat, 16-token integer P blocks p = round(255 * 2^(s - max_block)) everywhere.
 //
-// One CTA = 128 query rows of one KV head (row r = position r / qg, query r % qg) x a sequence of "passes", one per
-// 128-token group the rows attend to. Per pass, two tensor-core products with FP32 accumulators in tensor memory:
+// One CTA = two tiles of 128 query rows of one KV head (row r = position r / qg, query r % qg) x a sequence of "passes",
+// one per 128-token group the rows attend to. Per pass and tile, two tensor-core products with FP32 accumulators in
+// tensor memory:
 //   S[128 rows x 128 tokens]  = Qop[rows x 128 ch] . Kop[tokens x 128 ch]^T
 //   O[128 rows x 128 ch]     += P'[rows x 128 tokens] . V'[ch x 128 tokens]^T
 // Closed group: Qop = qhat (integers in [-127, 127]) and Kop = the 6-bit codes, both as FP16 -- products and the FP32
@@ -13,12 +14,16 @@
 // products, FP32 sums). P' = fp16(w_j p_t): the integer P block times its block weight 2^(m_j - m_row); V' =
 // fp16(base + step * code) (closed) or fp16(v) (BF16), so O accumulates across ALL passes in tensor memory and is read
 // once, at the end. The two FP16 roundings (relative 2^-11, zero mean) are the only deviations from the reference's
-// arithmetic; they stay far inside the 2e-3 output tolerance (measured ~1e-4).
+// arithmetic; they stay far inside the 2e-3 output tolerance.
 //
-// Warps 0-3: one thread per row (tensor-memory lane): qhat of the pass, softmax of S, P' into shared memory, output.
-// Warps 4-7: operands: unpack the group's records (bulk-copied raw into shared memory) into the K / V' tiles.
-// Warp 8: allocates tensor memory; its lane 0 issues the bulk copies and the products, which complete on mbarriers.
-// Operand tiles are K-major with the 128-byte swizzle (8-row x 128-byte atoms, 16-byte chunk c of row r at c ^ (r % 8)).
+// Warps 0-3 / 4-7: tile 0 / 1, one thread per row (tensor-memory lane): qhat of the pass, softmax of S, P', output.
+// Warps 8-11: operands, shared by both tiles: unpack the group's records (bulk-copied raw into shared memory) into the
+// Kop / V' tiles. Warp 12: allocates tensor memory; its lane 0 issues the bulk copies and the products, which complete
+// on mbarriers. The two tiles run the same passes half a pass apart, so one tile's products overlap the other's
+// arithmetic. P' is written over qhat (dead once S is complete). Operand tiles are K-major with the 128-byte swizzle
+// (8-row x 128-byte atoms, 16-byte chunk c of row r at c ^ (r % 8)).
+// What bounds it: per (row, group) the reference's semantics need ~130 exp2 and the requantisation of the row's 128
+// query channels on the CUDA cores; the tensor-core share of a pass is about as long as its exp2 share alone.
 // Every wait is bounded: on a timeout the thread raises a flag, everybody drains, tensor memory is freed, the kernel
 // returns and the host sees fbla_k_attend_tc_status() != 0.
 #include "fbla_device.cuh"
@@ -30,7 +35,9 @@
 namespace fbla {
 namespace tc {
 
-constexpr int ROWS = 128;
+constexpr int ROWS = 128;                 // rows of a tile
+constexpr int CTA_ROWS = 2 * ROWS;
+constexpr int THREADS = 13 * 32;
 constexpr int SLAB = ROWS * 128;          // bytes of one K slab (128 rows x 128 bytes): 64 FP16 / BF16 of the K extent
 constexpr int TILE = 2 * SLAB;            // a [128 x 128] 16-bit operand tile: 32 KiB
 constexpr int RAW = 8 * 2048 + 8 * 1536;  // largest raw group (coarse 8 x 2048 + fine 8 x 1536 covers both formats)
@@ -39,14 +46,14 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 __device__ int g_status = 0;  // nonzero: a bounded wait gave up in some launch since the last read
 
 struct __align__(1024) Smem {
-  uint8_t q[TILE];    // Qop of BF16 passes: the rows' q, BF16
-  uint8_t qh[TILE];   // Qop of closed passes: qhat, FP16
-  uint8_t k[TILE];    // Kop
-  uint8_t v[TILE];    // V'
-  uint8_t p[TILE];    // P'
-  uint8_t raw[RAW];   // the group's coarse records, then its fine records
+  uint8_t q[2][TILE];   // Qop of BF16 passes: the rows' q, BF16
+  uint8_t qp[2][TILE];  // Qop of closed passes (qhat, FP16), then P' of the same pass
+  uint8_t k[TILE];      // Kop
+  uint8_t v[TILE];      // V'
+  uint8_t raw[RAW];     // the group's coarse records, then its fine records
   uint8_t meta[1024];
-  uint64_t bar_raw, bar_kv, bar_q, bar_s, bar_p, bar_o;
+  float ks[128], kb[128];  // the group's K steps and bases as FP32
+  uint64_t bar_raw, bar_mf, bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -131,8 +138,15 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   return *reinterpret_cast<const uint32_t *>(&h);
 }
 
+// FP16 pairs (code as FP16) * step + base, one rounding
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t code2, __half2 step, __half2 base) {
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&code2), step, base);
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+__device__ __forceinline__ float2 bf2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
+
 template <int CB, int FB>
-__global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill a) {
+__global__ void __launch_bounds__(THREADS, 1) attend_tc_kernel(const fbla_k_prefill a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
@@ -140,42 +154,39 @@ __global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill 
   const int bh = blockIdx.y, b = bh / a.kv_heads, kh = bh - b * a.kv_heads, qg = a.q_heads / a.kv_heads;
   const int n0 = (a.length ? a.length[a.lstride ? b : 0] : 0) + a.n0;
   const int count = a.dcount ? *a.dcount : a.count, n1 = n0 + count;
-  const int rows = count * qg, r0 = blockIdx.x * ROWS;
+  const int rows = count * qg, r0 = blockIdx.x * CTA_ROWS;
   if (r0 >= rows) return;  // (CTA-uniform)
-  const int last_row = min(r0 + ROWS, rows) - 1;
+  const int last_row = min(r0 + CTA_ROWS, rows) - 1;
   const int own_min = (n0 + r0 / qg) / G, own_max = (n0 + last_row / qg) / G;
-  // passes: closed groups 1 .. own_max - 1, then the BF16 groups 0, own_min (if > 0), own_max (if another)
-  const int n_closed = max(own_max - 1, 0);
-  const int n_bf = 1 + (own_min > 0) + (own_max != own_min);
-  const int n_pass = n_closed + n_bf;
+  // passes: closed groups 1 .. own_max - 1, then the BF16 groups: 0 and the rows' own groups
+  const int n_closed = max(own_max - 1, 0), own_lo = max(own_min, 1);
+  const int n_pass = n_closed + 1 + max(own_max - own_lo + 1, 0);
   auto pass_group = [&](int n, bool &closed) {
     closed = n < n_closed;
-    if (closed) return 1 + n;
-    const int j = n - n_closed;
-    return j == 0 ? 0 : (j == 1 && own_min > 0) ? own_min : own_max;
+    return closed ? 1 + n : n == n_closed ? 0 : own_lo + (n - n_closed - 1);
   };
 
   if (tid == 0) {
-    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_kv, 128); mbar_init(&sm.bar_q, 128);
-    mbar_init(&sm.bar_s, 1); mbar_init(&sm.bar_p, 128); mbar_init(&sm.bar_o, 1);
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_mf, 128); mbar_init(&sm.bar_k, 128); mbar_init(&sm.bar_v, 128);
+    for (int x = 0; x < 2; ++x) { mbar_init(&sm.bar_q[x], 128); mbar_init(&sm.bar_s[x], 1); mbar_init(&sm.bar_p[x], 128); mbar_init(&sm.bar_o[x], 1); }
     sm.abort = 0;
     mbar_init_fence();
   }
-  if (warp == 8) {  // 256 columns of tensor memory: S at 0, O at 128
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256) : "memory");
+  if (warp == 12) {  // all 512 columns of tensor memory: S of tile x at 128 x, O at 256 + 128 x
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = sm.tmem_base, tmem_s = tmem, tmem_o = tmem + 128;
+  const uint32_t tmem = sm.tmem_base;
   const size_t head = (size_t)bh * a.hs, eh = (size_t)bh * G * D, ih = (size_t)bh * a.count * D;
   // the BF16 row of position tp: the chunk, the sink window, or the window of the group that was open before the chunk
   auto token_row = [&](int tp, const uint16_t *in, const uint16_t *sink, const uint16_t *open) -> const uint16_t * {
     return tp >= n0 ? in + ih + (size_t)(tp - n0) * D : tp < G ? sink + eh + (size_t)tp * D : open + eh + (size_t)(tp - (n0 - 1) / G * G) * D;
   };
 
-  if (warp == 8) {
+  if (warp == 12) {
     // ================= issuer: bulk copies of the raw groups, the products =================
     if (lane == 0) {
       auto fetch = [&](int g) {
@@ -189,41 +200,58 @@ __global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill 
       for (int n = 0; n < n_pass; ++n) {
         bool closed;
         pass_group(n, closed);
-        if (!wait(sm, &sm.bar_kv, n & 1) || !wait(sm, &sm.bar_q, n & 1)) break;
+        const uint32_t ph = n & 1, idesc = closed ? IDESC_F16 : IDESC_BF16;
+        if (!wait(sm, &sm.bar_k, ph)) break;
+        bool ok = true;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!(ok = wait(sm, &sm.bar_q[x], ph))) break;
+          tc_fence_after();
+          const uint8_t *qop = closed ? sm.qp[x] : sm.q[x];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) mma_f16(tmem + 128 * x, smem_desc(qop, kk >> 2, kk & 3), smem_desc(sm.k, kk >> 2, kk & 3), idesc, kk > 0);
+          mma_commit(&sm.bar_s[x]);
+        }
+        if (!ok || !wait(sm, &sm.bar_v, ph)) break;
         if (n + 1 < n_closed) fetch(2 + n);  // the raw buffer has been consumed: the next closed group's records
-        tc_fence_after();
-        const uint8_t *qop = closed ? sm.qh : sm.q;
-        const uint32_t idesc = closed ? IDESC_F16 : IDESC_BF16;
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!(ok = wait(sm, &sm.bar_p[x], ph))) break;
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_f16(tmem_s, smem_desc(qop, kk >> 2, kk & 3), smem_desc(sm.k, kk >> 2, kk & 3), idesc, kk > 0);
-        mma_commit(&sm.bar_s);
-        if (!wait(sm, &sm.bar_p, n & 1)) break;
-        tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) mma_f16(tmem_o, smem_desc(sm.p, kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
-        mma_commit(&sm.bar_o);
+          for (int kk = 0; kk < 8; ++kk)
+            mma_f16(tmem + 256 + 128 * x, smem_desc(sm.qp[x], kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
+          mma_commit(&sm.bar_o[x]);
+        }
+        if (!ok) break;
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 8) {
     // ================= operand producers =================
-    const int pt = tid - 128;  // 0 .. 127
+    const int pt = tid - 256;  // 0 .. 127
+    const int l = pt & 31;
     int raw_uses = 0;
     for (int n = 0; n < n_pass; ++n) {
       bool closed;
       const int g = pass_group(n, closed);
-      if (closed && !wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
-      if (n > 0 && !wait(sm, &sm.bar_o, (n - 1) & 1)) break;  // the previous pass's products have read the K and V' tiles
+      const uint32_t prev = (n - 1) & 1;
       if (closed) {
-        // (record j, lane l) pairs: pt handles j = pt / 32 and j + 4, lane l = pt % 32, of K and of V
-        const int l = pt & 31;
+        if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
+        {  // K bases and steps of channel pt as FP32 for the row threads
+          const uint8_t *m = sm.meta + 16 * (pt >> 2) + 2 * (pt & 3);
+          sm.kb[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
+          sm.ks[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
+        }
+        mbar_arrive(&sm.bar_mf);
+      }
+      // ---- Kop (free once both tiles' S of the previous pass are complete) ----
+      if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
+      if (closed) {
+        // (record j, lane l): token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
 #pragma unroll 1
         for (int jj = 0; jj < 2; ++jj) {
           const int j = (pt >> 5) + 4 * jj;
-          const uint8_t *rc = sm.raw + j * RC, *rf = sm.raw + SBG * RC + j * RF;
           uint32_t Wc[2 * CB], Wf[2 * FB];
-          // K: token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
-          lane_words<CB>(rc, 0, l, Wc);
-          lane_words<FB>(rf, 0, l, Wf);
+          lane_words<CB>(sm.raw + j * RC, 0, l, Wc);
+          lane_words<FB>(sm.raw + SBG * RC + j * RF, 0, l, Wf);
           const int tok = 16 * j + (l & 15);
 #pragma unroll
           for (int s2 = 0; s2 < 8; ++s2) {
@@ -231,35 +259,46 @@ __global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill 
             const uint2 y = bytes_to_half4((slot_value<CB>(Wc, 2 * s2 + 1) << FB) | slot_value<FB>(Wf, 2 * s2 + 1));
             *reinterpret_cast<uint4 *>(chunk_at(sm.k, tok, 64 * (l >> 4) + 8 * s2)) = make_uint4(x.x, x.y, y.x, y.y);
           }
-          // V': channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code
-          lane_words<CB>(rc, 1, l, Wc);
-          lane_words<FB>(rf, 1, l, Wf);
-          const uint4 vm = lds128(sm.meta + 512 + 16 * l);
-          const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
+        }
+      } else {
+        for (int e = pt; e < G * 16; e += 128) {  // BF16 group g: K rows as they are
+          const int tk = e >> 4, c = e & 15, tp = g * G + tk;
+          const uint4 kw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.k, a.c.sink_k, a.c.open_k)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4 *>(chunk_at(sm.k, tk, 8 * c)) = kw;
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_k);
+      // ---- V' (free once both tiles' O products of the previous pass are complete) ----
+      if (n > 0 && (!wait(sm, &sm.bar_o[0], prev) || !wait(sm, &sm.bar_o[1], prev))) break;
+      if (closed) {
+        // (record j, lane l): channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code in FP16 arithmetic
+        const uint4 vm = lds128(sm.meta + 512 + 16 * l);
+        const __half2 vb[4] = {__float2half2_rn(bf_lo(vm.x)), __float2half2_rn(bf_hi(vm.x)), __float2half2_rn(bf_lo(vm.y)), __float2half2_rn(bf_hi(vm.y))};
+        const __half2 vs[4] = {__float2half2_rn(bf_lo(vm.z)), __float2half2_rn(bf_hi(vm.z)), __float2half2_rn(bf_lo(vm.w)), __float2half2_rn(bf_hi(vm.w))};
+#pragma unroll 1
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = (pt >> 5) + 4 * jj;
+          uint32_t Wc[2 * CB], Wf[2 * FB];
+          lane_words<CB>(sm.raw + j * RC, 1, l, Wc);
+          lane_words<FB>(sm.raw + SBG * RC + j * RF, 1, l, Wf);
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
             uint32_t h[8];
 #pragma unroll
             for (int quad = 0; quad < 4; ++quad) {
-              const uint32_t code = (slot_value<CB>(Wc, v_slot_of(CB, cc, quad)) << FB) | slot_value<FB>(Wf, v_slot_of(FB, cc, quad));
-              float f[4];
-#pragma unroll
-              for (int x = 0; x < 4; ++x) f[x] = fmaf(vs[cc], __uint_as_float(0x4B000000u | ((code >> (8 * x)) & 255u)) - 8388608.f, vb[cc]);
-              h[2 * quad] = pack_half2(f[0], f[1]); h[2 * quad + 1] = pack_half2(f[2], f[3]);
+              const uint2 c4 = bytes_to_half4((slot_value<CB>(Wc, v_slot_of(CB, cc, quad)) << FB) | slot_value<FB>(Wf, v_slot_of(FB, cc, quad)));
+              h[2 * quad] = hfma2_bits(c4.x, vs[cc], vb[cc]);
+              h[2 * quad + 1] = hfma2_bits(c4.y, vs[cc], vb[cc]);
             }
-            uint8_t *dst = chunk_at(sm.v, 4 * l + cc, 16 * j);
-            *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(chunk_at(sm.v, 4 * l + cc, 16 * j)) = make_uint4(h[0], h[1], h[2], h[3]);
             *reinterpret_cast<uint4 *>(chunk_at(sm.v, 4 * l + cc, 16 * j + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
           }
         }
       } else {
-        // BF16 group g: K rows as they are; V rows converted to FP16 and transposed (tokens along the K extent)
-        for (int e = pt; e < G * 16; e += 128) {
+        for (int e = pt; e < G * 16; e += 128) {  // V rows converted to FP16 and transposed (tokens along the K extent)
           const int tk = e >> 4, c = e & 15, tp = g * G + tk;
-          const bool live = tp < n1;
-          const uint4 kw = live ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.k, a.c.sink_k, a.c.open_k)) + c) : make_uint4(0u, 0u, 0u, 0u);
-          *reinterpret_cast<uint4 *>(chunk_at(sm.k, tk, 8 * c)) = kw;
-          const uint4 vw = live ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.v, a.c.sink_v, a.c.open_v)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          const uint4 vw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.v, a.c.sink_v, a.c.open_v)) + c) : make_uint4(0u, 0u, 0u, 0u);
           const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
 #pragma unroll
           for (int x = 0; x < 8; ++x) {
@@ -269,147 +308,170 @@ __global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill 
         }
       }
       fence_async_smem();
-      mbar_arrive(&sm.bar_kv);
+      mbar_arrive(&sm.bar_v);
     }
   } else {
     // ================= row threads: qhat, softmax, P', output =================
-    const int r = tid, R = r0 + r;
+    const int X = warp >> 2, r = tid & 127, R = r0 + ROWS * X + r;
     const bool valid = R < rows;
     const int i = valid ? R / qg : 0, hq = kh * qg + (valid ? R - i * qg : 0), pos = n0 + i, own = pos / G;
+    uint8_t *const qt = sm.q[X], *const pt_ = sm.qp[X];
     // the row's q into the BF16 Q tile (rows past the end: zeros)
     {
-      const uint4 *qp = reinterpret_cast<const uint4 *>(a.q + ((size_t)(b * a.q_heads + hq) * a.count + i) * D);
+      const uint4 *qsrc = reinterpret_cast<const uint4 *>(a.q + ((size_t)(b * a.q_heads + hq) * a.count + i) * D);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4 *>(chunk_at(sm.q, r, 8 * c)) = valid ? __ldg(qp + c) : make_uint4(0u, 0u, 0u, 0u);
+      for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4 *>(chunk_at(qt, r, 8 * c)) = valid ? __ldg(qsrc + c) : make_uint4(0u, 0u, 0u, 0u);
     }
     float m_run = -INFINITY, l_run = 0.f;
-    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
-    int raw_uses = 0;
+    const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16, tmem_s = tmem + 128 * X + lane_base, tmem_o = tmem + 256 + 128 * X + lane_base;
+    int mf_uses = 0;
     bool ok = true;
-    for (int n = 0; n < n_pass && ok; ++n) {
+    for (int n = 0; n < n_pass; ++n) {
       bool closed;
       const int g = pass_group(n, closed);
       const bool include = valid && (closed ? g < own : (g == 0 || g == own));
+      const bool any = __any_sync(FULL, include);
+      // the previous pass's O product has read P' (the buffer qhat goes to) and O is stable
+      if (n > 0 && !__all_sync(FULL, wait(sm, &sm.bar_o[X], (n - 1) & 1))) { ok = false; break; }
       float sq = 0.f, qb = 0.f;
       if (closed) {
-        if (!__all_sync(FULL, wait(sm, &sm.bar_raw, raw_uses++ & 1))) { ok = false; break; }
-        // qhat of the row for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r); written as FP16
-        float amax = 0.f, dot = 0.f;
+        if (!__all_sync(FULL, wait(sm, &sm.bar_mf, mf_uses++ & 1))) { ok = false; break; }
+        if (any) {
+          // qhat of the row for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r); written as FP16
+          float amax = 0.f;
+          float2 dot = make_float2(0.f, 0.f);
 #pragma unroll 4
-        for (int c = 0; c < 16; ++c) {
-          const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(sm.q, r, 8 * c));
-          const uint4 m0 = lds128(sm.meta + 32 * c), m1 = lds128(sm.meta + 32 * c + 16);  // channels 8 c .. + 3 and + 4 .. + 7: 4 bases, 4 steps each
-          const float qf[8] = {bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y), bf_lo(qw.z), bf_hi(qw.z), bf_lo(qw.w), bf_hi(qw.w)};
-          const float kb[8] = {bf_lo(m0.x), bf_hi(m0.x), bf_lo(m0.y), bf_hi(m0.y), bf_lo(m1.x), bf_hi(m1.x), bf_lo(m1.y), bf_hi(m1.y)};
-          const float ks[8] = {bf_lo(m0.z), bf_hi(m0.z), bf_lo(m0.w), bf_hi(m0.w), bf_lo(m1.z), bf_hi(m1.z), bf_lo(m1.w), bf_hi(m1.w)};
-#pragma unroll
-          for (int x = 0; x < 8; ++x) { amax = fmaxf(amax, fabsf(__fmul_rn(qf[x], ks[x]))); dot = fmaf(qf[x], kb[x], dot); }
-        }
-        float rc;
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
-        rc = fmaf(fmaf(-amax, rc, 1.f), rc, rc);
-        const float q0 = __fmul_rn(127.f, rc), rr = amax > 0.f ? fmaf(fmaf(-amax, q0, 127.f), rc, q0) : 0.f;
-        sq = __fmul_rn(amax, __fmul_rn(a.sl, 1.f / 127.f));
-        qb = __fmul_rn(dot, a.sl);
-#pragma unroll 4
-        for (int c = 0; c < 16; ++c) {
-          const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(sm.q, r, 8 * c));
-          const uint4 m0 = lds128(sm.meta + 32 * c), m1 = lds128(sm.meta + 32 * c + 16);
-          const float qf[8] = {bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y), bf_lo(qw.z), bf_hi(qw.z), bf_lo(qw.w), bf_hi(qw.w)};
-          const float ks[8] = {bf_lo(m0.z), bf_hi(m0.z), bf_lo(m0.w), bf_hi(m0.w), bf_lo(m1.z), bf_hi(m1.z), bf_lo(m1.w), bf_hi(m1.w)};
-          uint32_t h[4];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {  // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
-            const float t0 = fmaf(__fmul_rn(qf[2 * x], ks[2 * x]), rr, MAGICF) - MAGICF, t1 = fmaf(__fmul_rn(qf[2 * x + 1], ks[2 * x + 1]), rr, MAGICF) - MAGICF;
-            h[x] = pack_half2(t0, t1);
+          for (int c = 0; c < 16; ++c) {
+            const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(qt, r, 8 * c));
+            const float4 s0 = *reinterpret_cast<const float4 *>(&sm.ks[8 * c]), s1 = *reinterpret_cast<const float4 *>(&sm.ks[8 * c + 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&sm.kb[8 * c]), b1 = *reinterpret_cast<const float4 *>(&sm.kb[8 * c + 4]);
+            const float2 q0 = bf2(qw.x), q1 = bf2(qw.y), q2 = bf2(qw.z), q3 = bf2(qw.w);
+            const float2 z0 = __fmul2_rn(q0, make_float2(s0.x, s0.y)), z1 = __fmul2_rn(q1, make_float2(s0.z, s0.w));
+            const float2 z2 = __fmul2_rn(q2, make_float2(s1.x, s1.y)), z3 = __fmul2_rn(q3, make_float2(s1.z, s1.w));
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(z0.x), fabsf(z0.y))), fmaxf(fabsf(z1.x), fabsf(z1.y)));
+            amax = fmaxf(fmaxf(amax, fmaxf(fabsf(z2.x), fabsf(z2.y))), fmaxf(fabsf(z3.x), fabsf(z3.y)));
+            dot = __ffma2_rn(q0, make_float2(b0.x, b0.y), dot); dot = __ffma2_rn(q1, make_float2(b0.z, b0.w), dot);
+            dot = __ffma2_rn(q2, make_float2(b1.x, b1.y), dot); dot = __ffma2_rn(q3, make_float2(b1.z, b1.w), dot);
           }
-          *reinterpret_cast<uint4 *>(chunk_at(sm.qh, r, 8 * c)) = make_uint4(h[0], h[1], h[2], h[3]);
+          float rc;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
+          rc = fmaf(fmaf(-amax, rc, 1.f), rc, rc);
+          const float q0_ = __fmul_rn(127.f, rc), rr = amax > 0.f ? fmaf(fmaf(-amax, q0_, 127.f), rc, q0_) : 0.f;
+          sq = __fmul_rn(amax, __fmul_rn(a.sl, 1.f / 127.f));
+          qb = __fmul_rn(dot.x + dot.y, a.sl);
+          const float2 rr2 = splat(rr), mg = splat(MAGICF), ng = splat(-MAGICF);
+#pragma unroll 4
+          for (int c = 0; c < 16; ++c) {
+            const uint4 qw = *reinterpret_cast<const uint4 *>(chunk_at(qt, r, 8 * c));
+            const float4 s0 = *reinterpret_cast<const float4 *>(&sm.ks[8 * c]), s1 = *reinterpret_cast<const float4 *>(&sm.ks[8 * c + 4]);
+            // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
+            const float2 t0 = __fadd2_rn(__ffma2_rn(__fmul2_rn(bf2(qw.x), make_float2(s0.x, s0.y)), rr2, mg), ng);
+            const float2 t1 = __fadd2_rn(__ffma2_rn(__fmul2_rn(bf2(qw.y), make_float2(s0.z, s0.w)), rr2, mg), ng);
+            const float2 t2 = __fadd2_rn(__ffma2_rn(__fmul2_rn(bf2(qw.z), make_float2(s1.x, s1.y)), rr2, mg), ng);
+            const float2 t3 = __fadd2_rn(__ffma2_rn(__fmul2_rn(bf2(qw.w), make_float2(s1.z, s1.w)), rr2, mg), ng);
+            *reinterpret_cast<uint4 *>(chunk_at(pt_, r, 8 * c)) = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
+          }
         }
       }
       fence_async_smem();
-      mbar_arrive(&sm.bar_q);
-      if (!__all_sync(FULL, wait(sm, &sm.bar_s, n & 1))) { ok = false; break; }
-      if (n > 0 && !__all_sync(FULL, wait(sm, &sm.bar_o, (n - 1) & 1))) { ok = false; break; }  // P' tile free, O stable
+      mbar_arrive(&sm.bar_q[X]);
+      if (!__all_sync(FULL, wait(sm, &sm.bar_s[X], n & 1))) { ok = false; break; }
       tc_fence_after();
       // softmax of the row over the pass's 128 tokens, by 16-token blocks; P' = fp16(2^(m_block - m_row) p)
-      const float sl = a.sl;
+      const int lim = include ? (closed ? G : pos - g * G) : -1;  // tokens 0 .. lim of the group are attended
+      const float2 mul = splat(closed ? sq : a.sl), add = splat(closed ? qb : 0.f);
+      if (!any) {  // (warp-uniform) nothing to attend: P' = 0
+#pragma unroll
+        for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4 *>(chunk_at(pt_, r, 8 * c)) = make_uint4(0u, 0u, 0u, 0u);
+      } else {
 #pragma unroll 1
-      for (int cq = 0; cq < 4; ++cq) {  // 32 columns at a time
-        uint32_t x[32];
-        tmem_ld32(tmem_s + lane_base + 32 * cq, x);
+        for (int cq = 0; cq < 4; ++cq) {  // 32 columns at a time
+          uint32_t x[32];
+          tmem_ld32(tmem_s + 32 * cq, x);
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {  // the two 16-token blocks of the 32 columns
-          const int t0 = 32 * cq + 16 * hb;
-          float s[16], mb = -INFINITY;
+          for (int hb = 0; hb < 2; ++hb) {  // the two 16-token blocks of the 32 columns
+            const int t0 = 32 * cq + 16 * hb;
+            float2 sc[8];
+            float mb = -INFINITY;
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
-            const float xv = __uint_as_float(x[16 * hb + t]);
-            float sv = closed ? fmaf(sq, xv, qb) : __fmul_rn(xv, sl);
-            if (!include || (!closed && g * G + t0 + t > pos)) sv = -INFINITY;
-            s[t] = sv;
-            mb = fmaxf(mb, sv);
-          }
-          // the row's running maximum moves only when a block exceeds it by more than 2^8 (rare): its sums, its O row in
-          // tensor memory and the P' chunks already written in this pass are rescaled. Tensor-memory accesses are
-          // warp-wide, so the whole warp takes part (rows that do not move scale by 1).
-          const bool need = mb > m_run + 8.f;
-          const float al = need ? ex2(m_run - mb) : 1.f;  // 0 on the row's first block
-          if (__any_sync(FULL, need)) {
-            if (n > 0) {
-#pragma unroll 1
-              for (int oc = 0; oc < 4; ++oc) {
-                uint32_t o[32];
-                tmem_ld32(tmem_o + lane_base + 32 * oc, o);
+            for (int t = 0; t < 8; ++t)
+              sc[t] = __ffma2_rn(make_float2(__uint_as_float(x[16 * hb + 2 * t]), __uint_as_float(x[16 * hb + 2 * t + 1])), mul, add);
+            if (lim < t0 + 15) {  // the causal edge (or a row that does not attend to this group)
 #pragma unroll
-                for (int z = 0; z < 32; ++z) o[z] = __float_as_uint(__uint_as_float(o[z]) * al);
-                tmem_st32(tmem_o + lane_base + 32 * oc, o);
+              for (int t = 0; t < 8; ++t) {
+                if (t0 + 2 * t > lim) sc[t].x = -INFINITY;
+                if (t0 + 2 * t + 1 > lim) sc[t].y = -INFINITY;
               }
             }
-            if (need) {
-              l_run *= al;
-              for (int tb = 0; tb < t0; tb += 8) {
-                uint4 *pc = reinterpret_cast<uint4 *>(chunk_at(sm.p, r, tb));
-                uint4 w = *pc;
-                uint32_t *ww = reinterpret_cast<uint32_t *>(&w);
 #pragma unroll
-                for (int z = 0; z < 4; ++z) {
-                  const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ww[z]));
-                  ww[z] = pack_half2(f.x * al, f.y * al);
+            for (int t = 0; t < 8; ++t) mb = fmaxf(mb, fmaxf(sc[t].x, sc[t].y));
+            // the row's running maximum moves only when a block exceeds it by more than 2^8 (rare): its sums, its O row in
+            // tensor memory and the P' chunks already written in this pass are rescaled. Tensor-memory accesses are
+            // warp-wide, so the whole warp takes part (rows that do not move scale by 1).
+            const bool need = mb > m_run + 8.f;
+            const float al = need ? ex2(m_run - mb) : 1.f;  // 0 on the row's first block
+            if (__any_sync(FULL, need)) {
+              if (n > 0) {
+#pragma unroll 1
+                for (int oc = 0; oc < 4; ++oc) {
+                  uint32_t o[32];
+                  tmem_ld32(tmem_o + 32 * oc, o);
+#pragma unroll
+                  for (int z = 0; z < 32; ++z) o[z] = __float_as_uint(__uint_as_float(o[z]) * al);
+                  tmem_st32(tmem_o + 32 * oc, o);
                 }
-                *pc = w;
               }
-              m_run = mb;
+              if (need) {
+                l_run *= al;
+                for (int tb = 0; tb < t0; tb += 8) {
+                  uint4 *pc = reinterpret_cast<uint4 *>(chunk_at(pt_, r, tb));
+                  uint4 w = *pc;
+                  uint32_t *ww = reinterpret_cast<uint32_t *>(&w);
+#pragma unroll
+                  for (int z = 0; z < 4; ++z) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&ww[z]));
+                    ww[z] = pack_half2(f.x * al, f.y * al);
+                  }
+                  *pc = w;
+                }
+                m_run = mb;
+              }
             }
+            uint32_t h[8];
+            if (mb == -INFINITY) {
+#pragma unroll
+              for (int t = 0; t < 8; ++t) h[t] = 0u;
+            } else {
+              const float w = ex2(mb - m_run);
+              const float2 nm = splat(-mb), w2 = splat(w), c255 = splat(255.f), mg = splat(MAGICF), ng = splat(-MAGICF);
+              float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                const float2 d = __fadd2_rn(sc[t], nm);
+                const float2 pf = __fadd2_rn(__ffma2_rn(make_float2(ex2(d.x), ex2(d.y)), c255, mg), ng);
+                acc = __fadd2_rn(acc, pf);
+                const float2 pw = __fmul2_rn(pf, w2);
+                h[t] = pack_half2(pw.x, pw.y);
+              }
+              l_run = fmaf(w, acc.x + acc.y, l_run);
+            }
+            *reinterpret_cast<uint4 *>(chunk_at(pt_, r, t0)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(chunk_at(pt_, r, t0 + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
           }
-          uint32_t h[8];
-          if (mb == -INFINITY) {
-#pragma unroll
-            for (int t = 0; t < 8; ++t) h[t] = 0u;
-          } else {
-            const float w = ex2(mb - m_run);
-            float sp = 0.f, pf[16];
-#pragma unroll
-            for (int t = 0; t < 16; ++t) { pf[t] = fmaf(ex2(s[t] - mb), 255.f, MAGICF) - MAGICF; sp += pf[t]; }
-            l_run = fmaf(w, sp, l_run);
-#pragma unroll
-            for (int t = 0; t < 8; ++t) h[t] = pack_half2(w * pf[2 * t], w * pf[2 * t + 1]);
-          }
-          *reinterpret_cast<uint4 *>(chunk_at(sm.p, r, t0)) = make_uint4(h[0], h[1], h[2], h[3]);
-          *reinterpret_cast<uint4 *>(chunk_at(sm.p, r, t0 + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
         }
       }
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&sm.bar_p);
+      mbar_arrive(&sm.bar_p[X]);
     }
-    if (ok && __all_sync(FULL, wait(sm, &sm.bar_o, (n_pass - 1) & 1))) {
+    if (ok && __all_sync(FULL, wait(sm, &sm.bar_o[X], (n_pass - 1) & 1))) {
       tc_fence_after();
       const float inv = 1.f / l_run;
       uint16_t *orow = a.out + (size_t)(b * a.q_heads + hq) * a.out_hs + (size_t)i * a.out_ts;
 #pragma unroll 1
       for (int oc = 0; oc < 4; ++oc) {
         uint32_t o[32];
-        tmem_ld32(tmem_o + lane_base + 32 * oc, o);
+        tmem_ld32(tmem_o + 32 * oc, o);
         if (valid) {
 #pragma unroll
           for (int z = 0; z < 4; ++z) {
@@ -425,9 +487,9 @@ __global__ void __launch_bounds__(288, 1) attend_tc_kernel(const fbla_k_prefill 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 12) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
 
@@ -444,7 +506,7 @@ extern "C" int fbla_k_attend_tc_status(void) {
 extern "C" cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream) {
   using namespace fbla::tc;
   const int qg = a->q_heads / a->kv_heads;
-  const dim3 grid((a->count * qg + ROWS - 1) / ROWS, a->batch * a->kv_heads);
+  const dim3 grid((a->count * qg + CTA_ROWS - 1) / CTA_ROWS, a->batch * a->kv_heads);
   const size_t smem = sizeof(Smem) + 1024;
   static thread_local int configured[64] = {0};
   int dev = 0;
@@ -455,8 +517,8 @@ extern "C" cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStre
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64) configured[dev] = 1;
   }
-  if (a->cb == 3) attend_tc_kernel<3, 3><<<grid, 288, smem, stream>>>(*a);
-  else attend_tc_kernel<4, 2><<<grid, 288, smem, stream>>>(*a);
+  if (a->cb == 3) attend_tc_kernel<3, 3><<<grid, THREADS, smem, stream>>>(*a);
+  else attend_tc_kernel<4, 2><<<grid, THREADS, smem, stream>>>(*a);
   return cudaGetLastError();
 }
 
