@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_tc_kernel(const fbla_k_pref
 #pragma unroll
               for (int t = 0; t < 16; ++t) if (t0 + t <= lim) xm = fmaxf(xm, __uint_as_float(x[16 * hb + t]));
             }
-            mbk[2 * cq + hb] = fmaf(mul1, xm, add1);  // -inf for a block without attended tokens
+            mbk[2 * cq + hb] = xm == -INFINITY ? -INFINITY : fmaf(mul1, xm, add1);  // -inf: a block without attended tokens
           }
         }
         sm.ex2[X][r][hf] = fmaxf(fmaxf(mbk[0], mbk[1]), fmaxf(mbk[2], mbk[3]));
@@ -558,7 +558,7 @@ __global__ void __launch_bounds__(THREADS, 1) attend_tc_kernel(const fbla_k_pref
           for (int hb = 0; hb < 2; ++hb) {
             const int t0 = 32 * cq + 16 * hb;
             const float mb = mbk[2 * cq + hb];
-            const float2 nm = splat(mb == -INFINITY ? 0.f : -mb), w2 = splat(ex2(mb - m_run));
+            const float2 nm = splat(mb == -INFINITY ? 0.f : -mb), w2 = splat(mb == -INFINITY ? 0.f : ex2(mb - m_run));
             float2 sc[8];
 #pragma unroll
             for (int t = 0; t < 8; ++t)

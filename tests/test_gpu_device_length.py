@@ -118,7 +118,8 @@ def test_per_row_lengths(ours, oracle, mode, QH, KH, lens):
 @pytest.mark.parametrize("B,QH,KH,n0,counts", [(1, 2, 2, 100, [100, 100]), (1, 4, 2, 1000, [300, 212, 128, 1, 1407]), (2, 8, 2, 2048, [512, 512, 700, 330])])
 def test_prefill_at_equals_prefill(ours, mode, B, QH, KH, n0, counts):
     """Chunks with the start and count on the device (launches sized by the ceiling alone) against the host-length
-    calls: outputs of the chunk's positions and the whole cache bit-identical; rows past the count stay untouched."""
+    calls: outputs of the chunk's positions (bit-identical whenever both calls run the same attention kernel) and the whole
+    cache bit-identical; rows past the count stay untouched."""
     total = n0 + sum(counts)
     q, k, v = datagen.uneven_case(62, B, QH, KH, total, q_rows=total)
     qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
@@ -137,7 +138,13 @@ def test_prefill_at_equals_prefill(ours, mode, B, QH, KH, n0, counts):
         ours.prefill_at(b, pad(kd), pad(vd), pad(qd), length, count, max_count, out=out)
         length.add_(n)
         torch.cuda.synchronize()
-        assert torch.equal(out[:, :, :n], want), (t, n)
+        qg = QH // KH
+        if (n * qg >= 64) == (max_count * qg >= 64):  # the same kernel serves both calls: bit-identical
+            assert torch.equal(out[:, :, :n], want), (t, n)
+        else:  # the host-length call of a tiny chunk takes the warp-per-row kernel, the ceiling-sized launch the tensor-core one
+            w = datagen.bf16_to_f32(gu.bits_of(want)).astype(np.float64)
+            g = datagen.bf16_to_f32(gu.bits_of(out[:, :, :n].contiguous())).astype(np.float64)
+            assert (np.abs(g - w) <= 2e-3 * np.abs(w).max() + gu.bf16_ulp(w)).all(), (t, n)
         assert (out[:, :, n:] == -7.0).all()
         t += n
     b["tokens"] = a["tokens"]

@@ -3,9 +3,8 @@ the same seeded inputs -- packed bytes bit-exact, attention outputs within 2e-3 
 reference's own CUDA library was built into oracle/_ref, against that library on the same device buffers.
 The case list follows the reference's own matrix (attention/fbla/tests/test_fbla.cu:1181-1282,
 attention/python/tests/test_attention.py)."""
-import os
-
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -193,6 +192,8 @@ def test_decode_status_word_clear(ours):
     (2, 8, 2, 1500, [300, 212, 128, 1, 859], 23),
     (1, 16, 8, 1024, [512, 512], 24),
     (1, 6, 2, 700, [260, 440], 30),
+    (1, 2, 2, 1000, [1000], 31),      # one query per KV head: a 256-row CTA spans three groups
+    (1, 8, 1, 600, [37, 563], 32),    # eight queries per KV head
 ])
 def test_prefill_matches_oracle(ours, oracle, mode, B, QH, KH, N, chunks, seed):
     q, k, v = datagen.uneven_case(seed, B, QH, KH, N, q_rows=N)
