@@ -340,15 +340,105 @@ def run_seqsplit(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """BASELINE configs[3]: causal prefill, batch 4, sequence 8192, 32q/8kv, 4+2. One step = one prefill call on an empty
+    cache: quantize-on-write of the chunk's groups, attention over the compressed cache (tensor cores), window update.
+    N > 1: every rank prefills its own batch (weak). FLOPs: 4 * 128 per (query, attended key) pair (QK and PV)."""
+    import torch
+    import torch.distributed as dist
+
+    from mlops_b200 import attention
+    from tests import datagen
+
+    B, QH, KH, S, mode = 4, 32, 8, 8192, "4+2"
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    q, k, v = datagen.baseline_case(1004 + 7919 * rank, B, QH, KH, S, q_rows=S, outliers=True)
+    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).view(torch.bfloat16)
+    host = [bf(x).pin_memory() for x in (q, k, v)]
+    qd, kd, vd = [x.to(dev) for x in host]
+    cache = attention.empty(B, KH, S, mode, device=dev)
+    steps, warmup = min(args.steps, 20), max(min(args.warmup, 5), 3)
+
+    def step():
+        cache.tokens = 0  # the same buffers, refilled from the start
+        return attention.prefill(qd, kd, vd, cache)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(warmup):
+        out = step()
+    stream = torch.cuda.current_stream()
+    sampler = ClockSampler(local)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record(stream)
+    for _ in range(steps):
+        out = step()
+    ev1.record(stream)
+    barrier()
+    ms = ev0.elapsed_time(ev1) / steps
+    clocks = sampler.result()
+    out_host = torch.empty(out.shape, dtype=torch.bfloat16).pin_memory()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        cache.tokens = 0
+        o = attention.prefill(host[0].to(dev, non_blocking=True), host[1].to(dev, non_blocking=True), host[2].to(dev, non_blocking=True), cache)
+        out_host.copy_(o, non_blocking=True)
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / steps
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = t.tolist()
+    if rank == 0:
+        flops = 4.0 * 128 * B * QH * S * (S + 1) / 2
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        peak, peak_kind = (peaks["bf16_tflops_sustained"], "measured, sustained") if "bf16_tflops_sustained" in peaks else (1400.0, "fallback")
+        ach = flops / (ms * 1e-3) / 1e12
+        rows_per_cta = 256
+        print(json.dumps(dict(metric="prefill_tflops", value=world * ach, unit="TFLOP/s", n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms,
+                              higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f16 products of 6-bit codes and int8 queries, f32 accumulation",
+                              data="synthetic",
+                              config=dict(workload="causal prefill B4 S8192 32q/8kv 4+2 (BASELINE configs[3]); per rank", l2="q + k + v + cache = 0.5 GB per step > L2",
+                                          batch=B, q_heads=QH, kv_heads=KH, tokens=S, mode=mode),
+                              e2e=dict(value=world * flops / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=sum(x.numel() * 2 for x in host),
+                                       d2h_bytes_per_step=out_host.numel() * 2),
+                              gpu_launches=3 * steps,
+                              roofline=dict(bound="tensor", achieved=ach, peak=peak, unit="TFLOP/s", frac=ach / peak, traffic=None, peak_kind=peak_kind,
+                                            kernel="prefill call (close + attend_tc + finish); attend_tc is > 95 % of it", algorithmic_flops=flops,
+                                            rows_per_cta=rows_per_cta),
+                              clocks=clocks)))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m"],
-                    help="decode_b8: the headline (BASELINE configs[1]); seqsplit_*: one long sequence split over the ranks (configs[2])")
+    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m", "prefill_b4"],
+                    help="decode_b8: the headline (BASELINE configs[1]); seqsplit_*: one long sequence split over the ranks (configs[2]); "
+                         "prefill_b4: causal prefill in TFLOP/s (configs[3])")
     args = ap.parse_args()
+    if args.workload == "prefill_b4" and args.impl == "ours":
+        return run_prefill(args)
     if args.workload != "decode_b8" and args.impl == "ours":
         return run_seqsplit(args)
     if args.impl == "reference":
