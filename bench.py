@@ -350,7 +350,7 @@ def run_prefill(args):
     from mlops_b200 import attention
     from tests import datagen
 
-    B, QH, KH, S, mode = 4, 32, 8, 8192, "4+2"
+    B, QH, KH, S, mode = (4 if args.workload == "prefill_b4" else 1), 32, 8, 8192, "4+2"  # prefill_b1: the small case for profiler captures
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -414,7 +414,7 @@ def run_prefill(args):
         print(json.dumps(dict(metric="prefill_tflops", value=world * ach, unit="TFLOP/s", n_gpus=world, steps=steps, warmup=warmup, ms_per_step=ms,
                               higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f16 products of 6-bit codes and int8 queries, f32 accumulation",
                               data="synthetic",
-                              config=dict(workload="causal prefill B4 S8192 32q/8kv 4+2 (BASELINE configs[3]); per rank", l2="q + k + v + cache = 0.5 GB per step > L2",
+                              config=dict(workload=f"causal prefill B{B} S8192 32q/8kv 4+2 (BASELINE configs[3]" + ("" if B == 4 else ", one of its four sequences") + "); per rank", l2="q + k + v + cache = 0.5 GB per step > L2",
                                           batch=B, q_heads=QH, kv_heads=KH, tokens=S, mode=mode),
                               e2e=dict(value=world * flops / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", h2d_bytes_per_step=sum(x.numel() * 2 for x in host),
                                        d2h_bytes_per_step=out_host.numel() * 2),
@@ -433,11 +433,11 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m", "prefill_b4"],
+    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m", "prefill_b4", "prefill_b1"],
                     help="decode_b8: the headline (BASELINE configs[1]); seqsplit_*: one long sequence split over the ranks (configs[2]); "
-                         "prefill_b4: causal prefill in TFLOP/s (configs[3])")
+                         "prefill_b4: causal prefill in TFLOP/s (configs[3]); prefill_b1: one of its four sequences (profiler captures)")
     args = ap.parse_args()
-    if args.workload == "prefill_b4" and args.impl == "ours":
+    if args.workload.startswith("prefill") and args.impl == "ours":
         return run_prefill(args)
     if args.workload != "decode_b8" and args.impl == "ours":
         return run_seqsplit(args)

@@ -102,17 +102,6 @@ typedef struct {
   size_t images;
 } mlops_fbla_sizes;
 
-/* reference: mlops_fbla.h:153-163 (inputs of the fused per-token step) */
-typedef struct {
-  const uint16_t *q, *k, *v;
-  int64_t batch_stride, q_group_stride, kv_group_stride;
-  const uint16_t *q_norm, *k_norm;
-  float eps;
-  const float *freq;
-  float attention_factor;
-  uint16_t *q_out;
-} mlops_fbla_token;
-
 /* Bytes of scratch one decode of cfg needs on the current device; 0 for an invalid cfg. The scratch needs no
  * initial contents and may be reused by later calls that fit. reference: mlops_fbla.h:93 */
 size_t mlops_fbla_decode_scratch_bytes(const mlops_fbla_config *cfg);
@@ -159,6 +148,40 @@ mlops_fbla_status mlops_fbla_decode_at(const mlops_fbla_config *cfg, const int *
  * reference: mlops_fbla.h:154-155 */
 mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *cfg, const int *length, const uint16_t *k, const uint16_t *v,
                                        const mlops_fbla_cache *cache, cudaStream_t stream);
+
+/* The attention inputs of new tokens as the model's projection leaves them. q head h of KV head g = h / (q_heads /
+ * kv_heads) of batch row b starts at q + b * batch_stride + g * q_group_stride + (h % (q_heads / kv_heads)) * 128; k and
+ * v of KV head g at k / v + b * batch_stride + g * kv_group_stride (strides in elements; BF16, 128 per head; 4-byte
+ * aligned). q_norm / k_norm: a head's RMSNorm weights (128 BF16 each), or both NULL for no norm; eps is the norm's.
+ * freq: device, 64 x 4 floats per rotary pair (i, i + 64), each frequency f = inv_freq / 2 pi split as (fh, fl) with
+ * fh = float(f), fl = float(f - fh), and g = frac(65536 f) split the same way (gh, gl). attention_factor 0 means 1.
+ * q_out [batch, q_heads, 128] BF16: the q that mlops_fbla_decode_at takes. 96 bytes. reference: mlops_fbla.h:157-167 */
+typedef struct {
+  const uint16_t *q, *k, *v;
+  int64_t batch_stride, q_group_stride, kv_group_stride;
+  const uint16_t *q_norm, *k_norm;
+  float eps;
+  const float *freq;
+  float attention_factor;
+  uint16_t *q_out;
+} mlops_fbla_token;
+
+/* One decode step's attention inputs at the device length (position *length + cfg->tokens; per-row lengths with
+ * cfg->length_stride 1): per head the RMSNorm of q and k (FP32 sum of squares, 1 / sqrt(mean + eps) rounded to nearest,
+ * x r rounded to BF16, times the weight rounded to BF16), the rotary embedding (phase reduced exactly, one rounding to
+ * BF16), q to token->q_out, k and v appended to the cache as mlops_fbla_append_at does. cfg->capacity > 0; launches do
+ * not depend on the length. reference: mlops_fbla.h:169-173 */
+mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *cfg, const int *length, const mlops_fbla_token *token,
+                                    const mlops_fbla_cache *cache, cudaStream_t stream);
+
+/* The attention inputs of a prefill chunk of *count (<= max_count) tokens at the device length: token->q / k / v point
+ * at row 0 of the projection's [count][token->batch_stride] BF16 rows (group strides as for one token); per position
+ * the RMSNorm of q and k and the rotary embedding at *length + cfg->tokens + i; written as mlops_fbla_prefill_at takes
+ * them: q_out [q_heads, max_count, 128], k_out, v_out [kv_heads, max_count, 128] BF16 (token->q_out unused). Batch 1;
+ * rows past *count are not written; launches depend on neither *length nor *count. reference: mlops_fbla.h:175-181 */
+mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *cfg, const int *length, const int *count, int max_count,
+                                            const mlops_fbla_token *token, uint16_t *q_out, uint16_t *k_out, uint16_t *v_out,
+                                            cudaStream_t stream);
 
 /* Decode without a caller-provided scratch, for callers that cannot allocate device memory (an engine whose allocator
  * is closed after start-up, a plugin host that forbids cudaMalloc, a real-time loop): the scratch is a 32 MiB array

@@ -296,6 +296,82 @@ mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *c, const int *le
   return prefill_at("mlops_fbla_append_at", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, stream);
 }
 
+// ---- fused QKV step (reference: attention/fbla/src/fbla.cu:307-400) ---------------------------------------------------------
+static mlops_fbla_status token_common(const char *fn, const mlops_fbla_token *t, fbla_k_token &a) {
+  if (!t->q_norm != !t->k_norm) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q_norm and k_norm both or neither", fn);
+  if (!(t->eps >= 0.f) || !(t->attention_factor >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: eps and attention_factor nonnegative", fn);
+  a.q = t->q; a.k = t->k; a.v = t->v;
+  a.batch_stride = t->batch_stride; a.q_group_stride = t->q_group_stride; a.kv_group_stride = t->kv_group_stride;
+  a.q_norm = t->q_norm; a.k_norm = t->k_norm; a.freq = t->freq; a.eps = t->eps;
+  a.att = t->attention_factor == 0.f ? 1.f : t->attention_factor;
+  return MLOPS_FBLA_OK;
+}
+
+mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
+                                    cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_qkv_at";
+  if (!c || !length || !t || !cache || !t->q || !t->k || !t->v || !t->freq || !t->q_out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 || !valid_strides(c))
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch and heads must be positive, q_heads a multiple of kv_heads, tokens >= 0, capacity positive, "
+                "strides both 0 or both positive", fn);
+  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
+  fbla_k_token a{};
+  mlops_fbla_status st = token_common(fn, t, a);
+  if (st != MLOPS_FBLA_OK) return st;
+  if (!cache_complete(cache)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
+  const void *p16[] = {cache->coarse, cache->fine, cache->meta, cache->exact_sink_k, cache->exact_sink_v, cache->exact_open_k, cache->exact_open_v, t->freq};
+  for (const void *p : p16)
+    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: cache pointers and freq must be 16-byte aligned", fn);
+  const void *p4[] = {length, t->q, t->k, t->v, t->q_norm, t->k_norm, t->q_out};
+  for (const void *p : p4)
+    if (!aligned(p, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length and the token's pointers must be 4-byte aligned", fn);
+  if (t->batch_stride % 2 || t->q_group_stride % 2 || t->kv_group_stride % 2)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: strides must be even (4-byte rows)", fn);
+  if (t->batch_stride < 0 || t->q_group_stride < 0 || t->kv_group_stride < 0 || t->batch_stride > INT32_MAX || t->q_group_stride > INT32_MAX ||
+      t->kv_group_stride > INT32_MAX)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: strides are nonnegative and below 2^31", fn);
+  if (!aligned(cache->tc_images, 128)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: tc_images must be 128-byte aligned", fn);
+  if (c->length_stride != 0 && c->length_stride != 1) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0 or 1", fn);
+  // the group that the position closes (when it is a multiple of 128) is quantized from the open window first
+  fbla_k_prefill cl{};
+  fill_prefill(c, 1, c->capacity, nullptr, nullptr, nullptr, cache, nullptr, cl);
+  cl.length = length; cl.lstride = c->length_stride;
+  a.c = cl.c; a.length = length; a.lstride = c->length_stride; a.n0 = c->tokens; a.max_count = 1;
+  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads; a.q_out = t->q_out;
+  cudaError_t e = fbla_k_close_launch(&cl, 1, stream);
+  if (e == cudaSuccess) e = fbla_k_qkv_token_launch(&a, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
+}
+
+mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
+                                            uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_qkv_prefill_at";
+  if (!c || !length || !count || !t || !t->q || !t->k || !t->v || !t->freq || !q_out || !k_out || !v_out)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
+  if (c->batch != 1 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || max_count <= 0 || c->capacity <= 0 ||
+      (long long)c->tokens + max_count > c->capacity)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch 1, positive heads (q_heads a multiple of kv_heads), tokens >= 0, max_count > 0, "
+                "tokens + max_count <= capacity", fn);
+  fbla_k_token a{};
+  mlops_fbla_status st = token_common(fn, t, a);
+  if (st != MLOPS_FBLA_OK) return st;
+  if (t->batch_stride < D || t->batch_stride % 2 || t->q_group_stride % 2 || t->kv_group_stride % 2 || t->q_group_stride < 0 || t->kv_group_stride < 0)
+    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: the row stride (batch_stride) and the group strides must be even, the row at least 128", fn);
+  const void *p16[] = {q_out, k_out, v_out, t->freq};
+  for (const void *p : p16)
+    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: outputs and freq must be 16-byte aligned", fn);
+  const void *p4[] = {length, count, t->q, t->k, t->v, t->q_norm, t->k_norm};
+  for (const void *p : p4)
+    if (!aligned(p, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length, count and the projection's pointers must be 4-byte aligned", fn);
+  a.length = length; a.dcount = count; a.n0 = c->tokens; a.max_count = max_count;
+  a.batch = 1; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads;
+  a.q_out = q_out; a.k_out = k_out; a.v_out = v_out;
+  const cudaError_t e = fbla_k_qkv_chunk_launch(&a, stream);
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return ok();
+}
+
 // ---- sequence shards (include/mlops_fbla_shard.h) ------------------------------------------------------------------------
 static mlops_fbla_status shard_args(const char *fn, const mlops_fbla_shard *sh, fbla_k_decode &a) {
   if (!sh || sh->group_first < 0 || sh->group_count < 0 || (sh->windows & ~3))

@@ -22,6 +22,12 @@ constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 
 // Streaming warps per CTA and ring slots per warp, per coarse bit width. A slot holds one record pair (32 tokens);
 // the group's metadata has two slots of its own. NP <= 4 (one group of lookahead) keeps two metadata slots enough.
+#ifndef FBLA_RW
+#define FBLA_RW 12   /* refine warps per CTA */
+#endif
+#ifndef FBLA_RNST
+#define FBLA_RNST 2  /* refine ring stages per warp */
+#endif
 #ifndef FBLA_CW4
 #define FBLA_CW4 10
 #endif
@@ -41,6 +47,7 @@ template <int CB> struct CoarseShape {
   static constexpr int PAIR_BYTES = 2 * record_bytes(CB), CHUNK_BYTES = FBLA_PPC * PAIR_BYTES;
   static constexpr int GROUP_BYTES = SBG * record_bytes(CB);
 };
+static_assert(FBLA_RNST == 2, "the refine pass keeps the metadata of two groups");
 static_assert(FBLA_NP >= 2 && FBLA_NP * FBLA_PPC <= 4 && 4 % FBLA_PPC == 0, "ring slots per warp: at most one group of lookahead");
 
 // ---- where a batch row's tokens put its units -----------------------------------------------------------------------
@@ -734,12 +741,13 @@ __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
 
 // ---- refine: full - coarse of every selected sub-block ----------------------------------------------------------------------
 template <int CB, int FB> struct RefineShape {
-  static constexpr int WARPS = 12, NST = 2;
+  static constexpr int WARPS = FBLA_RW, NST = FBLA_RNST;
   static constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
-  static constexpr int STAGE = RC + RF + 1024;
+  static constexpr int STAGE = RC + RF;
 };
 template <int CB, int FB> struct __align__(128) RefineWarp {
   uint8_t stage[RefineShape<CB, FB>::NST][RefineShape<CB, FB>::STAGE];
+  uint8_t meta[2][1024];  // the metadata of the two groups that items in flight can belong to (NST = 2: the item in work and one ahead)
   uint8_t qst[8 * QST_ROW];
   uint8_t pst[128];  // rows 0..3: P under the full scores, rows 4..7: under the coarse scores; 16 tokens each
   uint64_t bar[RefineShape<CB, FB>::NST];
@@ -809,13 +817,20 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
     while (pre[e + 1] <= k) ++e;
     return __ldcg(a.items + (size_t)e * SLICE + (k - pre[e]));
   };
+  long long issued_unit = -1;  // (lane 0) the (virtual head, group) of the last item issued, and which metadata buffer it uses
+  int issued_par = 1;
   auto issue = [&](int it, int e, int s) {  // lane 0
     const int vh = e / a.nslices, bh = vh / a.vg, sb = it >> 4;
     const size_t unit = (size_t)bh * a.hs + (size_t)(sb / SBG) * a.gs, rec = unit * SBG + sb % SBG;
-    mbar_expect_tx(&w.bar[s], Sh::STAGE);
+    const long long vu = (long long)vh * a.nblocks + sb / SBG;
+    const bool fresh = vu != issued_unit;  // the group's metadata travels with its first item only
+    mbar_expect_tx(&w.bar[s], Sh::STAGE + (fresh ? 1024 : 0));
     bulk_g2s(w.stage[s], a.c.coarse + rec * Sh::RC, Sh::RC, &w.bar[s]);
     bulk_g2s(w.stage[s] + Sh::RC, a.c.fine + rec * Sh::RF, Sh::RF, &w.bar[s]);
-    bulk_g2s(w.stage[s] + Sh::RC + Sh::RF, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
+    if (fresh) {
+      issued_unit = vu; issued_par ^= 1;
+      bulk_g2s(w.meta[issued_par], reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
+    }
   };
   int fit[Sh::NST];  // the items in flight (warp-uniform)
 #pragma unroll
@@ -834,8 +849,8 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
   float4 q4[QG];
   float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
   uint32_t B[8];
-  int cur_vh = -1;
-  long long cur_unit = -1;
+  int cur_vh = -1, cur_par = 1;
+  long long cur_unit = -1, cur_unit2 = -1;  // cur_unit is also reset when the virtual head changes; cur_unit2 follows the groups only
   for (int k = lo; k < hi; ++k) {
     const int s = (k - lo) % Sh::NST;
     const int it = item_at(k, ce), vh = ce / a.nslices, sb = it >> 4;
@@ -857,8 +872,10 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
       if (lane == 0) report(a, 3);
       return;
     }
-    const uint8_t *crec = w.stage[s], *frec = crec + Sh::RC, *meta = frec + Sh::RF;
+    const uint8_t *crec = w.stage[s], *frec = crec + Sh::RC;
     const long long unit = (long long)vh * a.nblocks + sb / SBG;
+    if (unit != cur_unit2) { cur_unit2 = unit; cur_par ^= 1; }  // (the same sequence of groups as the issuing side)
+    const uint8_t *meta = w.meta[cur_par];
     if (unit != cur_unit) {  // the group's qhat: the same function of the same inputs as the coarse pass
       cur_unit = unit;
       __syncwarp();

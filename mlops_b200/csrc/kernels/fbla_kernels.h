@@ -91,6 +91,22 @@ cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream
 int fbla_k_attend_tc_status(void);
 #define FBLA_K_TC_MIN_ROWS 64
 
+// ---- fused QKV step: RMSNorm + rotary embedding of new tokens (+ the window stores of the one-token step) ------------------
+typedef struct {
+  fbla_k_cache c;                 // token step only
+  const uint16_t *q, *k, *v;      // the projection's output
+  int64_t batch_stride, q_group_stride, kv_group_stride;  // elements; batch_stride is the row stride of a chunk
+  const uint16_t *q_norm, *k_norm;  // both or neither
+  const float *freq;              // 64 x (fh, fl, gh, gl)
+  float eps, att;
+  const int *length, *dcount;
+  int lstride, n0, max_count;
+  int batch, q_heads, kv_heads;
+  uint16_t *q_out, *k_out, *v_out;
+} fbla_k_token;
+cudaError_t fbla_k_qkv_token_launch(const fbla_k_token *a, cudaStream_t stream);
+cudaError_t fbla_k_qkv_chunk_launch(const fbla_k_token *a, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

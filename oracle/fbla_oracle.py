@@ -155,3 +155,27 @@ def exact_decode(q_bits, k_bits, v_bits, scale=None):
                                        _p(np.ascontiguousarray(q_bits[b])), _p(np.ascontiguousarray(k_bits[b])),
                                        _p(np.ascontiguousarray(v_bits[b])), _p(out[b]))
     return out
+
+
+def rope_freq(theta=1e6, n=64):
+    """The 64 x 4 float table of the rotary frequencies inv_freq = theta^(-2 i / 128), split as the kernels take them."""
+    inv = np.asarray([theta ** (-2.0 * i / (2 * n)) for i in range(n)], np.float64)
+    out = np.zeros((n, 4), np.float32)
+    lib().fbla_oracle_rope_freq(_p(inv), ctypes.c_int(n), _p(out))
+    return out
+
+
+def norm_rope(x_bits, w_bits, eps, pos, freq, att=1.0):
+    """x_bits [..., 128] uint16 (BF16) -> the head after the optional RMSNorm (w_bits 128 BF16 or None) and the rotation at
+    position pos (an int, or an array broadcastable to x's leading shape)."""
+    x = np.ascontiguousarray(x_bits, np.uint16)
+    out = np.zeros_like(x)
+    flat_x, flat_o = x.reshape(-1, 128), out.reshape(-1, 128)
+    posv = np.broadcast_to(np.asarray(pos, np.int64), x.shape[:-1]).reshape(-1)
+    w = None if w_bits is None else np.ascontiguousarray(w_bits, np.uint16)
+    f = np.ascontiguousarray(freq, np.float32)
+    fn = lib().fbla_oracle_norm_rope
+    fn.restype = None
+    for i in range(flat_x.shape[0]):
+        fn(_p(flat_x[i]), _p(w), ctypes.c_float(eps), ctypes.c_int(int(posv[i])), _p(f), ctypes.c_float(att), _p(flat_o[i]))
+    return out

@@ -23,6 +23,12 @@ class Cache(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in ("coarse", "fine", "meta", "sink_k", "sink_v", "open_k", "open_v", "images")]
 
 
+class Token(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("batch_stride", ctypes.c_int64),
+                ("q_group_stride", ctypes.c_int64), ("kv_group_stride", ctypes.c_int64), ("q_norm", ctypes.c_void_p), ("k_norm", ctypes.c_void_p),
+                ("eps", ctypes.c_float), ("freq", ctypes.c_void_p), ("attention_factor", ctypes.c_float), ("q_out", ctypes.c_void_p)]
+
+
 def bf16_tensor(bits, device="cuda"):
     """numpy uint16 BF16 bit patterns -> torch bfloat16 tensor on the device"""
     return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(device).view(torch.bfloat16)
@@ -60,6 +66,11 @@ class CLib:
         L.mlops_fbla_append_at.restype = ctypes.c_int
         L.mlops_fbla_append_at.argtypes = [cp, vp, vp, vp, kp, vp]
         L.mlops_fbla_last_error.restype = ctypes.c_char_p
+        tp = ctypes.POINTER(Token)
+        L.mlops_fbla_qkv_at.restype = ctypes.c_int
+        L.mlops_fbla_qkv_at.argtypes = [cp, vp, tp, kp, vp]
+        L.mlops_fbla_qkv_prefill_at.restype = ctypes.c_int
+        L.mlops_fbla_qkv_prefill_at.argtypes = [cp, vp, vp, ctypes.c_int, tp, vp, vp, vp, vp]
 
     def error(self):
         return self.lib.mlops_fbla_last_error().decode()
@@ -148,6 +159,40 @@ class CLib:
         st = self.lib.mlops_fbla_append_at(ctypes.byref(cfg), length.data_ptr(), k.data_ptr(), v.data_ptr(), ctypes.byref(kc), self._stream())
         if st:
             raise RuntimeError(f"append_at status {st}: {self.error()}")
+
+    @staticmethod
+    def _token(proj, q_heads, kv_heads, row_stride, q_norm, k_norm, eps, freq, att, q_out):
+        """proj: the projection's rows, per row [kv_heads][(qg + 2) * 128] = a KV head's q heads, then k, then v"""
+        qg = q_heads // kv_heads
+        base = proj.data_ptr()
+        return Token(base, base + 2 * qg * 128, base + 2 * (qg + 1) * 128, row_stride, (qg + 2) * 128, (qg + 2) * 128,
+                     q_norm.data_ptr() if q_norm is not None else None, k_norm.data_ptr() if k_norm is not None else None, eps, freq.data_ptr(),
+                     att, q_out.data_ptr() if q_out is not None else None)
+
+    def qkv_at(self, c, proj, q_heads, length, freq, q_norm=None, k_norm=None, eps=1e-6, att=0.0, tokens_offset=0, length_stride=0):
+        """proj [B, kv_heads * (qg + 2) * 128] bf16 (one token per sequence); returns q_out [B, q_heads, 128]; appends k, v."""
+        B, kvh = c["batch"], c["kv_heads"]
+        q_out = torch.empty((B, q_heads, 128), dtype=torch.bfloat16, device=proj.device)
+        cfg = Config(B, q_heads, kvh, tokens_offset, 0, 0, FORMATS[c["mode"]][2], c["capacity"], 0, 0, 0, 0, length_stride)
+        tok = self._token(proj, q_heads, kvh, proj.shape[1], q_norm, k_norm, eps, freq, att, q_out)
+        kc = self._cache(c)
+        st = self.lib.mlops_fbla_qkv_at(ctypes.byref(cfg), length.data_ptr(), ctypes.byref(tok), ctypes.byref(kc), self._stream())
+        if st:
+            raise RuntimeError(f"qkv_at status {st}: {self.error()}")
+        return q_out
+
+    def qkv_prefill_at(self, proj, q_heads, kv_heads, length, count, max_count, capacity, freq, q_norm=None, k_norm=None, eps=1e-6, att=0.0,
+                       tokens_offset=0, fill=None):
+        """proj [rows, kv_heads * (qg + 2) * 128] bf16; returns (q [q_heads, max_count, 128], k, v [kv_heads, max_count, 128])."""
+        mk = lambda h: (torch.empty if fill is None else lambda *a, **k: torch.full(*a, fill, **k))((h, max_count, 128), dtype=torch.bfloat16, device=proj.device)
+        q_out, k_out, v_out = mk(q_heads), mk(kv_heads), mk(kv_heads)
+        cfg = Config(1, q_heads, kv_heads, tokens_offset, 0, 0, 0, capacity, 0, 0, 0, 0, 0)
+        tok = self._token(proj, q_heads, kv_heads, proj.shape[1], q_norm, k_norm, eps, freq, att, None)
+        st = self.lib.mlops_fbla_qkv_prefill_at(ctypes.byref(cfg), length.data_ptr(), count.data_ptr(), max_count, ctypes.byref(tok),
+                                                q_out.data_ptr(), k_out.data_ptr(), v_out.data_ptr(), self._stream())
+        if st:
+            raise RuntimeError(f"qkv_prefill_at status {st}: {self.error()}")
+        return q_out, k_out, v_out
 
     def prefill_at(self, c, k, v, q, length, count, max_count, tokens_offset=0, out=None):
         """k, v [B, Hkv, max_count, 128], q [B, Hq, max_count, 128] or None; the chunk is their first *count positions."""
