@@ -40,6 +40,9 @@ def test_struct_sizes(C):
     assert ctypes.sizeof(C.Config) == 64 and ctypes.sizeof(C.Cache) == 64 and ctypes.sizeof(C.Sizes) == 40
     assert C.Config.scale.offset == 16 and C.Config.format.offset == 24 and C.Config.capacity.offset == 28
     assert C.Config.out_head_stride.offset == 40 and C.Config.length_stride.offset == 56
+    from tests import gpu_util
+    assert ctypes.sizeof(gpu_util.Token) == 96 and gpu_util.Token.eps.offset == 64 and gpu_util.Token.freq.offset == 72
+    assert gpu_util.Token.attention_factor.offset == 80 and gpu_util.Token.q_out.offset == 88
 
 
 def cfg(C, **kw):
@@ -114,3 +117,27 @@ def test_python_interface_rejects_without_cuda(C):
     if not torch.cuda.is_available():
         with pytest.raises(ValueError):
             attention.encode(k, k)  # not CUDA tensors
+
+
+def test_qkv_validation_without_a_device(C):
+    from tests import gpu_util
+    lib = C.lib
+    lib.mlops_fbla_qkv_at.restype = ctypes.c_int
+    lib.mlops_fbla_qkv_prefill_at.restype = ctypes.c_int
+    cache = C.Cache(*([0x1000] * 7), None)
+    tok = gpu_util.Token(0x1000, 0x1000, 0x1000, 1024, 768, 768, None, None, 1e-6, 0x1000, 0.0, 0x1000)
+    c = cfg(C, capacity=4096, tokens=0)
+    vp = ctypes.c_void_p
+    assert lib.mlops_fbla_qkv_at(ctypes.byref(c), None, ctypes.byref(tok), ctypes.byref(cache), None) == C.INVALID_VALUE and "null" in C.last_error()
+    tok.q_norm = 0x1000  # one norm weight without the other
+    assert lib.mlops_fbla_qkv_at(ctypes.byref(c), vp(0x1000), ctypes.byref(tok), ctypes.byref(cache), None) == C.INVALID_VALUE
+    assert "both or neither" in C.last_error()
+    tok.q_norm = None
+    tok.batch_stride = 1023  # odd stride
+    assert lib.mlops_fbla_qkv_at(ctypes.byref(c), vp(0x1000), ctypes.byref(tok), ctypes.byref(cache), None) == C.INVALID_VALUE
+    tok.batch_stride = 64  # a chunk row shorter than one head
+    st = lib.mlops_fbla_qkv_prefill_at(ctypes.byref(c), vp(0x1000), vp(0x1000), ctypes.c_int(8), ctypes.byref(tok), vp(0x1000), vp(0x1000), vp(0x1000), None)
+    assert st == C.INVALID_VALUE and "row" in C.last_error()
+    st = lib.mlops_fbla_qkv_prefill_at(ctypes.byref(cfg(C, batch=2, capacity=4096, tokens=0)), vp(0x1000), vp(0x1000), ctypes.c_int(8), ctypes.byref(tok),
+                                       vp(0x1000), vp(0x1000), vp(0x1000), None)
+    assert st == C.INVALID_VALUE and "batch 1" in C.last_error()
