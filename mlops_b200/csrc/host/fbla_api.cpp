@@ -6,6 +6,7 @@
 // host threads at once.
 #include "../../../include/mlops_fbla.h"
 #include "../../../include/mlops_fbla_shard.h"
+#include "../../../include/mlops_fbla_items.h"
 #include "../kernels/fbla_kernels.h"
 
 #include <cmath>
@@ -197,9 +198,9 @@ mlops_fbla_status run_prefill(const char *fn, const fbla_k_prefill &a, int close
   if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
   return ok();
 }
-mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
+mlops_fbla_status prefill_at_prepare(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
                              const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
-                             cudaStream_t stream) {
+                             fbla_k_prefill &a) {
   if (!c || !length || !cache || !k || !v) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
   if (q && !out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q needs output", fn);
   if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 ||
@@ -211,11 +212,18 @@ mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const i
   const mlops_fbla_status st = prefill_common(fn, c, q, k, v, cache, out);
   if (st != MLOPS_FBLA_OK) return st;
   if (!aligned(length, 4) || !aligned(dcount, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length and count must be 4-byte aligned", fn);
-  fbla_k_prefill a{};
+  a = fbla_k_prefill{};
   fill_prefill(c, max_count, c->capacity, q, k, v, cache, out, a);
   a.length = length; a.dcount = dcount; a.lstride = c->length_stride;
+  return MLOPS_FBLA_OK;
+}
+mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
+                             const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
+                             cudaStream_t stream) {
+  fbla_k_prefill a;
+  const mlops_fbla_status st = prefill_at_prepare(fn, c, length, dcount, max_count, q, k, v, cache, out, a);
   // a chunk of at most max_count tokens starting anywhere closes at most max_count / 128 + 1 groups
-  return run_prefill(fn, a, max_count / G + 1, stream);
+  return st != MLOPS_FBLA_OK ? st : run_prefill(fn, a, max_count / G + 1, stream);
 }
 
 }  // namespace
@@ -307,15 +315,15 @@ static mlops_fbla_status token_common(const char *fn, const mlops_fbla_token *t,
   return MLOPS_FBLA_OK;
 }
 
-mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
-                                    cudaStream_t stream) {
+static mlops_fbla_status qkv_at_prepare(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
+                                        fbla_k_prefill &cl, fbla_k_token &a) {
   constexpr const char *fn = "mlops_fbla_qkv_at";
   if (!c || !length || !t || !cache || !t->q || !t->k || !t->v || !t->freq || !t->q_out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
   if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 || !valid_strides(c))
     return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch and heads must be positive, q_heads a multiple of kv_heads, tokens >= 0, capacity positive, "
                 "strides both 0 or both positive", fn);
   if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
-  fbla_k_token a{};
+  a = fbla_k_token{};
   mlops_fbla_status st = token_common(fn, t, a);
   if (st != MLOPS_FBLA_OK) return st;
   if (!cache_complete(cache)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
@@ -333,19 +341,27 @@ mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *c, const int *lengt
   if (!aligned(cache->tc_images, 128)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: tc_images must be 128-byte aligned", fn);
   if (c->length_stride != 0 && c->length_stride != 1) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0 or 1", fn);
   // the group that the position closes (when it is a multiple of 128) is quantized from the open window first
-  fbla_k_prefill cl{};
+  cl = fbla_k_prefill{};
   fill_prefill(c, 1, c->capacity, nullptr, nullptr, nullptr, cache, nullptr, cl);
   cl.length = length; cl.lstride = c->length_stride;
   a.c = cl.c; a.length = length; a.lstride = c->length_stride; a.n0 = c->tokens; a.max_count = 1;
   a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads; a.q_out = t->q_out;
+  return MLOPS_FBLA_OK;
+}
+mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
+                                    cudaStream_t stream) {
+  fbla_k_prefill cl;
+  fbla_k_token a;
+  const mlops_fbla_status st = qkv_at_prepare(c, length, t, cache, cl, a);
+  if (st != MLOPS_FBLA_OK) return st;
   cudaError_t e = fbla_k_close_launch(&cl, 1, stream);
   if (e == cudaSuccess) e = fbla_k_qkv_token_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "mlops_fbla_qkv_at: %s", cudaGetErrorString(e));
   return ok();
 }
 
-mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
-                                            uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, cudaStream_t stream) {
+static mlops_fbla_status qkv_chunk_prepare(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
+                                           uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, fbla_k_token &a) {
   constexpr const char *fn = "mlops_fbla_qkv_prefill_at";
   if (!c || !length || !count || !t || !t->q || !t->k || !t->v || !t->freq || !q_out || !k_out || !v_out)
     return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
@@ -353,7 +369,7 @@ mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const in
       (long long)c->tokens + max_count > c->capacity)
     return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch 1, positive heads (q_heads a multiple of kv_heads), tokens >= 0, max_count > 0, "
                 "tokens + max_count <= capacity", fn);
-  fbla_k_token a{};
+  a = fbla_k_token{};
   mlops_fbla_status st = token_common(fn, t, a);
   if (st != MLOPS_FBLA_OK) return st;
   if (t->batch_stride < D || t->batch_stride % 2 || t->q_group_stride % 2 || t->kv_group_stride % 2 || t->q_group_stride < 0 || t->kv_group_stride < 0)
@@ -367,8 +383,15 @@ mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const in
   a.length = length; a.dcount = count; a.n0 = c->tokens; a.max_count = max_count;
   a.batch = 1; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads;
   a.q_out = q_out; a.k_out = k_out; a.v_out = v_out;
+  return MLOPS_FBLA_OK;
+}
+mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
+                                            uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, cudaStream_t stream) {
+  fbla_k_token a;
+  const mlops_fbla_status st = qkv_chunk_prepare(c, length, count, max_count, t, q_out, k_out, v_out, a);
+  if (st != MLOPS_FBLA_OK) return st;
   const cudaError_t e = fbla_k_qkv_chunk_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "mlops_fbla_qkv_prefill_at: %s", cudaGetErrorString(e));
   return ok();
 }
 
@@ -424,6 +447,266 @@ mlops_fbla_status mlops_fbla_shard_combine(int rows, const float *partial_sum, u
   const cudaError_t e = fbla_k_combine_launch(partial_sum, output, rows, stream);
   if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
   return ok();
+}
+
+// ---- work items (include/mlops_fbla_items.h; reference: attention/fbla/src/fbla_kernels.cuh:1446-1510 plan builders,
+// attention/fbla/src/fbla.cu:587-810 access ranges) -------------------------------------------------------------------------
+extern "C++" {
+namespace {
+// geometry slots of this library beyond the shared ones: 3 = item_off offset, 4 = status offset (decode scratch);
+// 3 = the chunk's ceiling (prefill family)
+template <class A> bool fill_pass(mlops_fbla_items &p, int kind, const fbla_k_pass &k, const char *args_type, const A &args) {
+  static_assert(sizeof(A) <= MLOPS_FBLA_ITEM_ARGS_BYTES, "argument structure exceeds the blob");
+  memset(&p, 0, sizeof p);
+  p.kind = kind; p.items = k.gx * k.gy * k.gz; p.threads = k.threads; p.smem_bytes = k.smem_bytes; p.regs = k.regs; p.arch = 100;
+  snprintf(p.entry, sizeof p.entry, "%s", k.entry);
+  snprintf(p.args_type, sizeof p.args_type, "%s", args_type);
+  p.args_bytes = (int)sizeof(A);
+  memcpy(p.args.bytes, &args, sizeof(A));
+  p.geom[MLOPS_FBLA_GEOM_GRID_X] = k.gx; p.geom[MLOPS_FBLA_GEOM_GRID_Y] = k.gy; p.geom[MLOPS_FBLA_GEOM_GRID_Z] = k.gz;
+  return true;
+}
+void cache_geom(mlops_fbla_items &p, int hs, int gs, long long capacity, int cb, int fb) {
+  p.geom[MLOPS_FBLA_GEOM_HEAD_STRIDE] = hs; p.geom[MLOPS_FBLA_GEOM_GROUP_STRIDE] = gs;
+  p.geom[MLOPS_FBLA_GEOM_CAPACITY_GROUPS] = (capacity + G - 1) / G;
+  p.geom[MLOPS_FBLA_GEOM_COARSE_BYTES] = 2 * cb * 256; p.geom[MLOPS_FBLA_GEOM_FINE_BYTES] = 2 * fb * 256;
+}
+int plan_fail(const cudaError_t e, const char *fn) {
+  fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  return -1;
+}
+
+struct Ranges {
+  mlops_fbla_item_range *out;
+  int max, n;
+  void add(int arg, int write, long long offset, long long bytes, long long stride = 0, int rows = 1) {
+    if (bytes <= 0 || rows <= 0) return;
+    if (n < max) out[n] = mlops_fbla_item_range{arg, write, offset, bytes, rows > 1 ? stride : bytes, rows};
+    ++n;
+  }
+};
+// the units of KV head h (all groups the layout holds): records and metadata
+void head_units(Ranges &r, const mlops_fbla_items &p, int h, int write, bool coarse, bool fine, bool meta) {
+  const long long hs = p.geom[MLOPS_FBLA_GEOM_HEAD_STRIDE], gs = p.geom[MLOPS_FBLA_GEOM_GROUP_STRIDE], cg = p.geom[MLOPS_FBLA_GEOM_CAPACITY_GROUPS];
+  const long long uc = SBG * p.geom[MLOPS_FBLA_GEOM_COARSE_BYTES], uf = SBG * p.geom[MLOPS_FBLA_GEOM_FINE_BYTES];
+  if (coarse) r.add(MLOPS_FBLA_ARG_COARSE, write, h * hs * uc, uc, gs * uc, (int)cg);
+  if (fine) r.add(MLOPS_FBLA_ARG_FINE, write, h * hs * uf, uf, gs * uf, (int)cg);
+  if (meta) r.add(MLOPS_FBLA_ARG_META, write, h * hs * 1024, 1024, gs * 1024, (int)cg);
+}
+void head_windows(Ranges &r, int h, int write, bool sink, bool open) {
+  const long long w = (long long)G * D * 2;
+  if (sink) { r.add(MLOPS_FBLA_ARG_SINK_K, write, h * w, w); r.add(MLOPS_FBLA_ARG_SINK_V, write, h * w, w); }
+  if (open) { r.add(MLOPS_FBLA_ARG_OPEN_K, write, h * w, w); r.add(MLOPS_FBLA_ARG_OPEN_V, write, h * w, w); }
+}
+}  // namespace
+}  // extern "C++"
+
+int mlops_fbla_decode_at_items(const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k, uint16_t *out,
+                               void *scratch, size_t scratch_bytes, int /*per_head*/, mlops_fbla_items *passes, int max) {
+  constexpr const char *fn = "mlops_fbla_decode_at_items";
+  if (!length) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: null length", fn); return -1; }
+  if (c && c->capacity <= 0) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: capacity must be positive", fn); return -1; }
+  fbla_k_decode a;
+  if (prepare_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { ok(); return 4; }
+  if (!passes || max < 4) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 4 passes is needed", fn); return -1; }
+  fbla_k_pass info[4];
+  const cudaError_t e = fbla_k_decode_passes(&a, info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  const int kinds[4] = {MLOPS_FBLA_ITEM_COARSE, MLOPS_FBLA_ITEM_SELECT, MLOPS_FBLA_ITEM_REFINE, MLOPS_FBLA_ITEM_MERGE};
+  const char *base = static_cast<const char *>(scratch);
+  for (int i = 0; i < 4; ++i) {
+    mlops_fbla_items &p = passes[i];
+    fill_pass(p, kinds[i], info[i], "fbla_k_decode", a);
+    cache_geom(p, a.hs, a.gs, c->capacity, a.cb, a.fb);
+    p.geom[MLOPS_FBLA_GEOM_LSE] = (const char *)a.lse - base; p.geom[MLOPS_FBLA_GEOM_PART] = (const char *)a.part - base;
+    p.geom[MLOPS_FBLA_GEOM_DPART] = (const char *)a.dpart - base; p.geom[MLOPS_FBLA_GEOM_ROW_LSE] = (const char *)a.row_r - base;
+    p.geom[MLOPS_FBLA_GEOM_ITEMS] = (const char *)a.items - base; p.geom[MLOPS_FBLA_GEOM_COUNTS] = (const char *)a.counts - base;
+    p.geom[3] = (const char *)a.item_off - base; p.geom[4] = (const char *)a.status - base;
+  }
+  ok();
+  return 4;
+}
+
+static int prefill_items(const char *fn, const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q,
+                         const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out, mlops_fbla_items *passes, int max) {
+  fbla_k_prefill a;
+  if (prefill_at_prepare(fn, c, length, count, max_count, q, k, v, cache, out, a) != MLOPS_FBLA_OK) return -1;
+  const int n = q ? 3 : 2;
+  if (max == 0) { ok(); return n; }
+  if (!passes || max < n) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for %d passes is needed", fn, n); return -1; }
+  fbla_k_pass info;
+  int at = 0, tensor = 0;
+  cudaError_t e = fbla_k_close_pass(&a, max_count / G + 1, &info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  fill_pass(passes[at++], MLOPS_FBLA_ITEM_CLOSE, info, "fbla_k_prefill", a);
+  if (q) {
+    e = fbla_k_attend_pass(&a, &info, &tensor);
+    if (e != cudaSuccess) return plan_fail(e, fn);
+    fill_pass(passes[at++], tensor ? MLOPS_FBLA_ITEM_TC : MLOPS_FBLA_ITEM_STREAM, info, "fbla_k_prefill", a);
+  }
+  e = fbla_k_finish_pass(&a, &info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  fill_pass(passes[at++], MLOPS_FBLA_ITEM_FINISH, info, "fbla_k_prefill", a);
+  for (int i = 0; i < at; ++i) { cache_geom(passes[i], a.hs, a.gs, c->capacity, a.cb, a.fb); passes[i].geom[3] = max_count; }
+  ok();
+  return at;
+}
+
+int mlops_fbla_prefill_at_items(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q, const uint16_t *k,
+                                const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out, mlops_fbla_items *passes, int max) {
+  if (!count) { fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_prefill_at_items: null argument"); return -1; }
+  return prefill_items("mlops_fbla_prefill_at_items", c, length, count, max_count, q, k, v, cache, out, passes, max);
+}
+
+int mlops_fbla_append_at_items(const mlops_fbla_config *c, const int *length, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache,
+                               mlops_fbla_items *passes, int max) {
+  return prefill_items("mlops_fbla_append_at_items", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, passes, max);
+}
+
+int mlops_fbla_qkv_at_items(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
+                            mlops_fbla_items *passes, int max) {
+  constexpr const char *fn = "mlops_fbla_qkv_at_items";
+  fbla_k_prefill cl;
+  fbla_k_token a;
+  if (qkv_at_prepare(c, length, t, cache, cl, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { ok(); return 2; }
+  if (!passes || max < 2) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 2 passes is needed", fn); return -1; }
+  fbla_k_pass info;
+  cudaError_t e = fbla_k_close_pass(&cl, 1, &info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  fill_pass(passes[0], MLOPS_FBLA_ITEM_CLOSE, info, "fbla_k_prefill", cl);
+  e = fbla_k_qkv_token_pass(&a, &info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  fill_pass(passes[1], MLOPS_FBLA_ITEM_QKV, info, "fbla_k_token", a);
+  for (int i = 0; i < 2; ++i) { cache_geom(passes[i], cl.hs, cl.gs, c->capacity, cl.cb, cl.fb); passes[i].geom[3] = 1; }
+  ok();
+  return 2;
+}
+
+int mlops_fbla_qkv_prefill_at_items(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
+                                    uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, mlops_fbla_items *passes, int max) {
+  constexpr const char *fn = "mlops_fbla_qkv_prefill_at_items";
+  fbla_k_token a;
+  if (qkv_chunk_prepare(c, length, count, max_count, t, q_out, k_out, v_out, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { ok(); return 1; }
+  if (!passes || max < 1) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 1 pass is needed", fn); return -1; }
+  fbla_k_pass info;
+  const cudaError_t e = fbla_k_qkv_chunk_pass(&a, &info);
+  if (e != cudaSuccess) return plan_fail(e, fn);
+  fill_pass(passes[0], MLOPS_FBLA_ITEM_QKV_CHUNK, info, "fbla_k_token", a);
+  passes[0].geom[3] = max_count;
+  ok();
+  return 1;
+}
+
+int mlops_fbla_item_call(const mlops_fbla_items *p, char *out, size_t capacity) {
+  if (!p || !out || p->kind < MLOPS_FBLA_ITEM_CLOSE || p->kind > MLOPS_FBLA_ITEM_QKV_CHUNK || !p->entry[0]) return -1;
+  const int n = snprintf(out, capacity,
+                         "mlops_fbla::position(item, %lld, %lld, %lld); __syncthreads(); "
+                         "%s(*reinterpret_cast<const %s *>(args), reinterpret_cast<unsigned char *>(sm));",
+                         p->geom[0], p->geom[1], p->geom[2], p->entry, p->args_type);
+  return n < 0 || (size_t)n >= capacity ? -1 : n;
+}
+
+int mlops_fbla_item_access(const mlops_fbla_items *passes, int npasses, int pass, int item, mlops_fbla_item_range *ranges, int max) {
+  if (!passes || pass < 0 || pass >= npasses || max < 0 || (max > 0 && !ranges)) return -1;
+  const mlops_fbla_items &p = passes[pass];
+  if (item < 0 || item >= p.items) return -1;
+  Ranges r{ranges, max, 0};
+  const int x = item % (int)p.geom[0], y = (item / (int)p.geom[0]) % (int)p.geom[1];
+  const long long row = D * 2;  // bytes of one head vector
+  if (p.kind >= MLOPS_FBLA_ITEM_COARSE && p.kind <= MLOPS_FBLA_ITEM_MERGE) {
+    fbla_k_decode a;
+    memcpy(&a, p.args.bytes, sizeof a);
+    const int heads = a.batch * a.kv_heads, hpr = a.kv_heads * a.vg, vheads = a.batch * hpr;
+    const long long lse = p.geom[MLOPS_FBLA_GEOM_LSE], part = p.geom[MLOPS_FBLA_GEOM_PART], dpart = p.geom[MLOPS_FBLA_GEOM_DPART];
+    const long long row_r = p.geom[MLOPS_FBLA_GEOM_ROW_LSE], items = p.geom[MLOPS_FBLA_GEOM_ITEMS], counts = p.geom[MLOPS_FBLA_GEOM_COUNTS];
+    const long long item_off = p.geom[3], status = p.geom[4];
+    r.add(MLOPS_FBLA_ARG_LENGTH, 0, 0, 4, 4, a.lstride ? a.batch : 1);
+    if (p.kind == MLOPS_FBLA_ITEM_COARSE || p.kind == MLOPS_FBLA_ITEM_REFINE) {
+      // a persistent CTA's unit range depends on the device length: every head's units are the envelope
+      r.add(MLOPS_FBLA_ARG_Q, 0, 0, (long long)a.batch * a.q_heads * row);
+      for (int h = 0; h < heads; ++h) head_units(r, p, h, 0, true, p.kind == MLOPS_FBLA_ITEM_REFINE, true);
+    }
+    if (p.kind == MLOPS_FBLA_ITEM_COARSE) {
+      for (int h = 0; h < heads; ++h) head_windows(r, h, 0, true, true);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, lse, part - lse);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, part, dpart - part);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, status, 16);
+    } else if (p.kind == MLOPS_FBLA_ITEM_SELECT) {
+      const long long per = (long long)a.nblocks * a.qg * 4;
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, lse + y * per, per);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, part, dpart - part);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, row_r + (long long)y * a.qg * 4, a.qg * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, counts + ((long long)y * a.nslices + x) * 4, 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, items + ((long long)y * a.nslices + x) * FBLA_K_SLICE * 4, FBLA_K_SLICE * 4);
+    } else if (p.kind == MLOPS_FBLA_ITEM_REFINE) {
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, row_r, (long long)vheads * a.qg * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, counts, (long long)vheads * a.nslices * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, items, (long long)vheads * a.nslices * FBLA_K_SLICE * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, dpart, row_r - dpart);
+      if (x == 0) r.add(MLOPS_FBLA_ARG_SCRATCH, 1, item_off, (long long)(vheads + 1) * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 1, status, 16);
+    } else {
+      const int vh = item / a.qg, qi = item % a.qg, b = vh / hpr, hir = vh % hpr;
+      const long long qrow = (long long)b * a.q_heads + (hir / a.vg) * (a.qg * a.vg) + (hir % a.vg) * a.qg + qi;
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, part, dpart - part);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, dpart, row_r - dpart);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, row_r + (long long)vh * a.qg * 4, a.qg * 4);
+      r.add(MLOPS_FBLA_ARG_SCRATCH, 0, item_off, (long long)(vheads + 1) * 4);
+      r.add(MLOPS_FBLA_ARG_OUT, 1, qrow * row, row);
+    }
+  } else if (p.kind == MLOPS_FBLA_ITEM_QKV || p.kind == MLOPS_FBLA_ITEM_QKV_CHUNK) {
+    fbla_k_token a;
+    memcpy(&a, p.args.bytes, sizeof a);
+    const int qg = a.q_heads / a.kv_heads;
+    r.add(MLOPS_FBLA_ARG_TFREQ, 0, 0, 64 * 16);
+    if (a.q_norm) { r.add(MLOPS_FBLA_ARG_TQN, 0, 0, row); r.add(MLOPS_FBLA_ARG_TKN, 0, 0, row); }
+    if (p.kind == MLOPS_FBLA_ITEM_QKV) {
+      const int b = x / a.kv_heads, kh = x % a.kv_heads;
+      r.add(MLOPS_FBLA_ARG_LENGTH, 0, 0, 4, 4, a.lstride ? a.batch : 1);
+      r.add(MLOPS_FBLA_ARG_TQ, 0, (b * a.batch_stride + kh * a.q_group_stride) * 2, qg * row);
+      r.add(MLOPS_FBLA_ARG_TK, 0, (b * a.batch_stride + kh * a.kv_group_stride) * 2, row);
+      r.add(MLOPS_FBLA_ARG_TV, 0, (b * a.batch_stride + kh * a.kv_group_stride) * 2, row);
+      r.add(MLOPS_FBLA_ARG_TQ_OUT, 1, ((long long)b * a.q_heads + kh * qg) * row, qg * row);
+      head_windows(r, x, 1, true, true);
+    } else {
+      const long long i0 = 8LL * x, rows = a.max_count - i0 < 8 ? a.max_count - i0 : 8;
+      r.add(MLOPS_FBLA_ARG_LENGTH, 0, 0, 4);
+      r.add(MLOPS_FBLA_ARG_COUNT, 0, 0, 4);
+      r.add(MLOPS_FBLA_ARG_TQ, 0, (i0 * a.batch_stride + y * a.q_group_stride) * 2, qg * row, a.batch_stride * 2, (int)rows);
+      r.add(MLOPS_FBLA_ARG_TK, 0, (i0 * a.batch_stride + y * a.kv_group_stride) * 2, row, a.batch_stride * 2, (int)rows);
+      r.add(MLOPS_FBLA_ARG_TV, 0, (i0 * a.batch_stride + y * a.kv_group_stride) * 2, row, a.batch_stride * 2, (int)rows);
+      r.add(MLOPS_FBLA_ARG_Q, 1, (((long long)y * qg) * a.max_count + i0) * row, rows * row, a.max_count * row, qg);
+      r.add(MLOPS_FBLA_ARG_K, 1, ((long long)y * a.max_count + i0) * row, rows * row);
+      r.add(MLOPS_FBLA_ARG_V, 1, ((long long)y * a.max_count + i0) * row, rows * row);
+    }
+  } else {
+    fbla_k_prefill a;
+    memcpy(&a, p.args.bytes, sizeof a);
+    const int qg = a.q_heads / a.kv_heads;
+    const int h = p.kind == MLOPS_FBLA_ITEM_FINISH ? x : y, b = h / a.kv_heads, kh = h % a.kv_heads;  // the KV head of the item
+    const long long chunk = (long long)a.count * row;
+    if (a.length) r.add(MLOPS_FBLA_ARG_LENGTH, 0, 0, 4, 4, a.lstride ? a.batch : 1);
+    if (a.dcount) r.add(MLOPS_FBLA_ARG_COUNT, 0, 0, 4);
+    if (a.k) { r.add(MLOPS_FBLA_ARG_K, 0, h * chunk, chunk); r.add(MLOPS_FBLA_ARG_V, 0, h * chunk, chunk); }
+    if (p.kind == MLOPS_FBLA_ITEM_CLOSE) {  // which group closes depends on the device length: the head's units are the envelope
+      head_windows(r, h, 0, true, true);
+      head_units(r, p, h, 1, true, true, true);
+    } else if (p.kind == MLOPS_FBLA_ITEM_FINISH) {
+      head_windows(r, h, 1, true, true);
+    } else {
+      head_units(r, p, h, 0, true, true, true);
+      head_windows(r, h, 0, true, true);
+      for (int t = 0; t < qg; ++t) {
+        const long long hq = (long long)b * a.q_heads + kh * qg + t;
+        r.add(MLOPS_FBLA_ARG_Q, 0, hq * chunk, chunk);
+        r.add(MLOPS_FBLA_ARG_OUT, 1, hq * a.out_hs * 2, row, (long long)a.out_ts * 2, a.count);
+      }
+    }
+  }
+  return r.n;
 }
 
 const char *mlops_fbla_status_string(mlops_fbla_status status) {

@@ -1,1061 +1,28 @@
-// FBLA compressed-KV decode for sm_100a: coarse pass (+ the BF16 windows), select, refine, merge.
-//
-// Semantics follow the reference's decode (attention/fbla/src/fbla_kernels.cuh:315-359 qhat, :479-533 coarse blocks,
-// :866-920 select, :1036-1072 refine, :1270-1294 merge): per (query, group) int8 qhat, 16-token P blocks of integers
-// p = round(255 * 2^(s - max)), coarse cells decoded at their midpoint, blocks with 2^(lse_j - R) > tau corrected by
-// (full - coarse). The structure is new:
-//   * a persistent grid, one CTA per SM; every warp owns a contiguous range of the flattened list of closed
-//     (virtual head, group) units and a private 2-stage ring in shared memory that whole groups (8 records + 1 KiB
-//     metadata) are streamed into by 1-D bulk asynchronous copies completing on mbarriers (all waits bounded);
-//   * scores and values are integer tensor-core products taken straight from the packed records (fbla_frag.cuh):
-//     tokens on M for S^T = K_codes qhat^T, channels on M for O^T = V_codes^T P^T, both P blocks of a record pair
-//     in the 8 columns of one product; the instruction count per byte no longer grows with the GQA ratio;
-//   * one extra warp per CTA serves the BF16 sink / open windows with plain loads and FP32 FMAs.
-// Reduction orders are fixed by (warp, unit) ranges alone, so outputs are bit-reproducible run to run.
-#include "fbla_frag.cuh"
-#include "fbla_kernels.h"
+// Launchers of the decode passes (bodies: fbla_decode.cuh).
+#include "fbla_decode.cuh"
+#include <stdio.h>
 
 namespace fbla {
-
-constexpr int PSTRIDE = FBLA_K_PSTRIDE;  // floats of one partial row: o[128], m, l, 2 pad (coarse); o[128], dl, 3 pad (refine)
-constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
-
-// Streaming warps per CTA and ring slots per warp, per coarse bit width. A slot holds one record pair (32 tokens);
-// the group's metadata has two slots of its own. NP <= 4 (one group of lookahead) keeps two metadata slots enough.
-#ifndef FBLA_RW
-#define FBLA_RW 12   /* refine warps per CTA */
-#endif
-#ifndef FBLA_RNST
-#define FBLA_RNST 2  /* refine ring stages per warp */
-#endif
-#ifndef FBLA_CW4
-#define FBLA_CW4 10
-#endif
-#ifndef FBLA_CW3
-#define FBLA_CW3 10
-#endif
-#ifndef FBLA_NP
-#define FBLA_NP 2
-#endif
-#ifndef FBLA_PPC
-#define FBLA_PPC 2  // record pairs per chunk (one bulk copy, one barrier wait)
-#endif
-template <int CB> struct CoarseShape {
-  static constexpr int WARPS = CB == 4 ? FBLA_CW4 : FBLA_CW3;
-  static constexpr int NP = FBLA_NP;
-  static constexpr int PPC = FBLA_PPC, CPG = 4 / FBLA_PPC;  // pairs per chunk, chunks per group
-  static constexpr int PAIR_BYTES = 2 * record_bytes(CB), CHUNK_BYTES = FBLA_PPC * PAIR_BYTES;
-  static constexpr int GROUP_BYTES = SBG * record_bytes(CB);
-};
-static_assert(FBLA_RNST == 2, "the refine pass keeps the metadata of two groups");
-static_assert(FBLA_NP >= 2 && FBLA_NP * FBLA_PPC <= 4 && 4 % FBLA_PPC == 0, "ring slots per warp: at most one group of lookahead");
-
-// ---- where a batch row's tokens put its units -----------------------------------------------------------------------
-struct Row { int tokens, groups, g0, closed, na, exact; };  // g0: the first closed group processed; na: sink sub-blocks
-__device__ __forceinline__ Row row_of(const fbla_k_decode &a, int b) {
-  Row r;
-  r.tokens = (a.length ? __ldg(a.length + (a.lstride ? b : 0)) : 0) + a.tokens;
-  r.groups = (r.tokens + G - 1) / G;
-  int first = 1, last = r.groups - 1, win = 3;  // closed groups [first, last); the whole cache: 1 .. groups - 2
-  if (a.shard_on) { first = a.sh_first; last = min(last, a.sh_first + a.sh_count); win = a.sh_windows; }
-  r.g0 = first;
-  r.closed = max(last - first, 0);
-  r.na = !(win & 1) ? 0 : r.groups == 1 ? (r.tokens + S - 1) / S : (r.groups >= 2 ? SBG : 0);
-  // the open window: the last group's tokens; a cache of one group is read through its sink window unless only the open one is asked for
-  const int no = !(win & 2) ? 0 : r.groups >= 2 ? (r.tokens - G * (r.groups - 1) + S - 1) / S : (win & 1) ? 0 : (r.tokens + S - 1) / S;
-  r.exact = r.na + no;  // BF16 sub-blocks: the sink's, then the open group's
-  return r;
-}
-// Flattened unit lists. Closed groups: row b contributes hpr * closed(b) units, head-major. BF16 sub-blocks likewise.
-// A cursor walks one list; every warp builds its own from the row lengths (no shared state, no limit on the batch).
-struct Cursor {
-  int b, hir, i, n;  // batch row, virtual head within the row, index within the head's n units
-};
-// the group of closed-group cursor c
-__device__ __forceinline__ int group_of(const fbla_k_decode &a, const Cursor &c) { return row_of(a, c.b).g0 + c.i; }
-template <bool EXACT>
-__device__ __forceinline__ int units_of(const Row &r) { return EXACT ? r.exact : r.closed; }
-
-// (one length for every batch row: closed forms, no loop over the batch)
-template <bool EXACT>
-__device__ __forceinline__ long long total_units(const fbla_k_decode &a, int hpr) {
-  if (!a.lstride) return (long long)a.batch * hpr * units_of<EXACT>(row_of(a, 0));
-  long long t = 0;
-  for (int b = 0; b < a.batch; ++b) t += (long long)hpr * units_of<EXACT>(row_of(a, b));
-  return t;
-}
-// the cursor of flattened unit u (u < total)
-template <bool EXACT>
-__device__ __forceinline__ Cursor locate(const fbla_k_decode &a, int hpr, long long u) {
-  Cursor c{0, 0, 0, 0};
-  if (!a.lstride) {
-    const int n = units_of<EXACT>(row_of(a, 0)), h = (int)(u / n);
-    c.b = h / hpr; c.hir = h - c.b * hpr; c.i = (int)(u - (long long)h * n); c.n = n;
-    return c;
-  }
-  for (int b = 0; b < a.batch; ++b) {
-    const int n = units_of<EXACT>(row_of(a, b));
-    const long long span = (long long)hpr * n;
-    if (u < span) { c.b = b; c.hir = (int)(u / n); c.i = (int)(u % n); c.n = n; return c; }
-    u -= span;
-  }
-  c.b = a.batch;
-  return c;
-}
-template <bool EXACT>
-__device__ __forceinline__ void advance(const fbla_k_decode &a, int hpr, Cursor &c) {
-  if (++c.i < c.n) return;
-  c.i = 0;
-  if (++c.hir < hpr) return;
-  c.hir = 0;
-  for (++c.b; c.b < a.batch; ++c.b) {
-    c.n = units_of<EXACT>(row_of(a, c.b));
-    if (c.n) return;
-  }
-}
-// first flattened unit of virtual head vh, and the head's unit count
-template <bool EXACT>
-__device__ __forceinline__ long long head_offset(const fbla_k_decode &a, int hpr, int vh, int &n) {
-  if (!a.lstride) { n = units_of<EXACT>(row_of(a, 0)); return (long long)vh * n; }
-  const int bq = vh / hpr, hir = vh - bq * hpr;
-  long long off = 0;
-  for (int b = 0; b < bq; ++b) off += (long long)hpr * units_of<EXACT>(row_of(a, b));
-  n = units_of<EXACT>(row_of(a, bq));
-  return off + (long long)hir * n;
-}
-__device__ __forceinline__ long long ceil_div(long long a, long long b) { return (a + b - 1) / b; }
-
-// q row (batch b, virtual head hir = kh * vg + j, query qi) in q / out
-__device__ __forceinline__ int q_row(const fbla_k_decode &a, int b, int hir, int qi) {
-  const int kh = hir / a.vg, j = hir - kh * a.vg;
-  return b * a.q_heads + kh * (a.q_heads / a.kv_heads) + j * a.qg + qi;
-}
-
-// ---- per-group query quantization (the definition of include/mlops_fbla.h) --------------------------------------------
-// Lane l holds channels 4 l .. 4 l + 3: km = the lane's 16 metadata bytes of K (4 bases, 4 steps), q4 = its 4 q values.
-// Writes the lane's qhat word to qst_row[l]; returns through the references the warp-uniform sq, qb (= sl q . base),
-// qsum (= sum qhat).
-__device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, uint32_t *qst_row, int lane, float &sq, float &qb, float &qsum) {
-  const float kb[4] = {bf_lo(km.x), bf_hi(km.x), bf_lo(km.y), bf_hi(km.y)}, ks[4] = {bf_lo(km.z), bf_hi(km.z), bf_lo(km.w), bf_hi(km.w)};
-  const float qf[4] = {q4.x, q4.y, q4.z, q4.w};
-  float z[4], amax = 0.f, dot = 0.f;
-#pragma unroll
-  for (int x = 0; x < 4; ++x) { z[x] = __fmul_rn(qf[x], ks[x]); amax = fmaxf(amax, fabsf(z[x])); dot = fmaf(qf[x], kb[x], dot); }
-  amax = __uint_as_float(__reduce_max_sync(FULL, __float_as_uint(amax)));  // amax >= 0: the bit patterns order as the values
-  // r = fl(127 / amax), correctly rounded: reciprocal seed, one Newton step, quotient and its residual correction
-  float rc;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(amax));
-  rc = fmaf(fmaf(-amax, rc, 1.f), rc, rc);
-  const float q0 = __fmul_rn(127.f, rc);
-  const float r = amax > 0.f ? fmaf(fmaf(-amax, q0, 127.f), rc, q0) : 0.f;
-  uint32_t word = 0;
-#pragma unroll
-  for (int x = 0; x < 4; ++x)  // rint(z r) in the low mantissa bits: one rounding of the exact product
-    word |= (__float_as_uint(fmaf(z[x], r, MAGICF)) & 255u) << (8 * x);
-  qst_row[lane] = word;
-  sq = __fmul_rn(amax, __fmul_rn(sl, 1.f / 127.f));
-  qb = __fmul_rn(warp_sum(dot), sl);
-  qsum = (float)__reduce_add_sync(FULL, __dp4a((int)word, 0x01010101, 0));  // the exact integer sum of the codes
-}
-
-// ---- shared memory of the coarse kernel ---------------------------------------------------------------------------------
-template <int CB> struct __align__(128) StreamWarp {
-  uint8_t pair[CoarseShape<CB>::NP][CoarseShape<CB>::CHUNK_BYTES];  // ring of chunks (PPC record pairs each)
-  uint8_t meta[2][1024];                                           // metadata of the group in progress and of the next
-  uint8_t qst[8 * QST_ROW];  // qhat rows (rows >= QG stay zero)
-  uint8_t pst[128];          // P bytes of a record pair: [block parity][query 0..3][16 tokens]
-  uint64_t bar_pair[CoarseShape<CB>::NP], bar_meta[2];
-};
-struct __align__(16) ExactWarp {
-  float q[4][D];
-  uint8_t pst[4][16];
-};
-constexpr int XWARPS = FBLA_K_WINDOW_WARPS;
-template <int CB> struct CoarseSmem {
-  StreamWarp<CB> w[CoarseShape<CB>::WARPS];
-  ExactWarp x[XWARPS];
-};
-
-// Programmatic dependent launch: the next pass of a decode is launched while this one still runs (hiding its launch
-// latency) and waits here until the previous pass has completed and its writes are visible.
-__device__ __forceinline__ void wait_previous_pass() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void allow_next_pass() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
-  if (a.status) { atomicCAS(a.status, 0, pass); a.status[1] = blockIdx.x; }
-}
-
-// ---- the BF16 windows: one warp per CTA ----------------------------------------------------------------------------------
-// Unit = one 16-token sub-block of the sink (first) or the open window. Scores s = sl * (q . k) in FP32, the same
-// integer P block, values in FP32. Lane (t = lane % 16, h = lane / 16) scores token t over channels 64 h .. 64 h + 63;
-// for the values lane l owns channels 4 l .. 4 l + 3.
-// one window sub-block's rows in registers: the lane's 64 channels of its token's K row, and its 4 channels of all 16 V rows
-struct WindowTile {
-  uint4 k[8];
-  uint2 v[16];
-  int j, count;  // sub-block within its window, the window's token count
-};
-template <int QG>
-__device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
-  const int hpr = a.kv_heads * a.vg;
-  const long long total = total_units<true>(a, hpr), per = ceil_div(total, nxw);
-  const long long lo = (long long)xw * per, hi = min(total, lo + per);
-  if (lo >= hi) return;
-  const int slot0 = a.coarse_ctas * a.coarse_warps + a.batch * hpr;  // after the coarse slots
-  const int t = lane & 15, h = lane >> 4;
-  Cursor c = locate<true>(a, hpr, lo);
-  int cur_vh = -1;
-  float m[QG], l[QG], o[QG][4];
-  auto flush = [&]() {
-    float *p = a.part + (size_t)(slot0 + xw + cur_vh) * QG * PSTRIDE;
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      *reinterpret_cast<float4 *>(p + qi * PSTRIDE + 4 * lane) = make_float4(o[qi][0], o[qi][1], o[qi][2], o[qi][3]);
-      if (!lane) { p[qi * PSTRIDE + D] = m[qi]; p[qi * PSTRIDE + D + 1] = l[qi]; }
-    }
-  };
-  // all loads of a sub-block at once (the next sub-block's are issued before the current one is computed)
-  auto load = [&](const Cursor &cu, WindowTile &w) {
-    const Row r = row_of(a, cu.b);
-    const bool sink = cu.i < r.na;
-    w.j = sink ? cu.i : cu.i - r.na;
-    w.count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
-    const size_t eh = (size_t)((cu.b * hpr + cu.hir) / a.vg) * G * D;
-    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh;
-    const int tok = w.j * S + t;
-    const uint4 *kp = reinterpret_cast<const uint4 *>(ek + (size_t)min(tok, G - 1) * D + 64 * h);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w.k[i] = tok < w.count ? __ldcg(kp + i) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-    for (int tt = 0; tt < S; ++tt)
-      w.v[tt] = w.j * S + tt < w.count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(w.j * S + tt) * D) + lane) : make_uint2(0u, 0u);
-  };
-  WindowTile cur, nxt;
-  load(c, cur);
-  for (long long u = lo; u < hi; ++u) {
-    const int vh = c.b * hpr + c.hir;
-    if (vh != cur_vh) {
-      if (cur_vh >= 0) flush();
-      cur_vh = vh;
-      __syncwarp();
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, c.b, c.hir, qi) * D) + lane);
-        *reinterpret_cast<float4 *>(&sm.q[qi][4 * lane]) = make_float4(bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y));
-        m[qi] = -INFINITY; l[qi] = 0.f;
-        o[qi][0] = o[qi][1] = o[qi][2] = o[qi][3] = 0.f;
-      }
-      __syncwarp();
-    }
-    advance<true>(a, hpr, c);
-    if (u + 1 < hi) load(c, nxt);
-    const int tok = cur.j * S + t;
-    float x[QG];
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) x[qi] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 w = cur.k[i];
-      const float kv[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const float4 qa = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i]), qb = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i + 4]);
-        x[qi] = fmaf(qa.x, kv[0], x[qi]); x[qi] = fmaf(qa.y, kv[1], x[qi]); x[qi] = fmaf(qa.z, kv[2], x[qi]); x[qi] = fmaf(qa.w, kv[3], x[qi]);
-        x[qi] = fmaf(qb.x, kv[4], x[qi]); x[qi] = fmaf(qb.y, kv[5], x[qi]); x[qi] = fmaf(qb.z, kv[6], x[qi]); x[qi] = fmaf(qb.w, kv[7], x[qi]);
-      }
-    }
-    float al[QG], w[QG], sp[QG];
-    uint32_t P[QG][4];
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      x[qi] += __shfl_xor_sync(FULL, x[qi], 16);
-      const float s = tok < cur.count ? __fmul_rn(x[qi], a.sl) : -INFINITY;
-      float mb = s;
-#pragma unroll
-      for (int off = 8; off; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(FULL, mb, off));
-      const float mn = fmaxf(m[qi], mb);
-      al[qi] = ex2(m[qi] - mn); w[qi] = ex2(mb - mn);  // (2^-inf = 0; mb is finite: token 0 of a unit always exists)
-      m[qi] = mn;
-      const uint32_t pbits = __float_as_uint(fmaf(ex2(s - mb), 255.f, MAGICF));
-      if (lane < 16) sm.pst[qi][t] = (uint8_t)pbits;
-    }
-    __syncwarp();
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      const uint4 pw = *reinterpret_cast<const uint4 *>(sm.pst[qi]);
-      P[qi][0] = pw.x; P[qi][1] = pw.y; P[qi][2] = pw.z; P[qi][3] = pw.w;
-      sp[qi] = (float)(__dp4a(pw.x, 0x01010101u, 0u) + __dp4a(pw.y, 0x01010101u, 0u) + __dp4a(pw.z, 0x01010101u, 0u) + __dp4a(pw.w, 0x01010101u, 0u));
-    }
-    float y[QG][4];
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) y[qi][0] = y[qi][1] = y[qi][2] = y[qi][3] = 0.f;
-#pragma unroll
-    for (int tt = 0; tt < S; ++tt) {
-      const uint2 vw = cur.v[tt];
-      const float vv[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        // the byte as a float without a conversion instruction: the bits of 2^23 + p, minus 2^23
-        const float p = __uint_as_float(0x4B000000u | ((P[qi][tt >> 2] >> (8 * (tt & 3))) & 255u)) - 8388608.f;
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) y[qi][cc] = fmaf(p, vv[cc], y[qi][cc]);
-      }
-    }
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      l[qi] = fmaf(al[qi], l[qi], w[qi] * sp[qi]);
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) o[qi][cc] = fmaf(al[qi], o[qi][cc], w[qi] * y[qi][cc]);
-    }
-    __syncwarp();
-    cur = nxt;
-  }
-  flush();
-}
-
-// ---- one closed group on the tensor cores ----------------------------------------------------------------------------------
-// The warp's running softmax of its current virtual head. Thread (gid, tig): channels 4 (8 u + gid) + cc, u, cc = 0..3,
-// of queries qe = 2 (tig & 1) + e, e = 0, 1, summed over the sub-blocks of parity tig >> 1 only: the two parities'
-// threads are added when the partial is written.
-struct Run {
-  float m[2], l[2];
-  float2 o[4][4];  // (.x, .y) = queries e = 0, 1
-};
-template <int QG> __device__ __forceinline__ bool query_valid(int tig, int e) { return 2 * (tig & 1) + e < QG; }
-
-// The warp's stream of record pairs: chunk p = CPG k + i holds pairs PPC i .. of the k-th group of the warp's range, in ring
-// slot p % NP (its (p / NP)-th use); the group's metadata travels with chunk 0 into metadata slot k & 1. All lanes carry the
-// (warp-uniform) state; lane 0 issues the copies.
-template <int CB> struct Ring {
-  using Sh = CoarseShape<CB>;
-  StreamWarp<CB> &w;
-  const fbla_k_decode &a;
-  int hpr, lane;
-  Cursor fc;                           // the group of the next chunk to issue
-  int issued, chunks;                  // chunks issued / in the warp's range
-  const uint8_t *src_pair, *src_meta;  // that group's records and metadata
-  __device__ __forceinline__ void point() {
-    const int bh = (fc.b * hpr + fc.hir) / a.vg;
-    const size_t unit = (size_t)bh * a.hs + (size_t)group_of(a, fc) * a.gs;
-    src_pair = a.c.coarse + unit * Sh::GROUP_BYTES;
-    src_meta = reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024;
-  }
-  __device__ __forceinline__ void issue_next() {
-    if (issued >= chunks) return;
-    const int i = issued % Sh::CPG, slot = issued % Sh::NP, ms = (issued / Sh::CPG) & 1;
-    if (lane == 0) {  // (the slot's earlier reads have completed: their values were consumed before the __syncwarp above)
-      if (i == 0) {
-        mbar_expect_tx(&w.bar_meta[ms], 1024);
-        bulk_g2s(w.meta[ms], src_meta, 1024, &w.bar_meta[ms]);
-      }
-      mbar_expect_tx(&w.bar_pair[slot], Sh::CHUNK_BYTES);
-      bulk_g2s(w.pair[slot], src_pair + i * Sh::CHUNK_BYTES, Sh::CHUNK_BYTES, &w.bar_pair[slot]);
-    }
-    ++issued;
-    if (i == Sh::CPG - 1 && issued < chunks) { advance<false>(a, hpr, fc); point(); }
-  }
-  // false: a bounded wait gave up
-  __device__ __forceinline__ bool wait_meta(int k) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_meta[k & 1], (uint32_t)((k >> 1) & 1))); }
-  __device__ __forceinline__ bool wait_pair(int p) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_pair[p % Sh::NP], (uint32_t)((p / Sh::NP) & 1))); }
-};
-
-#ifdef FBLA_TIMING
-__device__ long long fbla_sec[148 * 16 * 8];
-__shared__ long long fbla_sec_sm[16 * 8];
-#define SEC(i) { const long long t_ = clock64(); if ((threadIdx.x & 31) == 0) fbla_sec_sm[(threadIdx.x >> 5) * 8 + (i)] += t_ - tsec_; tsec_ = clock64(); }
-#define SEC0 long long tsec_ = clock64();
-#else
-#define SEC(i)
-#define SEC0
-#endif
-// Group k of the warp's range. Returns false if a bounded wait gave up.
-template <int CB, int FB, int QG>
-__device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4 (&q4)[QG], float sl, int lane, Run &run,
-                                             float *lse_group /* [8 sub-blocks][QG] of this (virtual head, group) */) {
-  constexpr int RB = record_bytes(CB);
-  constexpr float HOFF = .5f * ((1 << FB) - 1);
-  StreamWarp<CB> &sm = ring.w;
-  const int gid = lane >> 2, tig = lane & 3;
-  const bool odd = tig >> 1;  // threads tig >= 2 accumulate the odd sub-block of every pair (columns 4..7 of the value products)
-  if (!ring.wait_meta(k)) return false;
-  const uint8_t *meta = sm.meta[k & 1];
-  // qhat of every query; c0 / sqc of the thread's two score columns
-  float c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f};
-  {
-    const uint4 km = lds128(meta + 16 * lane);
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      float sq, qb, qsum;
-      quantize_query(km, q4[qi], sl, reinterpret_cast<uint32_t *>(sm.qst + QST_ROW * qi), lane, sq, qb, qsum);
-      const float c = fmaf(__fmul_rn(sq, HOFF), qsum, qb), s2 = __fmul_rn(sq, (float)(1 << FB));
-      if (qi == 2 * (tig & 1)) { c0[0] = c; sqc[0] = s2; }
-      if (qi == 2 * (tig & 1) + 1) { c0[1] = c; sqc[1] = s2; }
-    }
-  }
-  __syncwarp();
-  uint32_t B[8];
-  qhat_frag<CB>(sm.qst, gid, tig, B);
-  // the group's sums in code units, relative to the running maximum run.m: A = sum w y, Bs = sum w sum p
-  float2 A[4][4], Bs = make_float2(0.f, 0.f);
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) A[u][cc] = make_float2(0.f, 0.f);
-  const float2 sqc2 = make_float2(sqc[0], sqc[1]), c02 = make_float2(c0[0], c0[1]);
-  // Software pipeline over the group's four record pairs: the scores of pair J + 1 (stage A: shared loads, score products,
-  // sub-block maxima) are issued before the softmax and value products of pair J (stage B), so that each stage's
-  // latencies are covered by the other's instructions.
-  struct Scores { float s[2][4], mb[2][2]; };
-  // stage A of pair J: scores s[par][i], i = (token gid, column 2 tig), (gid, 2 tig + 1), (gid + 8, 2 tig), (gid + 8, 2 tig + 1)
-  // (only columns < QG, i.e. threads tig < 2, are queries; the others multiply zero rows of qst), and their maxima
-  auto stage_a = [&](int J, Scores &sc) -> bool {
-    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;  // the pair's chunk
-    if (J % CoarseShape<CB>::PPC == 0 && !ring.wait_pair(p)) return false;
-    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP] + (J % CoarseShape<CB>::PPC) * CoarseShape<CB>::PAIR_BYTES, *rb = ra + RB;
-#pragma unroll
-    for (int par = 0; par < 2; ++par) {
-      float x[4];
-      qk_tile<CB>(par ? rb : ra, gid, tig, B, x);
-      const float2 s01 = __ffma2_rn(sqc2, make_float2(x[0], x[1]), c02), s23 = __ffma2_rn(sqc2, make_float2(x[2], x[3]), c02);
-      sc.s[par][0] = s01.x; sc.s[par][1] = s01.y; sc.s[par][2] = s23.x; sc.s[par][3] = s23.y;
-    }
-#pragma unroll
-    for (int par = 0; par < 2; ++par)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float v = fmaxf(sc.s[par][e], sc.s[par][2 + e]);
-        v = fmaxf(v, __shfl_xor_sync(FULL, v, 4));
-        v = fmaxf(v, __shfl_xor_sync(FULL, v, 8));
-        v = fmaxf(v, __shfl_xor_sync(FULL, v, 16));
-        sc.mb[par][e] = v;
-      }
-    return true;
-  };
-  // stage B of pair J: sub-blocks 2 J (parity 0) and 2 J + 1 (parity 1)
-  auto stage_b = [&](int J, const Scores &sc) {
-    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;
-    const uint8_t *ra = sm.pair[p % CoarseShape<CB>::NP] + (J % CoarseShape<CB>::PPC) * CoarseShape<CB>::PAIR_BYTES, *rb = ra + RB;
-    // the thread's own sub-block 2 J + (tig >> 1) of queries 2 (tig & 1) + e, and the pair's maximum (the same value in
-    // both parities' threads, so their running maxima stay equal)
-    float mbj[2], mp[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const float other = __shfl_xor_sync(FULL, sc.mb[1][e], 2);
-      mbj[e] = odd ? other : sc.mb[0][e];
-      const float pm = fmaxf(sc.mb[0][e], sc.mb[1][e]), pmo = __shfl_xor_sync(FULL, pm, 2);
-      mp[e] = odd ? pmo : pm;
-    }
-    // the running maximum moves only when a pair exceeds it by more than 2^8 (weights stay <= 2^8; the rescale is rare)
-    const bool grow = mp[0] > run.m[0] + 8.f || mp[1] > run.m[1] + 8.f;
-    if (__any_sync(FULL, grow)) {
-      float alv[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const float mn = mp[e] > run.m[e] + 8.f ? mp[e] : run.m[e], al = ex2(run.m[e] - mn);  // (2^-inf = 0 on the first group)
-        run.m[e] = mn;
-        run.l[e] *= al;
-        alv[e] = al;
-      }
-      const float2 al2 = make_float2(alv[0], alv[1]);
-      Bs = __fmul2_rn(Bs, al2);
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) { run.o[u][cc] = __fmul2_rn(run.o[u][cc], al2); A[u][cc] = __fmul2_rn(A[u][cc], al2); }
-    }
-    if (tig < 2) {  // P bytes: pst[parity][query][token]
-#pragma unroll
-      for (int par = 0; par < 2; ++par)
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-          if (query_valid<QG>(tig, e)) {
-            const int qe = 2 * tig + e;
-            sm.pst[(par * 4 + qe) * 16 + gid] = (uint8_t)__float_as_uint(fmaf(ex2(sc.s[par][e] - sc.mb[par][e]), 255.f, MAGICF));
-            sm.pst[(par * 4 + qe) * 16 + gid + 8] = (uint8_t)__float_as_uint(fmaf(ex2(sc.s[par][2 + e] - sc.mb[par][e]), 255.f, MAGICF));
-          }
-    }
-    __syncwarp();
-    // column gid of the value products: gid < 4: parity 0, query gid, k block = tokens 4 tig ..; gid >= 4: parity 1
-    const uint32_t pw = lds32(sm.pst + 4 * lane);
-    const uint32_t b0 = gid < 4 ? pw : 0u, b1 = gid < 4 ? 0u : pw;
-    const float2 wj = make_float2(ex2(mbj[0] - run.m[0]), ex2(mbj[1] - run.m[1]));
-    {  // sum p of both sub-blocks, every column: a product with an all-ones A
-      uint32_t d[4];
-      mma_u8u8_k32_from(d, 0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u, b0, b1, MAGIC);
-      const float2 sp = isum2(d[0], d[1]);
-      Bs = __ffma2_rn(wj, sp, Bs);
-      if (gid == 0) {
-        if (query_valid<QG>(tig, 0)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1)] = mbj[0] + lg2(sp.x);
-        if (query_valid<QG>(tig, 1)) lse_group[(2 * J + (tig >> 1)) * QG + 2 * (tig & 1) + 1] = mbj[1] + lg2(sp.y);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      uint32_t va[4], vb[4];
-      v_slots<CB>(ra, 8 * u + gid, tig, va);
-      v_slots<CB>(rb, 8 * u + gid, tig, vb);
-      uint32_t d01[4], d23[4];
-      mma_u8u8_k32_from(d01, va[0], va[1], vb[0], vb[1], b0, b1, MAGIC);  // rows gid: channel cc 0, gid + 8: cc 1
-      mma_u8u8_k32_from(d23, va[2], va[3], vb[2], vb[3], b0, b1, MAGIC);  // cc 2, cc 3
-      A[u][0] = __ffma2_rn(wj, isum2(d01[0], d01[1]), A[u][0]);
-      A[u][1] = __ffma2_rn(wj, isum2(d01[2], d01[3]), A[u][1]);
-      A[u][2] = __ffma2_rn(wj, isum2(d23[0], d23[1]), A[u][2]);
-      A[u][3] = __ffma2_rn(wj, isum2(d23[2], d23[3]), A[u][3]);
-    }
-    __syncwarp();  // pst is free; after a chunk's last pair its slot is too
-    if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();  // refill the slot with the chunk NP ahead
-  };
-#ifdef FBLA_NOCOMPUTE  // tuning builds only: stream the chunks without touching them
-#pragma unroll 1
-  for (int J = 0; J < SBG / 2; ++J) {
-    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;
-    if (J % CoarseShape<CB>::PPC == 0 && !ring.wait_pair(p)) return false;
-    __syncwarp();
-    if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();
-  }
-#else
-#pragma unroll 1
-  for (int J = 0; J < SBG / 2; ++J) {
-    Scores sc;
-    if (!stage_a(J, sc)) return false;
-    stage_b(J, sc);
-  }
-#endif
-  // fold the group into the running softmax: o += vs' A + vb' B, coarse cell midpoints folded into vb'
-  run.l[0] += Bs.x; run.l[1] += Bs.y;
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
-    const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      const float vbp = fmaf(vs[cc], HOFF, vb[cc]), vsp = __fmul_rn(vs[cc], (float)(1 << FB) * v_unscale<CB>(cc));
-      run.o[u][cc] = __fadd2_rn(run.o[u][cc], __ffma2_rn(splat(vsp), A[u][cc], __fmul2_rn(splat(vbp), Bs)));
-    }
-  }
-  return true;
-}
-
-// ---- the coarse kernel -------------------------------------------------------------------------------------------------
-template <int QG> __device__ __forceinline__ void reset(Run &r) {
-  r.m[0] = r.m[1] = -INFINITY; r.l[0] = r.l[1] = 0.f;
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) r.o[u][cc] = make_float2(0.f, 0.f);
-}
-// one partial row set: threads tig and tig ^ 2 hold the two sub-block parities of the same (channel, query) sums
-template <int QG> __device__ __forceinline__ void write_partial(float *p, const Run &r, int lane, bool correction) {
-  const int gid = lane >> 2, tig = lane & 3;
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    const float l = r.l[e] + __shfl_xor_sync(FULL, r.l[e], 2);
-    const int qe = 2 * tig + e;
-    float *row = p + qe * PSTRIDE;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      float4 v;
-      const float o0 = e ? r.o[u][0].y : r.o[u][0].x, o1 = e ? r.o[u][1].y : r.o[u][1].x;
-      const float o2 = e ? r.o[u][2].y : r.o[u][2].x, o3 = e ? r.o[u][3].y : r.o[u][3].x;
-      v.x = o0 + __shfl_xor_sync(FULL, o0, 2);
-      v.y = o1 + __shfl_xor_sync(FULL, o1, 2);
-      v.z = o2 + __shfl_xor_sync(FULL, o2, 2);
-      v.w = o3 + __shfl_xor_sync(FULL, o3, 2);
-      if (tig < 2 && qe < QG) *reinterpret_cast<float4 *>(row + 4 * (8 * u + gid)) = v;
-    }
-    if (tig < 2 && qe < QG && gid == 0) {
-      if (correction) row[D] = l;
-      else { row[D] = r.m[e]; row[D + 1] = l; }
-    }
-  }
-}
-
-#ifdef FBLA_TIMING  // tuning builds only: cycles every warp of the coarse kernel spent, read back by fbla_k_debug_read
-__device__ long long fbla_dbg[148 * 16];
-#define FBLA_T0 const long long t0_ = clock64(); if ((threadIdx.x & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) fbla_sec_sm[(threadIdx.x >> 5) * 8 + i_] = 0;
-#define FBLA_T1 if ((threadIdx.x & 31) == 0) { fbla_dbg[blockIdx.x * 16 + (threadIdx.x >> 5)] = clock64() - t0_; for (int i_ = 0; i_ < 8; ++i_) fbla_sec[(blockIdx.x * 16 + (threadIdx.x >> 5)) * 8 + i_] = fbla_sec_sm[(threadIdx.x >> 5) * 8 + i_]; }
-#else
-#define FBLA_T0
-#define FBLA_T1
-#endif
-
 template <int CB, int FB, int QG>
 __global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coarse_kernel(const fbla_k_decode a) {
-  using Sh = CoarseShape<CB>;
-  FBLA_T0
-  allow_next_pass();
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (blockIdx.x == 0 && threadIdx.x == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
-  if (warp >= Sh::WARPS) {
-#ifdef FBLA_NOWINDOW  // tuning builds only
-    return;
-#endif
-    exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, blockIdx.x * XWARPS + (warp - Sh::WARPS), gridDim.x * XWARPS);
-    FBLA_T1
-    return;
-  }
-#ifdef FBLA_NOSTREAM  // tuning builds only
-  return;
-#endif
-  StreamWarp<CB> &w = sm.w[warp];
-  for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
-  reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < Sh::NP; ++s) mbar_init(&w.bar_pair[s], 1);
-    mbar_init(&w.bar_meta[0], 1);
-    mbar_init(&w.bar_meta[1], 1);
-    mbar_init_fence();
-  }
-  __syncwarp();
-
-  const int hpr = a.kv_heads * a.vg;
-  const long long total = total_units<false>(a, hpr), tw = (long long)gridDim.x * Sh::WARPS, per = ceil_div(total, tw);
-  const long long gw = (long long)blockIdx.x * Sh::WARPS + warp, lo = gw * per, hi = min(total, lo + per);
-  if (lo >= hi) return;
-  Cursor cc = locate<false>(a, hpr, lo);
-  Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(Sh::CPG * (hi - lo)), nullptr, nullptr};
-  ring.point();
-#pragma unroll
-  for (int s = 0; s < Sh::NP; ++s) ring.issue_next();
-  Run run;
-  float4 q4[QG];
-  int cur_vh = -1;
-  for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
-    const int vh = cc.b * hpr + cc.hir;
-    if (vh != cur_vh) {
-      if (cur_vh >= 0) write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
-      cur_vh = vh;
-      reset<QG>(run);
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, cc.b, cc.hir, qi) * D) + lane);
-        q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
-      }
-    }
-    if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)group_of(a, cc) * SBG) * QG)) {
-      if (lane == 0) report(a, 1);
-      return;
-    }
-  }
-  write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
-  FBLA_T1
+  coarse_item<CB, FB, QG>(a, smem_raw);
 }
 
-// ---- which partial slots belong to a virtual head ------------------------------------------------------------------------
-struct Slots { int c0, c1, x0, x1; };  // coarse warps c0..c1 (slot w + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
-__device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
-  const int hpr = a.kv_heads * a.vg;
-  Slots s{0, -1, 0, -1};
-  int n;
-  const long long tw = (long long)a.coarse_ctas * a.coarse_warps;
-  long long off = head_offset<false>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), tw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
-  off = head_offset<true>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * XWARPS); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
-  return s;
-}
-__device__ __forceinline__ const float *coarse_slot(const fbla_k_decode &a, int w, int vh, int qi) {
-  return a.part + ((size_t)(w + vh) * a.qg + qi) * PSTRIDE;
-}
-__device__ __forceinline__ const float *window_slot(const fbla_k_decode &a, int x, int vh, int qi) {
-  const int base = a.coarse_ctas * a.coarse_warps + a.batch * a.kv_heads * a.vg;
-  return a.part + ((size_t)(base + x + vh) * a.qg + qi) * PSTRIDE;
-}
-
-// ---- select: R = log2 of the row's coarse mass; the sub-blocks holding more than tau of it for some query ------------
 template <int QG>
 __global__ void __launch_bounds__(256) select_kernel(const fbla_k_decode a) {
-  __shared__ float R[4];
-  __shared__ int wc[8];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, vh = blockIdx.y, slice = blockIdx.x;
-  const int hpr = a.kv_heads * a.vg;
-  allow_next_pass();
-  const Row row = row_of(a, vh / hpr);
-  const Slots s = slots_of(a, vh);
-  wait_previous_pass();
-  // the slice's sub-block masses first (they do not depend on R): every load of the warp in flight together
-  const int lo = slice * SLICE + warp * (SLICE / 8), first = SBG * row.g0, hi = SBG * (row.g0 + row.closed);
-  float x[4][QG];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int sb = lo + 32 * i + lane;
-    const bool closed = a.phase != 1 && sb >= first && sb < hi;
-    const float *p = a.lse + ((size_t)vh * a.nblocks + (closed ? sb : 0)) * QG;
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) x[i][qi] = closed ? __ldcg(p + qi) : -INFINITY;
-  }
-  if (a.phase == 2) {  // the rows' (global) log2 mass is given
-    if (threadIdx.x < QG) R[threadIdx.x] = __ldcg(a.row_r + vh * QG + threadIdx.x);
-  } else if (warp < QG) {  // R of query `warp`: one pass over the head's partial (m, l), merged online, then across lanes
-    const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
-    float mx = -INFINITY, ls = 0.f;
-    for (int i = lane; i < n; i += 32) {
-      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
-      const float m = __ldcg(p + D), l = __ldcg(p + D + 1);
-      if (m != -INFINITY) {
-        const float mn = fmaxf(mx, m);
-        ls = fmaf(ls, ex2(mx - mn), l * ex2(m - mn));
-        mx = mn;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float m2 = __shfl_xor_sync(FULL, mx, o), l2 = __shfl_xor_sync(FULL, ls, o);
-      const float mn = fmaxf(mx, m2);
-      // (lanes pair up symmetrically: both compute the same sum in the same order of magnitudes)
-      const float a1 = mx == -INFINITY ? 0.f : ls * ex2(mx - mn), a2 = m2 == -INFINITY ? 0.f : l2 * ex2(m2 - mn);
-      ls = (lane & o) ? a2 + a1 : a1 + a2;
-      mx = mn;
-    }
-    const float r = mx + lg2(ls);  // (-inf for a shard that holds nothing of this row)
-    if (!lane) { R[warp] = r; if (!slice) a.row_r[vh * QG + warp] = r; }
-  }
-  if (a.phase == 1) return;  // only the local mass was asked for
-  __syncthreads();
-  int qm[4], n = 0;
-  uint32_t bal[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    qm[i] = 0;
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) qm[i] |= (x[i][qi] - R[qi] > a.log2_tau) << qi;
-    bal[i] = __ballot_sync(FULL, qm[i] != 0);
-    n += __popc(bal[i]);
-  }
-  if (!lane) wc[warp] = n;
-  __syncthreads();
-  int off = 0, total = 0;
-#pragma unroll
-  for (int w = 0; w < 8; ++w) { off += w < warp ? wc[w] : 0; total += wc[w]; }
-  int *items = a.items + ((size_t)vh * a.nslices + slice) * SLICE;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (qm[i]) items[off + __popc(bal[i] & ((1u << lane) - 1u))] = (lo + 32 * i + lane) << 4 | qm[i];
-    off += __popc(bal[i]);
-  }
-  if (!threadIdx.x) a.counts[(size_t)vh * a.nslices + slice] = total;
+  select_item<QG>(a, nullptr);
 }
-
-// ---- refine: full - coarse of every selected sub-block ----------------------------------------------------------------------
-template <int CB, int FB> struct RefineShape {
-  static constexpr int WARPS = FBLA_RW, NST = FBLA_RNST;
-  static constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
-  static constexpr int STAGE = RC + RF;
-};
-template <int CB, int FB> struct __align__(128) RefineWarp {
-  uint8_t stage[RefineShape<CB, FB>::NST][RefineShape<CB, FB>::STAGE];
-  uint8_t meta[2][1024];  // the metadata of the two groups that items in flight can belong to (NST = 2: the item in work and one ahead)
-  uint8_t qst[8 * QST_ROW];
-  uint8_t pst[128];  // rows 0..3: P under the full scores, rows 4..7: under the coarse scores; 16 tokens each
-  uint64_t bar[RefineShape<CB, FB>::NST];
-};
 
 template <int CB, int FB, int QG>
 __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_kernel(const fbla_k_decode a) {
-  using Sh = RefineShape<CB, FB>;
-  constexpr float HOFF = .5f * ((1 << FB) - 1);
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  RefineWarp<CB, FB> *ws = reinterpret_cast<RefineWarp<CB, FB> *>(smem_raw);
-  int *pre = reinterpret_cast<int *>(smem_raw + sizeof(RefineWarp<CB, FB>) * Sh::WARPS);  // [entries + 1]
-  __shared__ int chunk_sum[256];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tig = lane & 3;
-  const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, entries = vheads * a.nslices;
-  allow_next_pass();
-  wait_previous_pass();
-  // exclusive prefix of the slices' counts: pre[e], e = vh * nslices + slice
-  {
-    const int per = (entries + 255) / 256, e0 = threadIdx.x * per, e1 = min(entries, e0 + per);
-    int sum = 0;
-    for (int e = e0; e < e1; ++e) sum += __ldcg(a.counts + e);
-    chunk_sum[threadIdx.x] = sum;
-    __syncthreads();
-    if (warp == 0) {
-      int run = 0;
-      for (int i0 = 0; i0 < 256; i0 += 32) {
-        const int v = chunk_sum[i0 + lane];
-        int x = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(FULL, x, o); x += lane >= o ? y : 0; }
-        chunk_sum[i0 + lane] = run + x - v;
-        run += __shfl_sync(FULL, x, 31);
-      }
-      if (!lane) pre[entries] = run;
-    }
-    __syncthreads();
-    int acc = chunk_sum[threadIdx.x];
-    for (int e = e0; e < e1; ++e) { pre[e] = acc; acc += __ldcg(a.counts + e); }
-    __syncthreads();
-    if (blockIdx.x == 0)  // for the merge: the first item of every virtual head, and the total
-      for (int v = threadIdx.x; v <= vheads; v += blockDim.x) a.item_off[v] = pre[v * a.nslices];
-  }
-  const int total = pre[entries];
-  const long long rw = (long long)gridDim.x * Sh::WARPS;
-  const int per = (int)ceil_div(total, rw), gw = blockIdx.x * Sh::WARPS + warp;
-  const int lo = gw * per, hi = min(total, lo + per);
-  if (lo >= hi) return;
-  RefineWarp<CB, FB> &w = ws[warp];
-  for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
-  reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < Sh::NST; ++s) mbar_init(&w.bar[s], 1);
-    mbar_init_fence();
-  }
-  __syncwarp();
-  // entry of item lo: the last e with pre[e] <= lo
-  int fe;
-  {
-    int l = 0, h = entries;  // pre[l] <= lo < pre[h]
-    while (h - l > 1) { const int mid = (l + h) >> 1; if (pre[mid] <= lo) l = mid; else h = mid; }
-    fe = l;
-  }
-  int ce = fe;
-  auto item_at = [&](int k, int &e) {  // item k (>= the previous k): its entry (advanced) and value
-    while (pre[e + 1] <= k) ++e;
-    return __ldcg(a.items + (size_t)e * SLICE + (k - pre[e]));
-  };
-  long long issued_unit = -1;  // (lane 0) the (virtual head, group) of the last item issued, and which metadata buffer it uses
-  int issued_par = 1;
-  auto issue = [&](int it, int e, int s) {  // lane 0
-    const int vh = e / a.nslices, bh = vh / a.vg, sb = it >> 4;
-    const size_t unit = (size_t)bh * a.hs + (size_t)(sb / SBG) * a.gs, rec = unit * SBG + sb % SBG;
-    const long long vu = (long long)vh * a.nblocks + sb / SBG;
-    const bool fresh = vu != issued_unit;  // the group's metadata travels with its first item only
-    mbar_expect_tx(&w.bar[s], Sh::STAGE + (fresh ? 1024 : 0));
-    bulk_g2s(w.stage[s], a.c.coarse + rec * Sh::RC, Sh::RC, &w.bar[s]);
-    bulk_g2s(w.stage[s] + Sh::RC, a.c.fine + rec * Sh::RF, Sh::RF, &w.bar[s]);
-    if (fresh) {
-      issued_unit = vu; issued_par ^= 1;
-      bulk_g2s(w.meta[issued_par], reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
-    }
-  };
-  int fit[Sh::NST];  // the items in flight (warp-uniform)
-#pragma unroll
-  for (int s = 0; s < Sh::NST; ++s)
-    if (lo + s < hi) {
-      fit[s] = item_at(lo + s, fe);
-      if (lane == 0) issue(fit[s], fe, s);
-    }
-  Run run;  // m unused: corrections are already in units of 2^-R
-  float2 Ag[4][4], Bg = make_float2(0.f, 0.f);  // the current group's sums in code units, (.x, .y) = queries e = 0, 1
-#pragma unroll
-  for (int u = 0; u < 4; ++u)
-#pragma unroll
-    for (int cc = 0; cc < 4; ++cc) Ag[u][cc] = make_float2(0.f, 0.f);
-  int pe = fe;  // entry cursor for peeking at the next item
-  float4 q4[QG];
-  float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
-  uint32_t B[8];
-  int cur_vh = -1, cur_par = 1;
-  long long cur_unit = -1, cur_unit2 = -1;  // cur_unit is also reset when the virtual head changes; cur_unit2 follows the groups only
-  for (int k = lo; k < hi; ++k) {
-    const int s = (k - lo) % Sh::NST;
-    const int it = item_at(k, ce), vh = ce / a.nslices, sb = it >> 4;
-    if (vh != cur_vh) {
-      if (cur_vh >= 0) write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
-      cur_vh = vh; cur_unit = -1;
-      reset<QG>(run);
-      const int b = vh / hpr, hir = vh - b * hpr;
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, b, hir, qi) * D) + lane);
-        q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
-      }
-#pragma unroll
-      for (int e = 0; e < 2; ++e) Rq[e] = query_valid<QG>(tig, e) ? __ldcg(a.row_r + vh * QG + 2 * (tig & 1) + e) : 0.f;
-    }
-    const bool ok = mbar_wait_bounded(&w.bar[s], ((k - lo) / Sh::NST) & 1);
-    if (!__all_sync(FULL, ok)) {
-      if (lane == 0) report(a, 3);
-      return;
-    }
-    const uint8_t *crec = w.stage[s], *frec = crec + Sh::RC;
-    const long long unit = (long long)vh * a.nblocks + sb / SBG;
-    if (unit != cur_unit2) { cur_unit2 = unit; cur_par ^= 1; }  // (the same sequence of groups as the issuing side)
-    const uint8_t *meta = w.meta[cur_par];
-    if (unit != cur_unit) {  // the group's qhat: the same function of the same inputs as the coarse pass
-      cur_unit = unit;
-      __syncwarp();
-      const uint4 km = lds128(meta + 16 * lane);
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        float sq, qb, qsum;
-        quantize_query(km, q4[qi], a.sl, reinterpret_cast<uint32_t *>(w.qst + QST_ROW * qi), lane, sq, qb, qsum);
-        const float c = fmaf(__fmul_rn(sq, HOFF), qsum, qb), s2 = __fmul_rn(sq, (float)(1 << FB));
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-          if (qi == 2 * (tig & 1) + e) { c0[e] = c; sqc[e] = s2; sqf[e] = sq; qbf[e] = qb; }
-      }
-      __syncwarp();
-      qhat_frag<CB>(w.qst, gid, tig, B);
-    }
-    float xh[4], xl[4];
-    qk_tile<CB>(crec, gid, tig, B, xh);
-    qk_tile<FB>(frec, gid, tig, B, xl);
-    // columns 2 tig + e (tig < 2: queries): coarse and full scores of tokens gid, gid + 8
-    float mc[2], mf[2], sc[2][2], sf[2][2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        sc[e][r] = fmaf(sqc[e], xh[2 * r + e], c0[e]);
-        sf[e][r] = fmaf(sqf[e], fmaf((float)(1 << FB), xh[2 * r + e], xl[2 * r + e]), qbf[e]);
-      }
-      float vc = fmaxf(sc[e][0], sc[e][1]), vf = fmaxf(sf[e][0], sf[e][1]);
-#pragma unroll
-      for (int o = 4; o <= 16; o <<= 1) { vc = fmaxf(vc, __shfl_xor_sync(FULL, vc, o)); vf = fmaxf(vf, __shfl_xor_sync(FULL, vf, o)); }
-      mc[e] = vc; mf[e] = vf;
-    }
-    if (tig < 2) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e)
-        if (query_valid<QG>(tig, e)) {
-          const int qe = 2 * tig + e;
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            w.pst[qe * 16 + gid + 8 * r] = (uint8_t)__float_as_uint(fmaf(ex2(sf[e][r] - mf[e]), 255.f, MAGICF));
-            w.pst[(4 + qe) * 16 + gid + 8 * r] = (uint8_t)__float_as_uint(fmaf(ex2(sc[e][r] - mc[e]), 255.f, MAGICF));
-          }
-        }
-    }
-    __syncwarp();
-    // Value products: column gid < 4: query gid under the full scores, gid >= 4: query gid - 4 under the coarse ones.
-    // Thread (gid, tig) reads columns 2 tig + e: tig < 2 holds the full-score sums of queries 2 tig + e, tig >= 2 the
-    // coarse-score sums of queries 2 (tig - 2) + e.
-    const bool cset = tig >> 1;
-    const uint32_t b0 = lds32(w.pst + 4 * lane);
-    float wgt[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const float mco = __shfl_xor_sync(FULL, mc[e], 2);
-      const bool on = query_valid<QG>(tig, e) && ((it >> (2 * (tig & 1) + e)) & 1);
-      wgt[e] = on ? (cset ? -ex2(mco - Rq[e]) : ex2(mf[e] - Rq[e])) : 0.f;
-    }
-    {
-      const float2 wgt2 = make_float2(wgt[0], wgt[1]);
-      {  // sum p of the thread's two columns: a product with an all-ones A
-        uint32_t d[4];
-        mma_u8u8_k16_from(d, 0x01010101u, 0x01010101u, b0, MAGIC);
-        Bg = __ffma2_rn(wgt2, isum2(d[0], d[1]), Bg);
-      }
-      // the group's weighted code sums: full-score threads add w (2^FB h + f), coarse-score threads -w 2^FB h
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint32_t vh4[4], vl4[4];
-        v_slots<CB>(crec, 8 * u + gid, tig, vh4);
-        v_slots<FB>(frec, 8 * u + gid, tig, vl4);
-        uint32_t h01[4], h23[4], l01[4], l23[4];
-        mma_u8u8_k16_from(h01, vh4[0], vh4[1], b0, MAGIC);
-        mma_u8u8_k16_from(h23, vh4[2], vh4[3], b0, MAGIC);
-        mma_u8u8_k16_from(l01, vl4[0], vl4[1], b0, MAGIC);
-        mma_u8u8_k16_from(l23, vl4[2], vl4[3], b0, MAGIC);
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          const float ch_ = (float)(1 << FB) * v_unscale<CB>(cc), cl_ = cset ? 0.f : v_unscale<FB>(cc);
-          const uint32_t *hh = cc < 2 ? h01 : h23, *ll = cc < 2 ? l01 : l23;
-          const float2 yh = isum2(hh[2 * (cc & 1)], hh[2 * (cc & 1) + 1]), yl = isum2(ll[2 * (cc & 1)], ll[2 * (cc & 1) + 1]);
-          Ag[u][cc] = __ffma2_rn(wgt2, __ffma2_rn(splat(ch_), yh, __fmul2_rn(splat(cl_), yl)), Ag[u][cc]);
-        }
-      }
-      // the group's last item of this warp: apply the V affine once (coarse cells at their midpoint)
-      bool last = k + 1 >= hi;
-      if (!last) {
-        const int nx = item_at(k + 1, pe);
-        last = pe / a.nslices != vh || (nx >> 4) / SBG != sb / SBG;
-      }
-      if (last) {
-        run.l[0] += Bg.x; run.l[1] += Bg.y;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const uint4 vm = lds128(meta + 512 + 16 * (8 * u + gid));
-          const float vb[4] = {bf_lo(vm.x), bf_hi(vm.x), bf_lo(vm.y), bf_hi(vm.y)}, vs[4] = {bf_lo(vm.z), bf_hi(vm.z), bf_lo(vm.w), bf_hi(vm.w)};
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            const float vbx = cset ? fmaf(vs[cc], HOFF, vb[cc]) : vb[cc];
-            run.o[u][cc] = __fadd2_rn(run.o[u][cc], __ffma2_rn(splat(vs[cc]), Ag[u][cc], __fmul2_rn(splat(vbx), Bg)));
-            Ag[u][cc] = make_float2(0.f, 0.f);
-          }
-        }
-        Bg = make_float2(0.f, 0.f);
-      }
-    }
-    __syncwarp();
-    if (k + Sh::NST < hi) {
-      fit[s] = item_at(k + Sh::NST, fe);
-      if (lane == 0) { fence_async_smem(); issue(fit[s], fe, s); }
-    }
-  }
-  write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
+  refine_item<CB, FB, QG>(a, smem_raw);
 }
 
-// ---- merge: out = (sum 2^(m_c - R) o_c + sum do) / (sum 2^(m_c - R) l_c + sum dl), BF16 ---------------------------------
-// One CTA per output row (virtual head, query): thread (ch, sl) sums the partial rows sl, sl + 4, ... of its channel,
-// the four lanes of a channel are then added in a fixed order.
 template <int QG>
 __global__ void __launch_bounds__(512) merge_kernel(const fbla_k_decode a) {
-  __shared__ float so[4][D], sl_[4];
-  __shared__ Slots ss;
-  __shared__ int rr[3];
-  const int vh = blockIdx.x / QG, qi = blockIdx.x % QG, ch = threadIdx.x & 127, sl = threadIdx.x >> 7;
-  const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, b = vh / hpr, hir = vh - b * hpr;
-  if (threadIdx.x == 0) ss = slots_of(a, vh);
-  wait_previous_pass();
-  if (threadIdx.x == 0) {
-    const int it0 = __ldcg(a.item_off + vh), it1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
-    rr[0] = 0; rr[1] = -1;
-    if (it1 > it0) {
-      const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
-      rr[0] = it0 / per; rr[1] = (it1 - 1) / per;
-    }
-  }
-  __syncthreads();
-  const Slots s = ss;
-  const float Rq = __ldcg(a.row_r + vh * QG + qi);
-  float O = 0.f, L = 0.f;
-  const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
-  for (int i0 = sl; i0 < n; i0 += 16) {
-    float m[4], l[4], o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int i = min(i0 + 4 * j, n - 1);
-      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, qi) : window_slot(a, s.x0 + i - nc, vh, qi);
-      m[j] = __ldcg(p + D); l[j] = __ldcg(p + D + 1); o[j] = __ldcg(p + ch);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (i0 + 4 * j < n) {
-        const float e = m[j] == -INFINITY ? 0.f : ex2(m[j] - Rq);
-        L = fmaf(e, l[j], L); O = fmaf(e, o[j], O);
-      }
-  }
-  const int w0 = rr[0], w1 = rr[1];
-  for (int i0 = w0 + sl; i0 <= w1; i0 += 16) {
-    float l[4], o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float *p = a.dpart + ((size_t)(min(i0 + 4 * j, w1) + vh) * QG + qi) * PSTRIDE;
-      l[j] = __ldcg(p + D); o[j] = __ldcg(p + ch);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (i0 + 4 * j <= w1) { L += l[j]; O += o[j]; }
-  }
-  so[sl][ch] = O;
-  if (ch == 0) sl_[sl] = L;
-  __syncthreads();
-  if (sl == 0) {
-    const float Os = (so[0][ch] + so[1][ch]) + (so[2][ch] + so[3][ch]), Ls = (sl_[0] + sl_[1]) + (sl_[2] + sl_[3]);
-    const size_t row = (size_t)q_row(a, b, hir, qi);
-    if (a.out_partial) {  // a shard's share of the row, in units of 2^-R: summed over the shards before the division
-      a.out_partial[row * PSTRIDE + ch] = Os;
-      if (ch == 0) a.out_partial[row * PSTRIDE + D] = Ls;
-    } else {
-      a.out[row * D + ch] = f32_to_bf16(__fdividef(Os, Ls));
-    }
-  }
+  merge_item<QG>(a, nullptr);
 }
 
 // a launch that may begin while the previous kernel of the stream still runs (the kernel calls wait_previous_pass)
@@ -1069,6 +36,17 @@ cudaError_t launch_dependent(void (*kernel)(P...), dim3 grid, dim3 block, size_t
   cfg.attrs = attr; cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
+
+namespace {
+template <class K> cudaError_t pass_of(K kernel, int gx, int gy, int threads, size_t smem, const char *entry, fbla_k_pass *p) {
+  cudaFuncAttributes fa;
+  const cudaError_t e = cudaFuncGetAttributes(&fa, kernel);
+  if (e != cudaSuccess) return e;
+  p->gx = gx; p->gy = gy; p->gz = 1; p->threads = threads; p->smem_bytes = (int)smem; p->regs = fa.numRegs;
+  snprintf(p->entry, sizeof p->entry, "%s", entry);
+  return cudaSuccess;
+}
+}  // namespace
 
 constexpr int REFINE_SMEM_MAX = 220 * 1024;  // dynamic shared memory of the refine pass (its ring + the slice prefix)
 template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a, cudaStream_t stream) {
@@ -1099,6 +77,23 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   if (e == cudaSuccess) e = launch_dependent(refine_kernel<CB, FB, QG>, dim3(a.refine_ctas), dim3(32 * RefineShape<CB, FB>::WARPS), rsm, stream, a);
   if (e == cudaSuccess) e = launch_dependent(merge_kernel<QG>, dim3(vheads * QG), dim3(512), 0, stream, a);
   return e;
+}
+
+template <int CB, int FB, int QG> cudaError_t passes_of(const fbla_k_decode &a, fbla_k_pass *p) {
+  const int vheads = a.batch * a.kv_heads * a.vg;
+  const size_t csm = sizeof(CoarseSmem<CB>) + 128;
+  const size_t rsm = sizeof(RefineWarp<CB, FB>) * RefineShape<CB, FB>::WARPS + sizeof(int) * ((size_t)vheads * a.nslices + 1) + 128;
+  if (rsm - 128 > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
+  char e[96];
+  snprintf(e, sizeof e, "fbla::coarse_item<%d, %d, %d>", CB, FB, QG);
+  cudaError_t st = pass_of(coarse_kernel<CB, FB, QG>, a.coarse_ctas, 1, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, e, p + 0);
+  snprintf(e, sizeof e, "fbla::select_item<%d>", QG);
+  if (st == cudaSuccess) st = pass_of(select_kernel<QG>, a.nslices, vheads, 256, 0, e, p + 1);
+  snprintf(e, sizeof e, "fbla::refine_item<%d, %d, %d>", CB, FB, QG);
+  if (st == cudaSuccess) st = pass_of(refine_kernel<CB, FB, QG>, a.refine_ctas, 1, 32 * RefineShape<CB, FB>::WARPS, rsm, e, p + 2);
+  snprintf(e, sizeof e, "fbla::merge_item<%d>", QG);
+  if (st == cudaSuccess) st = pass_of(merge_kernel<QG>, vheads * QG, 1, 512, 0, e, p + 3);
+  return st;
 }
 
 // a row's shares summed over the shards -> the BF16 output
@@ -1165,5 +160,21 @@ extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t
     case 1: return launch_all<4, 2, 1>(*a, stream);
     case 2: return launch_all<4, 2, 2>(*a, stream);
     default: return launch_all<4, 2, 4>(*a, stream);
+  }
+}
+
+extern "C" cudaError_t fbla_k_decode_passes(const fbla_k_decode *a, fbla_k_pass info[4]) {
+  using namespace fbla;
+  if (a->cb == 3) {
+    switch (a->qg) {
+      case 1: return passes_of<3, 3, 1>(*a, info);
+      case 2: return passes_of<3, 3, 2>(*a, info);
+      default: return passes_of<3, 3, 4>(*a, info);
+    }
+  }
+  switch (a->qg) {
+    case 1: return passes_of<4, 2, 1>(*a, info);
+    case 2: return passes_of<4, 2, 2>(*a, info);
+    default: return passes_of<4, 2, 4>(*a, info);
   }
 }

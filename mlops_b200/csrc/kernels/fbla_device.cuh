@@ -2,10 +2,46 @@
 // warp-level integer tensor-core instruction, 1-D bulk asynchronous copies with mbarrier completion and BOUNDED waits,
 // and the packed-record format as compile-time traits.
 #pragma once
+#ifdef __CUDACC_RTC__  // compiled at run time inside an executor's own kernels: no host headers
+typedef unsigned char uint8_t;
+typedef signed char int8_t;
+typedef unsigned short uint16_t;
+typedef unsigned int uint32_t;
+typedef int int32_t;
+typedef unsigned long long uint64_t;
+typedef long long int64_t;
+typedef unsigned long long uintptr_t;
+typedef unsigned long size_t;
+#else
 #include <cuda_runtime.h>
 #include <stdint.h>
+#endif
 
 namespace fbla {
+
+// Where a CTA stands in its pass. The library's own kernels are launched one CTA per item and read the hardware's
+// registers (GridPos); an executor that runs the passes' items from kernels of its own (include/mlops_fbla_items.h)
+// defines mlops_fbla::Pos with the same members and FBLA_POS to name it before including the item bodies.
+//   x y z nx ny nz: the item's coordinates in the pass's grid; tid: the thread within the item's CTA;
+//   ro(p): the read of a device length or count (at most once per call site);
+struct GridPos {
+  static __device__ __forceinline__ int x() { return blockIdx.x; }
+  static __device__ __forceinline__ int y() { return blockIdx.y; }
+  static __device__ __forceinline__ int z() { return blockIdx.z; }
+  static __device__ __forceinline__ int nx() { return gridDim.x; }
+  static __device__ __forceinline__ int ny() { return gridDim.y; }
+  static __device__ __forceinline__ int nz() { return gridDim.z; }
+  static __device__ __forceinline__ int tid() { return threadIdx.x; }
+  static __device__ __forceinline__ int ro(const int *p) { return __ldg(p); }
+};
+#ifndef FBLA_POS
+#define FBLA_POS ::fbla::GridPos
+#endif
+// programmatic dependent launch is used by the library's own stream launches only
+template <class A, class B> struct same_type { static constexpr bool value = false; };
+template <class A> struct same_type<A, A> { static constexpr bool value = true; };
+#define FBLA_STREAM_LAUNCH (::fbla::same_type<FBLA_POS, ::fbla::GridPos>::value)
+#define FBLA_INF (__int_as_float(0x7f800000))
 
 constexpr int D = 128;    // head dimension
 constexpr int G = 128;    // tokens per group

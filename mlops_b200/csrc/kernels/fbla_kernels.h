@@ -1,9 +1,13 @@
 // The thin C ABI between the C++ host layer (validation, geometry, dispatch) and the CUDA kernels: plain structs of
 // pointers and sizes, one launcher per pass. The host layer fills these; nothing here validates.
 #pragma once
-#include <cuda_runtime.h>
+#include "fbla_device.cuh"  /* fixed-width integers; under run-time compilation no host header is available */
+#ifndef __CUDACC_RTC__
 #include <stddef.h>
-#include <stdint.h>
+#define FBLA_HOST_API(decl) decl
+#else
+#define FBLA_HOST_API(decl)  /* launchers exist only in the library */
+#endif
 
 #ifdef __cplusplus
 extern "C" {
@@ -55,13 +59,13 @@ typedef struct {
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
 #define FBLA_K_WINDOW_WARPS 2 /* warps per coarse CTA that serve the BF16 sink / open windows */
 
-cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);
+FBLA_HOST_API(cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);)
 // out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
 // total[i] = log2 sum over shards of 2^mass[s][i]
-cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);
-cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out, int rows, cudaStream_t stream);
+FBLA_HOST_API(cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out, int rows, cudaStream_t stream);)
 // occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
-cudaError_t fbla_k_decode_shape(fbla_k_decode *a);
+FBLA_HOST_API(cudaError_t fbla_k_decode_shape(fbla_k_decode *a);)
 
 // ---- prefill: close the chunk's groups, attention, update the BF16 windows --------------------------------------------
 typedef struct {
@@ -80,15 +84,15 @@ typedef struct {
 } fbla_k_prefill;
 
 // close_blocks: grid x of the close pass (groups the chunk can close); 0 skips it
-cudaError_t fbla_k_close_launch(const fbla_k_prefill *a, int close_blocks, cudaStream_t stream);
-cudaError_t fbla_k_finish_launch(const fbla_k_prefill *a, cudaStream_t stream);
+FBLA_HOST_API(cudaError_t fbla_k_close_launch(const fbla_k_prefill *a, int close_blocks, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_finish_launch(const fbla_k_prefill *a, cudaStream_t stream);)
 // attention of the chunk's rows: the tensor-core kernel (tcgen05, 128 rows per CTA), or -- for chunks of fewer than
 // FBLA_K_TC_MIN_ROWS rows, or when the environment variable MLOPS_FBLA_PREFILL=rows asks for it -- one warp per row
-cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);
-cudaError_t fbla_k_attend_rows_launch(const fbla_k_prefill *a, cudaStream_t stream);
-cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream);
+FBLA_HOST_API(cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_rows_launch(const fbla_k_prefill *a, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream);)
 // 1 if a bounded wait of the tensor-core kernel gave up since the last call (and clears it), 0 if not, -1 on a CUDA error
-int fbla_k_attend_tc_status(void);
+FBLA_HOST_API(int fbla_k_attend_tc_status(void);)
 #define FBLA_K_TC_MIN_ROWS 64
 
 // ---- fused QKV step: RMSNorm + rotary embedding of new tokens (+ the window stores of the one-token step) ------------------
@@ -104,8 +108,24 @@ typedef struct {
   int batch, q_heads, kv_heads;
   uint16_t *q_out, *k_out, *v_out;
 } fbla_k_token;
-cudaError_t fbla_k_qkv_token_launch(const fbla_k_token *a, cudaStream_t stream);
-cudaError_t fbla_k_qkv_chunk_launch(const fbla_k_token *a, cudaStream_t stream);
+FBLA_HOST_API(cudaError_t fbla_k_qkv_token_launch(const fbla_k_token *a, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_qkv_chunk_launch(const fbla_k_token *a, cudaStream_t stream);)
+
+// ---- what an executor needs to run a pass from kernels of its own (include/mlops_fbla_items.h) ---------------------------
+typedef struct {
+  int gx, gy, gz;    // the grid of the equivalent launch: one item per CTA
+  int threads;       // the exact CTA size
+  int smem_bytes;    // shared memory to hand the entry (includes the slack entries use to re-align a 16-byte aligned pointer)
+  int regs;          // registers per thread of this library's kernel
+  char entry[96];    // the device function (kernels/*.cuh), called as entry(args, shared memory)
+} fbla_k_pass;
+FBLA_HOST_API(cudaError_t fbla_k_decode_passes(const fbla_k_decode *a, fbla_k_pass info[4]);)  // coarse, select, refine, merge
+FBLA_HOST_API(cudaError_t fbla_k_close_pass(const fbla_k_prefill *a, int close_blocks, fbla_k_pass *info);)
+FBLA_HOST_API(cudaError_t fbla_k_finish_pass(const fbla_k_prefill *a, fbla_k_pass *info);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_rows_pass(const fbla_k_prefill *a, fbla_k_pass *info);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_pass(const fbla_k_prefill *a, fbla_k_pass *info, int *tensor_cores);)
+FBLA_HOST_API(cudaError_t fbla_k_qkv_token_pass(const fbla_k_token *a, fbla_k_pass *info);)
+FBLA_HOST_API(cudaError_t fbla_k_qkv_chunk_pass(const fbla_k_token *a, fbla_k_pass *info);)
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,631 @@
+// Causal prefill attention over the compressed cache on Blackwell tensor cores: tcgen05.mma with TMEM accumulators.
+//
+// Semantics: the reference's DP4A prefill (attention/fbla/src/fbla_prefill.cuh:389-705) -- the row at position p attends
+// to 0..p: group 0 (sink) and its own group in BF16, closed groups 1..own-1 through their full 6-bit codes with the
+// per-(row, group) int8 qhat, 16-token integer P blocks p = round(255 * 2^(s - max_block)) everywhere.
+//
+// One CTA = two tiles of 128 query rows of one KV head (row r = position r / qg, query r % qg) x a sequence of "passes",
+// one per 128-token group the rows attend to. Per pass and tile, two tensor-core products with FP32 accumulators in
+// tensor memory:
+//   S[128 rows x 128 tokens]  = Qop[rows x 128 ch] . Kop[tokens x 128 ch]^T
+//   O[128 rows x 128 ch]     += P'[rows x 128 tokens] . V'[ch x 128 tokens]^T
+// Closed group: Qop = qhat (integers in [-127, 127]) and Kop = the 6-bit codes, both as FP16 -- products and the FP32
+// sums (< 2^24) are exact, so S is the reference's integer dot product; BF16 group: Qop = q, Kop = k in BF16 (exact
+// products, FP32 sums). P' = fp16(w_j p_t): the integer P block times its block weight 2^(m_j - m_row); V' =
+// fp16(base + step * code) (closed) or fp16(v) (BF16), so O accumulates across ALL passes in tensor memory and is read
+// once, at the end. The two FP16 roundings (relative 2^-11, zero mean) are the only deviations from the reference's
+// arithmetic; they stay far inside the 2e-3 output tolerance.
+//
+// Warps 0-3 / 4-7: tile 0 / 1, one thread per row (tensor-memory lane): qhat of the pass, softmax of S, P', output.
+// Warps 8-11: operands, shared by both tiles: unpack the group's records (bulk-copied raw into shared memory) into the
+// Kop / V' tiles. Warp 12: allocates tensor memory; its lane 0 issues the bulk copies and the products, which complete
+// on mbarriers. The two tiles run the same passes half a pass apart, so one tile's products overlap the other's
+// arithmetic. P' is written over qhat (dead once S is complete). Operand tiles are K-major with the 128-byte swizzle
+// (8-row x 128-byte atoms, 16-byte chunk c of row r at c ^ (r % 8)).
+// What bounds it: per (row, group) the reference's semantics need ~130 exp2 and the requantisation of the row's 128
+// query channels on the CUDA cores; the tensor-core share of a pass is about as long as its exp2 share alone.
+// Every wait is bounded: on a timeout the thread raises a flag, everybody drains, tensor memory is freed, the kernel
+// returns and the host sees fbla_k_attend_tc_status() != 0.
+#pragma once
+#include "fbla_device.cuh"
+#include "fbla_kernels.h"
+#include <cuda_fp16.h>
+
+namespace fbla {
+namespace tc {
+
+constexpr int ROWS = 128;                 // rows of a tile
+constexpr int CTA_ROWS = 2 * ROWS;
+constexpr int PRODUCER_WARP0 = 16, ISSUER_WARP = 20;  // warps 0-15: rows
+constexpr int THREADS = 21 * 32;
+constexpr int SLAB = ROWS * 128;          // bytes of one K slab (128 rows x 128 bytes): 64 FP16 / BF16 of the K extent
+constexpr int TILE = 2 * SLAB;            // a [128 x 128] 16-bit operand tile: 32 KiB
+constexpr int RAW = 8 * 3072;              // a raw group: 8 coarse + 8 fine records, 3072 bytes per pair in both formats
+constexpr uint32_t WAIT_LIMIT = 1u << 18;
+
+__device__ int g_status = 0;  // nonzero: a bounded wait gave up in some launch since the last read
+
+#ifdef FBLA_PF_TIMING  // tuning only: cycles per role and section, summed over CTAs (lane 0 of one warp per role)
+__device__ unsigned long long g_prof[64];  // 4 roles x 16 slots
+#define PF_DECL long long pf_prev = clock64(); unsigned long long pf_acc[16] = {0};
+#define PF_MARK(slot) { const long long pf_t = clock64(); pf_acc[slot] += pf_t - pf_prev; pf_prev = pf_t; }
+#define PF_FLUSH(role) { for (int pf_i = 0; pf_i < 16; ++pf_i) atomicAdd(&g_prof[16 * (role) + pf_i], pf_acc[pf_i]); }
+#else
+#define PF_DECL
+#define PF_MARK(slot)
+#define PF_FLUSH(role) {}
+#endif
+
+struct __align__(1024) Smem {
+  uint8_t q[2][TILE];   // Qop of BF16 passes: the rows' q, BF16
+  uint8_t qp[2][TILE];  // Qop of closed passes (qhat, FP16), then P' of the same pass
+  uint8_t k[TILE];      // Kop
+  uint8_t v[TILE];      // V'
+  uint8_t raw[RAW];     // the group's coarse records, then its fine records
+  uint8_t meta[1024];
+  float ks[128], kb[128];  // the group's K steps and bases as FP32
+  float qscale[2][128], qbias[2][128];  // per row of a tile: the pass's score scale and bias (from the quantising lanes to the row's threads)
+  float ex2[2][128][2];  // exchange between the two threads of a row: pass maximum, final sum
+  uint64_t bar_raw, bar_mf, bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
+  uint32_t tmem_base;
+  int abort;
+};
+
+static_assert(sizeof(Smem) + 1024 <= 232448, "operand tiles exceed the shared memory of an SM");
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t smem_desc(const void *tile_base, int slab, int kstep) {  // K-major, 128-byte swizzle
+  const uint32_t addr = smem_u32(tile_base) + slab * SLAB + kstep * 32;
+  return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+constexpr uint32_t IDESC_F16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);           // D FP32, A / B FP16, M 128, N 128
+constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);                                // A / B BF16
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, bool accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\ttcgen05.wait::ld.sync.aligned;"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+                 "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+                 "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// bounded wait (each poll may suspend up to ~2 us in hardware) that also gives up when some thread has raised the abort flag
+__device__ __forceinline__ bool try_wait_hint(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool wait(Smem &sm, uint64_t *bar, uint32_t parity) {
+  if (try_wait_hint(bar, parity)) return true;
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (*reinterpret_cast<volatile int *>(&sm.abort)) return false;
+    if (try_wait_hint(bar, parity)) return true;
+  }
+  *reinterpret_cast<volatile int *>(&sm.abort) = 1;
+  atomicExch(&g_status, 1);
+  return false;
+}
+
+// V' tile row (= O column) of channel ch: 32 (ch % 4) + ch / 4, so that the 32 lanes of a record (4 channels each) write
+// rows with all residues mod 8 -- conflict-free under the swizzle; the epilogue undoes it
+__device__ __forceinline__ int vrow(int ch) { return 32 * (ch & 3) + (ch >> 2); }
+// byte address of the 16-byte chunk holding K-extent element k0 (a multiple of 8) of tile row r
+__device__ __forceinline__ uint8_t *chunk_at(uint8_t *tile, int r, int k0) {
+  const int slab = k0 >> 6, c = (k0 & 63) >> 3;
+  return tile + slab * SLAB + r * 128 + ((c ^ (r & 7)) << 4);
+}
+
+// ---- record unpacking (the slot maps of include/mlops_fbla.h) --------------------------------------------------------------
+template <int BITS> __device__ __forceinline__ uint32_t slot_value(const uint32_t *W, int s) {  // 4 codes, one per byte, unscaled
+  if (BITS == 4) return s < 8 ? W[s] & 0x0f0f0f0fu : (W[s - 8] >> 4) & 0x0f0f0f0fu;
+  if (BITS == 2) return (W[s & 3] >> (2 * (s >> 2))) & 0x03030303u;
+  if (s < 6) return W[s] & 0x07070707u;
+  if (s < 12) return (W[s - 6] >> 3) & 0x07070707u;
+  const int r = s - 12;
+  return ((W[r] >> 6) & 0x03030303u) | ((W[4 + (r >> 1)] >> (4 + (r & 1))) & 0x04040404u);
+}
+__host__ __device__ constexpr int v_slot_of(int bits, int cc, int quad) {
+  return bits == 4 ? (cc < 2 ? 2 * quad + cc : 8 + 2 * quad + (cc - 2))
+       : bits == 2 ? 4 * cc + quad
+       : cc == 0 ? quad : cc == 1 ? 6 + quad : cc == 2 ? (quad < 2 ? 4 + quad : 8 + quad) : 12 + quad;
+}
+template <int BITS> __device__ __forceinline__ void lane_words(const uint8_t *rec, int tensor, int lane, uint32_t *W) {
+#pragma unroll
+  for (int w = 0; w < 2 * BITS; ++w) W[w] = lds32(rec + word_offset(BITS, tensor, lane, w));
+}
+// four small unsigned integers (bytes of x, each < 1024) as two packed FP16 pairs: 0x6400 | b is 1024 + b
+__device__ __forceinline__ uint2 bytes_to_half4(uint32_t x) {
+  const uint32_t lo = __byte_perm(x, 0x64646464u, 0x7170), hi = __byte_perm(x, 0x64646464u, 0x7372);  // (b1 | 0x64 << 8) << 16 | b0 | 0x64 << 8
+  const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6400));
+  const __half2 a = __hsub2(*reinterpret_cast<const __half2 *>(&lo), bias), b = __hsub2(*reinterpret_cast<const __half2 *>(&hi), bias);
+  return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// FP16 pairs (code as FP16) * step + base, one rounding
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t code2, __half2 step, __half2 base) {
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&code2), step, base);
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
+__device__ __forceinline__ float2 bf2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
+// pairs of FP32 operations: the packed FP32x2 instructions of sm_100 (FBLA_PF_SCALAR, tuning only: scalar instructions)
+#ifndef FBLA_PF_SCALAR
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+#else
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
+#endif
+
+template <int CB, int FB>
+__device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t *smem_raw) {
+  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
+  const int tid = FBLA_POS::tid(), warp = tid >> 5, lane = tid & 31;
+  const int bh = FBLA_POS::y(), b = bh / a.kv_heads, kh = bh - b * a.kv_heads, qg = a.q_heads / a.kv_heads;
+  const int n0 = (a.length ? FBLA_POS::ro(a.length + (a.lstride ? b : 0)) : 0) + a.n0;
+  const int count = a.dcount ? FBLA_POS::ro(a.dcount) : a.count, n1 = n0 + count;
+  const int rows = count * qg, r0 = FBLA_POS::x() * CTA_ROWS;
+  if (r0 >= rows) return;  // (CTA-uniform)
+  const int last_row = min(r0 + CTA_ROWS, rows) - 1;
+  const int own_min = (n0 + r0 / qg) / G, own_max = (n0 + last_row / qg) / G;
+  // passes: closed groups 1 .. own_max - 1, then the BF16 groups: 0 and the rows' own groups
+  const int n_closed = max(own_max - 1, 0), own_lo = max(own_min, 1);
+  const int n_pass = n_closed + 1 + max(own_max - own_lo + 1, 0);
+  auto pass_group = [&](int n, bool &closed) {
+    closed = n < n_closed;
+    return closed ? 1 + n : n == n_closed ? 0 : own_lo + (n - n_closed - 1);
+  };
+
+  if (tid == 0) {
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_mf, 128); mbar_init(&sm.bar_k, 128); mbar_init(&sm.bar_v, 128);
+    for (int x = 0; x < 2; ++x) { mbar_init(&sm.bar_q[x], 256); mbar_init(&sm.bar_s[x], 1); mbar_init(&sm.bar_p[x], 256); mbar_init(&sm.bar_o[x], 1); }
+    sm.abort = 0;
+    mbar_init_fence();
+  }
+  if (warp == ISSUER_WARP) {  // all 512 columns of tensor memory: S of tile x at 128 x, O at 256 + 128 x
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  const size_t head = (size_t)bh * a.hs, eh = (size_t)bh * G * D, ih = (size_t)bh * a.count * D;
+  // the BF16 row of position tp: the chunk, the sink window, or the window of the group that was open before the chunk
+  auto token_row = [&](int tp, const uint16_t *in, const uint16_t *sink, const uint16_t *open) -> const uint16_t * {
+    return tp >= n0 ? in + ih + (size_t)(tp - n0) * D : tp < G ? sink + eh + (size_t)tp * D : open + eh + (size_t)(tp - (n0 - 1) / G * G) * D;
+  };
+
+  if (warp == ISSUER_WARP) {
+    // ================= issuer: bulk copies of the raw groups, the products =================
+    if (lane == 0) {
+      auto fetch = [&](int g) {
+        const size_t unit = head + (size_t)g * a.gs;
+        mbar_expect_tx(&sm.bar_raw, SBG * (RC + RF) + 1024);
+        bulk_g2s(sm.raw, a.c.coarse + unit * SBG * RC, SBG * RC, &sm.bar_raw);
+        bulk_g2s(sm.raw + SBG * RC, a.c.fine + unit * SBG * RF, SBG * RF, &sm.bar_raw);
+        bulk_g2s(sm.meta, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &sm.bar_raw);
+      };
+      if (n_closed > 0) fetch(1);
+      PF_DECL
+      for (int n = 0; n < n_pass; ++n) {
+        bool closed;
+        pass_group(n, closed);
+        const uint32_t ph = n & 1, idesc = closed ? IDESC_F16 : IDESC_BF16;
+        // Both tiles' S first, then both tiles' O: the tiles run in step (holding tile 1 back by half a pass, so that one
+        // tile quantises while the other exponentiates, measured slower: each tile then waits for the other's operands)
+        bool ok = wait(sm, &sm.bar_k, ph);
+        PF_MARK(0)
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!(ok = wait(sm, &sm.bar_q[x], ph))) break;
+          PF_MARK(1 + x)
+          tc_fence_after();
+          const uint8_t *qop = closed ? sm.qp[x] : sm.q[x];
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) mma_f16(tmem + 128 * x, smem_desc(qop, kk >> 2, kk & 3), smem_desc(sm.k, kk >> 2, kk & 3), idesc, kk > 0);
+          mma_commit(&sm.bar_s[x]);
+        }
+        PF_MARK(3)
+        if (!ok || !wait(sm, &sm.bar_v, ph)) break;
+        PF_MARK(4)
+        if (n + 1 < n_closed) fetch(2 + n);  // the raw buffer has been consumed: the next closed group's records
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (!(ok = wait(sm, &sm.bar_p[x], ph))) break;
+          PF_MARK(5 + x)
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_f16(tmem + 256 + 128 * x, smem_desc(sm.qp[x], kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
+          mma_commit(&sm.bar_o[x]);
+        }
+        PF_MARK(7)
+        if (!ok) break;
+      }
+      PF_FLUSH(0)
+    }
+  } else if (warp >= PRODUCER_WARP0) {
+    // ================= operand producers =================
+    const int pt = tid - 32 * PRODUCER_WARP0;  // 0 .. 127
+    const int l = pt & 31;
+    int raw_uses = 0;
+    PF_DECL
+    for (int n = 0; n < n_pass; ++n) {
+      bool closed;
+      const int g = pass_group(n, closed);
+      const uint32_t prev = (n - 1) & 1;
+      if (closed) {
+        if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
+        PF_MARK(0)
+        {  // K bases and steps of channel pt as FP32 for the row threads
+          const uint8_t *m = sm.meta + 16 * (pt >> 2) + 2 * (pt & 3);
+          sm.kb[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
+          sm.ks[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
+        }
+        mbar_arrive(&sm.bar_mf);
+      }
+      // ---- Kop (free once both tiles' S of the previous pass are complete) ----
+      PF_MARK(1)
+      if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
+      PF_MARK(2)
+      if (closed) {
+        // (record j, lane l): token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
+#pragma unroll 1
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = (pt >> 5) + 4 * jj;
+          uint32_t Wc[2 * CB], Wf[2 * FB];
+          lane_words<CB>(sm.raw + j * RC, 0, l, Wc);
+          lane_words<FB>(sm.raw + SBG * RC + j * RF, 0, l, Wf);
+          const int tok = 16 * j + (l & 15);
+#pragma unroll
+          for (int s2 = 0; s2 < 8; ++s2) {
+            const uint2 x = bytes_to_half4((slot_value<CB>(Wc, 2 * s2) << FB) | slot_value<FB>(Wf, 2 * s2));
+            const uint2 y = bytes_to_half4((slot_value<CB>(Wc, 2 * s2 + 1) << FB) | slot_value<FB>(Wf, 2 * s2 + 1));
+            *reinterpret_cast<uint4 *>(chunk_at(sm.k, tok, 64 * (l >> 4) + 8 * s2)) = make_uint4(x.x, x.y, y.x, y.y);
+          }
+        }
+      } else {
+        for (int e = pt; e < G * 16; e += 128) {  // BF16 group g: K rows as they are
+          const int tk = e >> 4, c = e & 15, tp = g * G + tk;
+          const uint4 kw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.k, a.c.sink_k, a.c.open_k)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4 *>(chunk_at(sm.k, tk, 8 * c)) = kw;
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_k);
+      PF_MARK(3)
+      // ---- V' (free once both tiles' O products of the previous pass are complete) ----
+      if (n > 0 && (!wait(sm, &sm.bar_o[0], prev) || !wait(sm, &sm.bar_o[1], prev))) break;
+      PF_MARK(4)
+      if (closed) {
+        // (record j, lane l): channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code in FP16 arithmetic
+        const uint4 vm = lds128(sm.meta + 512 + 16 * l);
+        const __half2 vb[4] = {__float2half2_rn(bf_lo(vm.x)), __float2half2_rn(bf_hi(vm.x)), __float2half2_rn(bf_lo(vm.y)), __float2half2_rn(bf_hi(vm.y))};
+        const __half2 vs[4] = {__float2half2_rn(bf_lo(vm.z)), __float2half2_rn(bf_hi(vm.z)), __float2half2_rn(bf_lo(vm.w)), __float2half2_rn(bf_hi(vm.w))};
+#pragma unroll 1
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = (pt >> 5) + 4 * jj;
+          uint32_t Wc[2 * CB], Wf[2 * FB];
+          lane_words<CB>(sm.raw + j * RC, 1, l, Wc);
+          lane_words<FB>(sm.raw + SBG * RC + j * RF, 1, l, Wf);
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t h[8];
+#pragma unroll
+            for (int quad = 0; quad < 4; ++quad) {
+              const uint2 c4 = bytes_to_half4((slot_value<CB>(Wc, v_slot_of(CB, cc, quad)) << FB) | slot_value<FB>(Wf, v_slot_of(FB, cc, quad)));
+              h[2 * quad] = hfma2_bits(c4.x, vs[cc], vb[cc]);
+              h[2 * quad + 1] = hfma2_bits(c4.y, vs[cc], vb[cc]);
+            }
+            *reinterpret_cast<uint4 *>(chunk_at(sm.v, 32 * cc + l, 16 * j)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(chunk_at(sm.v, 32 * cc + l, 16 * j + 8)) = make_uint4(h[4], h[5], h[6], h[7]);
+          }
+        }
+      } else {
+        for (int e = pt; e < G * 16; e += 128) {  // V rows converted to FP16 and transposed (tokens along the K extent)
+          const int tk = e >> 4, c = e & 15, tp = g * G + tk;
+          const uint4 vw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.v, a.c.sink_v, a.c.open_v)) + c) : make_uint4(0u, 0u, 0u, 0u);
+          const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const float f = (x & 1) ? bf_hi(w4[x >> 1]) : bf_lo(w4[x >> 1]);
+            *reinterpret_cast<__half *>(chunk_at(sm.v, vrow(8 * c + x), tk & ~7) + 2 * (tk & 7)) = __float2half_rn(f);
+          }
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_v);
+      PF_MARK(5)
+    }
+    if (pt == 0) PF_FLUSH(1)
+  } else {
+    // ================= row threads: qhat, softmax, P', output =================
+    // Softmax: two threads per row (warps w and w + 8 share a tensor-memory lane quadrant): thread hf owns tokens
+    // 64 hf .. + 63 of S and P' (slab hf of the P' tile) and O columns 64 hf .. + 63; the pair meets on a named barrier to
+    // exchange the pass maximum. qhat: a different map -- a warp takes 16 rows of its tile, two rows at a time: lane
+    // (c = lane % 16, lane / 16) holds channels 8 c .. + 7 of one row, with the group's steps and bases of those channels
+    // in registers for the whole pass; max |z| and the bias dot product are reduced over the 16 lanes of a row. That
+    // keeps shared-memory traffic (the limiter of a thread-per-row quantiser, which re-reads steps and bases per row)
+    // at one load and one store per row chunk. A thread never leaves the pass loop early: after an abort every wait
+    // returns at once, so both threads of a pair still reach every named barrier.
+    const int hf = warp >> 3, X = (warp >> 2) & 1, r = 32 * (warp & 3) + lane, R = r0 + ROWS * X + r;
+    const int pair_bar = 1 + (warp & 7);
+    auto pair_sync = [&] { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    const bool valid = R < rows;
+    const int i = valid ? R / qg : 0, hq = kh * qg + (valid ? R - i * qg : 0), pos = n0 + i, own = pos / G;
+    const int tile_last = min(r0 + ROWS * X + ROWS, rows) - 1;                 // the tile's last row, if it has any
+    const int tile_own = tile_last >= r0 + ROWS * X ? (n0 + tile_last / qg) / G : -1;  // closed group g concerns the tile iff g < tile_own
+    // byte offsets of the row's eight 16-byte chunks within a slab
+    uint32_t sw[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) sw[c] = r * 128 + ((c ^ (r & 7)) << 4);
+    uint8_t *const pt_ = sm.qp[X] + hf * SLAB;  // the thread's slab of the P' tile
+    // quantiser lane: chunk qc of rows qrow0 + 2 it, it = 0 .. 7 (qrow0 % 8 is 0 or 1, so (row % 8) = (2 it) | (qrow0 & 1))
+    const int qc = lane & 15, qrow0 = 16 * ((warp & 3) + 4 * hf) + (lane >> 4);
+    const uint32_t qoff = (qc >> 3) * SLAB + qrow0 * 128, qcx = (uint32_t)((qc & 7) ^ (qrow0 & 1)) << 4;
+    const uint32_t qmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+    // the rows' q into the BF16 Q tile (rows past the end: zeros), by the same map
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rowq = qrow0 + 2 * it, Rq = r0 + ROWS * X + rowq;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (Rq < rows) {
+        const int iq = Rq / qg;
+        w = __ldg(reinterpret_cast<const uint4 *>(a.q + ((size_t)(b * a.q_heads + kh * qg + (Rq - iq * qg)) * a.count + iq) * D) + qc);
+      }
+      *reinterpret_cast<uint4 *>(sm.q[X] + qoff + 2 * it * 128 + (qcx ^ (((2 * it) & 7) << 4))) = w;
+    }
+    float m_run = -FBLA_INF, l_run = 0.f;  // l_run: this thread's tokens only
+    const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+    const uint32_t tmem_s = tmem + 128 * X + 64 * hf + lane_base, tmem_o = tmem + 256 + 128 * X + 64 * hf + lane_base;
+    int mf_uses = 0;
+    bool ok = true;
+    PF_DECL
+    for (int n = 0; n < n_pass; ++n) {
+      bool closed;
+      const int g = pass_group(n, closed);
+      const bool include = valid && (closed ? g < own : (g == 0 || g == own));
+      const bool any = __any_sync(FULL, include);
+      PF_MARK(0)
+      // the previous pass's O product has read P' (the buffer qhat goes to) and O is stable
+      if (n > 0) ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n - 1) & 1));
+      PF_MARK(1)
+      if (closed) {
+        ok &= __all_sync(FULL, wait(sm, &sm.bar_mf, mf_uses++ & 1));
+        PF_MARK(2)
+        if (g < tile_own) {
+          // qhat for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r) written as FP16; four rows per batch, with
+          // every load ahead of the arithmetic and every store behind it, so that the rows' dependency chains overlap
+          const float4 s0 = *reinterpret_cast<const float4 *>(&sm.ks[8 * qc]), s1 = *reinterpret_cast<const float4 *>(&sm.ks[8 * qc + 4]);
+          const float4 b0 = *reinterpret_cast<const float4 *>(&sm.kb[8 * qc]), b1 = *reinterpret_cast<const float4 *>(&sm.kb[8 * qc + 4]);
+          const float2 mg = splat(MAGICF), ng = splat(-MAGICF);
+          const float sl127 = __fmul_rn(a.sl, 1.f / 127.f);
+          const bool h3 = lane & 8, h2 = lane & 4;
+#pragma unroll
+          for (int bt = 0; bt < 2; ++bt) {
+            uint4 qv[4];
+            uint32_t off[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int it = 4 * bt + k;
+              off[k] = qoff + 2 * it * 128 + (qcx ^ (((2 * it) & 7) << 4));
+              qv[k] = *reinterpret_cast<const uint4 *>(sm.q[X] + off[k]);
+            }
+            float amax[4], dot[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // the lane's share of max |z| and of the bias dot product
+              const float2 q0 = bf2(qv[k].x), q1 = bf2(qv[k].y), q2 = bf2(qv[k].z), q3 = bf2(qv[k].w);
+              const float2 z0 = mul2(q0, make_float2(s0.x, s0.y)), z1 = mul2(q1, make_float2(s0.z, s0.w));
+              const float2 z2 = mul2(q2, make_float2(s1.x, s1.y)), z3 = mul2(q3, make_float2(s1.z, s1.w));
+              amax[k] = fmaxf(fmaxf(fmaxf(fabsf(z0.x), fabsf(z0.y)), fmaxf(fabsf(z1.x), fabsf(z1.y))),
+                              fmaxf(fmaxf(fabsf(z2.x), fabsf(z2.y)), fmaxf(fabsf(z3.x), fabsf(z3.y))));
+              float2 d2 = fma2(q0, make_float2(b0.x, b0.y), mul2(q1, make_float2(b0.z, b0.w)));
+              d2 = fma2(q2, make_float2(b1.x, b1.y), fma2(q3, make_float2(b1.z, b1.w), d2));
+              dot[k] = d2.x + d2.y;
+            }
+            // over the 16 lanes of a row: the maxima by independent reductions (nonnegative floats order as integers), the
+            // dot products by a merging butterfly that leaves row 2 b3 + b2 of the batch in the lanes with bits 3, 2 = b3, b2
+#pragma unroll
+            for (int k = 0; k < 4; ++k) amax[k] = __uint_as_float(__reduce_max_sync(qmask, __float_as_uint(amax[k])));
+            const float e0 = (h3 ? dot[2] : dot[0]) + __shfl_xor_sync(FULL, h3 ? dot[0] : dot[2], 8);
+            const float e1 = (h3 ? dot[3] : dot[1]) + __shfl_xor_sync(FULL, h3 ? dot[1] : dot[3], 8);
+            float dsum = (h2 ? e1 : e0) + __shfl_xor_sync(FULL, h2 ? e0 : e1, 4);
+            dsum += __shfl_xor_sync(FULL, dsum, 2);
+            dsum += __shfl_xor_sync(FULL, dsum, 1);
+            if (!(lane & 3)) sm.qbias[X][qrow0 + 2 * (4 * bt + ((lane >> 2) & 3))] = __fmul_rn(dsum, a.sl);
+            float rr[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float am = amax[k];
+              float rc;
+              asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(am));
+              rc = fmaf(fmaf(-am, rc, 1.f), rc, rc);
+              const float q0_ = __fmul_rn(127.f, rc);
+              rr[k] = am > 0.f ? fmaf(fmaf(-am, q0_, 127.f), rc, q0_) : 0.f;
+            }
+            uint4 out[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
+              const float2 rr2 = splat(rr[k]);
+              const float2 t0 = add2(fma2(mul2(bf2(qv[k].x), make_float2(s0.x, s0.y)), rr2, mg), ng);
+              const float2 t1 = add2(fma2(mul2(bf2(qv[k].y), make_float2(s0.z, s0.w)), rr2, mg), ng);
+              const float2 t2 = add2(fma2(mul2(bf2(qv[k].z), make_float2(s1.x, s1.y)), rr2, mg), ng);
+              const float2 t3 = add2(fma2(mul2(bf2(qv[k].w), make_float2(s1.z, s1.w)), rr2, mg), ng);
+              out[k] = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              *reinterpret_cast<uint4 *>(sm.qp[X] + off[k]) = out[k];
+              if (qc == 0) sm.qscale[X][qrow0 + 2 * (4 * bt + k)] = __fmul_rn(amax[k], sl127);
+            }
+          }
+        }
+      }
+      PF_MARK(3)
+      fence_async_smem();
+      mbar_arrive(&sm.bar_q[X]);
+      PF_MARK(6)
+      ok &= __all_sync(FULL, wait(sm, &sm.bar_s[X], n & 1));
+      PF_MARK(4)
+      tc_fence_after();
+      // softmax of the row over the pass's 128 tokens, by 16-token blocks; P' = fp16(2^(m_block - m_row) p)
+      const int lim = (include ? (closed ? G : pos - g * G) : -1) - 64 * hf;  // this thread's tokens 0 .. lim are attended
+      const float mul1 = closed ? sm.qscale[X][r] : a.sl, add1 = closed ? sm.qbias[X][r] : 0.f;  // score = mul x + add, monotonic in x (mul >= 0)
+      // sweep 1: the block maxima, from the raw sums
+      float mbk[4];
+      if (any) {
+#pragma unroll
+        for (int cq = 0; cq < 2; ++cq) {
+          uint32_t x[32];
+          tmem_ld32(tmem_s + 32 * cq, x);
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const int t0 = 32 * cq + 16 * hb;
+            float xm = -FBLA_INF;
+            if (lim >= t0 + 15) {
+#pragma unroll
+              for (int t = 0; t < 16; t += 2) xm = fmaxf(xm, fmaxf(__uint_as_float(x[16 * hb + t]), __uint_as_float(x[16 * hb + t + 1])));
+            } else {
+#pragma unroll
+              for (int t = 0; t < 16; ++t) if (t0 + t <= lim) xm = fmaxf(xm, __uint_as_float(x[16 * hb + t]));
+            }
+            mbk[2 * cq + hb] = xm == -FBLA_INF ? -FBLA_INF : fmaf(mul1, xm, add1);  // -inf: a block without attended tokens
+          }
+        }
+        sm.ex2[X][r][hf] = fmaxf(fmaxf(mbk[0], mbk[1]), fmaxf(mbk[2], mbk[3]));
+      }
+      pair_sync();
+      if (!any) {  // (warp-uniform, and the same in both warps of the pair) nothing to attend: P' = 0
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(pt_ + sw[c]) = make_uint4(0u, 0u, 0u, 0u);
+      } else {
+        const float2 e = *reinterpret_cast<const float2 *>(&sm.ex2[X][r][0]);
+        const float mp = fmaxf(e.x, e.y);
+        PF_MARK(10)
+        // the row's running maximum moves only when a block exceeds it by more than 2^8 (rare): its sums and its O row in
+        // tensor memory are rescaled. Tensor-memory accesses are warp-wide, so the whole warp takes part (rows that do
+        // not move scale by 1); both threads of a row decide alike and each rescales its own 64 columns.
+        const bool need = mp > m_run + 8.f;
+        if (__any_sync(FULL, need)) {
+          const float al = need ? ex2(m_run - mp) : 1.f;  // 0 on the row's first attended block
+          if (n > 0) {
+#pragma unroll 1
+            for (int oc = 0; oc < 2; ++oc) {
+              uint32_t o[32];
+              tmem_ld32(tmem_o + 32 * oc, o);
+#pragma unroll
+              for (int z = 0; z < 32; ++z) o[z] = __float_as_uint(__uint_as_float(o[z]) * al);
+              tmem_st32(tmem_o + 32 * oc, o);
+            }
+          }
+          if (need) { l_run *= al; m_run = mp; }
+        }
+        PF_MARK(11)
+        // sweep 2: the integer P blocks times their weights
+        const float2 mul = splat(mul1), add = splat(add1), c255 = splat(255.f), mg = splat(MAGICF), ng = splat(-MAGICF);
+        float2 lacc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int cq = 0; cq < 2; ++cq) {
+          uint32_t x[32];
+          tmem_ld32(tmem_s + 32 * cq, x);
+#pragma unroll
+          for (int hb = 0; hb < 2; ++hb) {
+            const int t0 = 32 * cq + 16 * hb;
+            const float mb = mbk[2 * cq + hb];
+            const float2 nm = splat(mb == -FBLA_INF ? 0.f : -mb), w2 = splat(mb == -FBLA_INF ? 0.f : ex2(mb - m_run));
+            float2 sc[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t)
+              sc[t] = fma2(make_float2(__uint_as_float(x[16 * hb + 2 * t]), __uint_as_float(x[16 * hb + 2 * t + 1])), mul, add);
+            if (lim < t0 + 15) {  // the causal edge (or a row that does not attend to this group)
+#pragma unroll
+              for (int t = 0; t < 8; ++t) {
+                if (t0 + 2 * t > lim) sc[t].x = -FBLA_INF;
+                if (t0 + 2 * t + 1 > lim) sc[t].y = -FBLA_INF;
+              }
+            }
+            uint32_t h[8];
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const float2 d = add2(sc[t], nm);
+              const float2 pf = add2(fma2(make_float2(ex2(d.x), ex2(d.y)), c255, mg), ng);
+              acc = add2(acc, pf);
+              const float2 pw = mul2(pf, w2);
+              h[t] = pack_half2(pw.x, pw.y);
+            }
+            lacc = fma2(acc, w2, lacc);
+            *reinterpret_cast<uint4 *>(pt_ + sw[4 * cq + 2 * hb]) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4 *>(pt_ + sw[4 * cq + 2 * hb + 1]) = make_uint4(h[4], h[5], h[6], h[7]);
+          }
+        }
+        l_run += lacc.x + lacc.y;
+      }
+      PF_MARK(5)
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(&sm.bar_p[X]);
+      PF_MARK(7)
+    }
+    if (lane == 0 && hf == 0 && (warp & 3) == 0) PF_FLUSH(2 + X)
+    ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n_pass - 1) & 1));
+    tc_fence_after();
+    pair_sync();  // (the partner has read the last pass's exchange)
+    sm.ex2[X][r][hf] = l_run;
+    pair_sync();
+    {
+      // O column 32 cc + l is channel 4 l + cc: through the row's (now free) P' row as BF16 in channel order, then out.
+      // This thread: O columns 64 hf .. + 63 (cc = 2 hf, 2 hf + 1); then it copies chunks 8 hf .. + 7 of the row.
+      const float inv = 1.f / (sm.ex2[X][r][0] + sm.ex2[X][r][1]);
+      uint16_t *stage = reinterpret_cast<uint16_t *>(sm.qp[X] + r * 256);  // 256 bytes per row, private to the pair
+#pragma unroll 1
+      for (int cu = 0; cu < 2; ++cu) {
+        const int cc = 2 * hf + cu;
+        uint32_t o[32];
+        tmem_ld32(tmem_o + 32 * cu, o);
+#pragma unroll
+        for (int l = 0; l < 32; ++l)  // channel 4 l + cc: 16-byte chunk l / 2 of the row, stored at chunk (l / 2) ^ (r % 16)
+          stage[8 * ((l >> 1) ^ (r & 15)) + 4 * (l & 1) + cc] = f32_to_bf16(__uint_as_float(o[l]) * inv);
+      }
+      pair_sync();
+      if (valid && ok) {
+        uint16_t *orow = a.out + (size_t)(b * a.q_heads + hq) * a.out_hs + (size_t)i * a.out_ts;
+#pragma unroll
+        for (int c = 8 * hf; c < 8 * hf + 8; ++c) reinterpret_cast<uint4 *>(orow)[c] = reinterpret_cast<const uint4 *>(stage)[c ^ (r & 15)];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == ISSUER_WARP) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
+}  // namespace tc
+}  // namespace fbla
