@@ -585,7 +585,7 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   using Sh = CoarseShape<CB>;
   FBLA_T0
   allow_next_pass();
-  smem_raw = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);  // (an executor's storage is 16-byte aligned)
+  smem_raw += (128u - (smem_u32(smem_raw) & 127u)) & 127u;  // (an executor's storage is 16-byte aligned; an offset keeps the pointer's address space known)
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = FBLA_POS::tid() & 31, warp = FBLA_POS::tid() >> 5;
   if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
@@ -758,7 +758,7 @@ template <int CB, int FB, int QG>
 __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *smem_raw) {
   using Sh = RefineShape<CB, FB>;
   constexpr float HOFF = .5f * ((1 << FB) - 1);
-  smem_raw = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);  // (an executor's storage is 16-byte aligned)
+  smem_raw += (128u - (smem_u32(smem_raw) & 127u)) & 127u;  // (an executor's storage is 16-byte aligned; an offset keeps the pointer's address space known)
   RefineWarp<CB, FB> *ws = reinterpret_cast<RefineWarp<CB, FB> *>(smem_raw);
   int *pre = reinterpret_cast<int *>(smem_raw + sizeof(RefineWarp<CB, FB>) * Sh::WARPS);  // [entries + 1]
   __shared__ int chunk_sum[256];

@@ -182,7 +182,8 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return ma
 
 template <int CB, int FB>
 __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t *smem_raw) {
-  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  smem_raw += (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;  // (an offset, not a rebuilt pointer: the address space stays known)
+  Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
   constexpr int RC = record_bytes(CB), RF = record_bytes(FB);
   const int tid = FBLA_POS::tid(), warp = tid >> 5, lane = tid & 31;
   const int bh = FBLA_POS::y(), b = bh / a.kv_heads, kh = bh - b * a.kv_heads, qg = a.q_heads / a.kv_heads;
