@@ -28,6 +28,10 @@ import numpy as np  # noqa: E402
 
 CFG = dict(batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002)
 METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of the four kernels of one decode step of this workload, from the ncu capture of
+# `bench.py --steps 4 --warmup 3` summarised in profiles/decode_b8_ctx16k_4p2_launches.md (coarse 152.6 MB, select 1.9 MB,
+# refine 164.0 MB, merge 7.2 MB); reported only while the refined share is the one of that capture
+NCU_DRAM_BYTES_PER_STEP = 325745920
 
 
 def make_inputs(rank=0):
@@ -226,7 +230,8 @@ def run_ours(args):
                     e2e=dict(value=world * CFG["batch"] / (ms_e2e / args.steps * 1e-3), unit=UNIT, h2d_bytes_per_step=q_host.numel() * 2,
                              d2h_bytes_per_step=out_host.numel() * 2),
                     gpu_launches=4 * args.steps,
-                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None, peak_kind=peak_kind,
+                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
+                                  traffic=NCU_DRAM_BYTES_PER_STEP if abs(share - 0.776) < 0.01 else None, peak_kind=peak_kind,
                                   kernel="decode call (coarse + select + refine + merge)", algorithmic_bytes=abytes, bytes_parts=parts),
                     clocks=clocks)
         if world == 1 and not light:
