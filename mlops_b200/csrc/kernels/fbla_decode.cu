@@ -125,15 +125,6 @@ extern "C" cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out
   return cudaGetLastError();
 }
 
-#ifdef FBLA_TIMING
-extern "C" cudaError_t fbla_k_debug_read(long long *host) { return cudaMemcpyFromSymbol(host, fbla::fbla_dbg, sizeof(fbla::fbla_dbg)); }
-extern "C" cudaError_t fbla_k_debug_sections(long long *host, int clear) {
-  cudaError_t e = cudaMemcpyFromSymbol(host, fbla::fbla_sec, sizeof(fbla::fbla_sec));
-  if (clear) { static long long zero[148 * 16 * 8]; cudaMemcpyToSymbol(fbla::fbla_sec, zero, sizeof(zero)); }
-  return e;
-}
-#endif
-
 extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);

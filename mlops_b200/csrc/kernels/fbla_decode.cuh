@@ -360,15 +360,6 @@ template <int CB> struct Ring {
   __device__ __forceinline__ bool wait_pair(int p) { return __all_sync(FULL, mbar_wait_bounded(&w.bar_pair[p % Sh::NP], (uint32_t)((p / Sh::NP) & 1))); }
 };
 
-#ifdef FBLA_TIMING
-__device__ long long fbla_sec[148 * 16 * 8];
-__shared__ long long fbla_sec_sm[16 * 8];
-#define SEC(i) { const long long t_ = clock64(); if ((FBLA_POS::tid() & 31) == 0) fbla_sec_sm[(FBLA_POS::tid() >> 5) * 8 + (i)] += t_ - tsec_; tsec_ = clock64(); }
-#define SEC0 long long tsec_ = clock64();
-#else
-#define SEC(i)
-#define SEC0
-#endif
 // Group k of the warp's range. Returns false if a bounded wait gave up.
 template <int CB, int FB, int QG>
 __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4 (&q4)[QG], float sl, int lane, Run &run,
@@ -571,19 +562,10 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
   }
 }
 
-#ifdef FBLA_TIMING  // tuning builds only: cycles every warp of the coarse kernel spent, read back by fbla_k_debug_read
-__device__ long long fbla_dbg[148 * 16];
-#define FBLA_T0 const long long t0_ = clock64(); if ((FBLA_POS::tid() & 31) == 0) for (int i_ = 0; i_ < 8; ++i_) fbla_sec_sm[(FBLA_POS::tid() >> 5) * 8 + i_] = 0;
-#define FBLA_T1 if ((FBLA_POS::tid() & 31) == 0) { fbla_dbg[FBLA_POS::x() * 16 + (FBLA_POS::tid() >> 5)] = clock64() - t0_; for (int i_ = 0; i_ < 8; ++i_) fbla_sec[(FBLA_POS::x() * 16 + (FBLA_POS::tid() >> 5)) * 8 + i_] = fbla_sec_sm[(FBLA_POS::tid() >> 5) * 8 + i_]; }
-#else
-#define FBLA_T0
-#define FBLA_T1
-#endif
 
 template <int CB, int FB, int QG>
 __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *smem_raw) {
   using Sh = CoarseShape<CB>;
-  FBLA_T0
   allow_next_pass();
   smem_raw += (128u - (smem_u32(smem_raw) & 127u)) & 127u;  // (an executor's storage is 16-byte aligned; an offset keeps the pointer's address space known)
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
@@ -594,7 +576,6 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
     return;
 #endif
     exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, FBLA_POS::x() * XWARPS + (warp - Sh::WARPS), FBLA_POS::nx() * XWARPS);
-    FBLA_T1
     return;
   }
 #ifdef FBLA_NOSTREAM  // tuning builds only
@@ -642,7 +623,6 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
     }
   }
   write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
-  FBLA_T1
 }
 
 // ---- which partial slots belong to a virtual head ------------------------------------------------------------------------

@@ -3,9 +3,9 @@
 # reference's own build system, which refuses architectures newer than sm_90) into oracle/_ref/ as a shared object.
 # Test infrastructure: the GPU parity tests and the bench's reference-GPU row load it next to the product library to
 # compare results on identical inputs. Sources are compiled where they lie; nothing is copied into this repository.
-#   usage: oracle/build_ref.sh [/root/reference]
+#   usage: oracle/build_ref.sh <path to the reference tree>   (default: $MLOPS_REFERENCE_ROOT)
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${MLOPS_REFERENCE_ROOT:?give the path to the reference tree}}"
 A="$REF/attention"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"

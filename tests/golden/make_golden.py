@@ -7,7 +7,7 @@
                                                         DP4A prefill of one position, test_attention.py:213-225)
 
 Run in the build container, where the reference tree is mounted:
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the reference tree>
 The fixture holds only OUTPUTS of reference code; the inputs are regenerated from seeds by tests/datagen.py.
 Records are packed by the oracle and accepted into the fixture only after the reference's decoder has read the
 expected codes back from them.
@@ -125,4 +125,4 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["MLOPS_REFERENCE_ROOT"])

@@ -4,7 +4,7 @@
 
 and, for the rotation and the RMSNorm, whose only CPU statement in the reference is the formula (transformers'
 apply_rotary_pos_emb and Qwen3RMSNorm, cited by attention/include/mlops_fbla.h:169-172), a float64 evaluation of that
-formula on seeded inputs. Run in the build container:  python tests/golden/make_rope_golden.py /root/reference
+formula on seeded inputs. Run in the build container:  python tests/golden/make_rope_golden.py <path to the reference tree>
 """
 import importlib.util
 import os
@@ -55,4 +55,4 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["MLOPS_REFERENCE_ROOT"])

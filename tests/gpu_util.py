@@ -184,7 +184,9 @@ class CLib:
     def qkv_prefill_at(self, proj, q_heads, kv_heads, length, count, max_count, capacity, freq, q_norm=None, k_norm=None, eps=1e-6, att=0.0,
                        tokens_offset=0, fill=None):
         """proj [rows, kv_heads * (qg + 2) * 128] bf16; returns (q [q_heads, max_count, 128], k, v [kv_heads, max_count, 128])."""
-        mk = lambda h: (torch.empty if fill is None else lambda *a, **k: torch.full(*a, fill, **k))((h, max_count, 128), dtype=torch.bfloat16, device=proj.device)
+        def mk(h):
+            shape, kw = (h, max_count, 128), dict(dtype=torch.bfloat16, device=proj.device)
+            return torch.empty(shape, **kw) if fill is None else torch.full(shape, fill, **kw)
         q_out, k_out, v_out = mk(q_heads), mk(kv_heads), mk(kv_heads)
         cfg = Config(1, q_heads, kv_heads, tokens_offset, 0, 0, 0, capacity, 0, 0, 0, 0, 0)
         tok = self._token(proj, q_heads, kv_heads, proj.shape[1], q_norm, k_norm, eps, freq, att, None)
