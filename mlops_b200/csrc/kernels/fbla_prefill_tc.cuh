@@ -62,11 +62,11 @@ struct __align__(1024) Smem {
   uint8_t k[TILE];      // Kop
   uint8_t v[TILE];      // V'
   uint8_t raw[RAW];     // the group's coarse records, then its fine records
-  uint8_t meta[1024];
+  uint8_t meta[2][1024];  // the metadata of closed pass c in buffer c % 2, fetched two passes ahead
   float ks[128], kb[128];  // the group's K steps and bases as FP32
   float qscale[2][128], qbias[2][128];  // per row of a tile: the pass's score scale and bias (from the quantising lanes to the row's threads)
   float ex2[2][128][2];  // exchange between the two threads of a row: pass maximum, final sum
-  uint64_t bar_raw, bar_mf, bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
+  uint64_t bar_raw, bar_meta[2], bar_mf, bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -202,7 +202,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   };
 
   if (tid == 0) {
-    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_mf, 128); mbar_init(&sm.bar_k, 128); mbar_init(&sm.bar_v, 128);
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_meta[0], 1); mbar_init(&sm.bar_meta[1], 1); mbar_init(&sm.bar_mf, 128); mbar_init(&sm.bar_k, 128); mbar_init(&sm.bar_v, 128);
     for (int x = 0; x < 2; ++x) { mbar_init(&sm.bar_q[x], 256); mbar_init(&sm.bar_s[x], 1); mbar_init(&sm.bar_p[x], 256); mbar_init(&sm.bar_o[x], 1); }
     sm.abort = 0;
     mbar_init_fence();
@@ -226,12 +226,16 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     if (lane == 0) {
       auto fetch = [&](int g) {
         const size_t unit = head + (size_t)g * a.gs;
-        mbar_expect_tx(&sm.bar_raw, SBG * (RC + RF) + 1024);
+        mbar_expect_tx(&sm.bar_raw, SBG * (RC + RF));
         bulk_g2s(sm.raw, a.c.coarse + unit * SBG * RC, SBG * RC, &sm.bar_raw);
         bulk_g2s(sm.raw + SBG * RC, a.c.fine + unit * SBG * RF, SBG * RF, &sm.bar_raw);
-        bulk_g2s(sm.meta, reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &sm.bar_raw);
       };
-      if (n_closed > 0) fetch(1);
+      auto fetch_meta = [&](int c) {  // closed pass c = group 1 + c: 1 KiB, two passes ahead of its use
+        mbar_expect_tx(&sm.bar_meta[c & 1], 1024);
+        bulk_g2s(sm.meta[c & 1], reinterpret_cast<const uint8_t *>(a.c.meta) + (head + (size_t)(1 + c) * a.gs) * 1024, 1024, &sm.bar_meta[c & 1]);
+      };
+      if (n_closed > 0) { fetch(1); fetch_meta(0); }
+      if (n_closed > 1) fetch_meta(1);
       PF_DECL
       for (int n = 0; n < n_pass; ++n) {
         bool closed;
@@ -254,6 +258,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
         if (!ok || !wait(sm, &sm.bar_v, ph)) break;
         PF_MARK(4)
         if (n + 1 < n_closed) fetch(2 + n);  // the raw buffer has been consumed: the next closed group's records
+        if (n + 2 < n_closed) fetch_meta(n + 2);  // (this pass's metadata has been consumed too)
         for (int x = 0; x < 2 && ok; ++x) {
           if (!(ok = wait(sm, &sm.bar_p[x], ph))) break;
           PF_MARK(5 + x)
@@ -278,20 +283,22 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       bool closed;
       const int g = pass_group(n, closed);
       const uint32_t prev = (n - 1) & 1;
+      // ---- Kop (free once both tiles' S of the previous pass are complete; the row threads are then done with the previous
+      // pass's steps and bases too) ----
+      PF_MARK(1)
+      if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
+      PF_MARK(2)
       if (closed) {
-        if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
-        PF_MARK(0)
-        {  // K bases and steps of channel pt as FP32 for the row threads
-          const uint8_t *m = sm.meta + 16 * (pt >> 2) + 2 * (pt & 3);
+        if (!wait(sm, &sm.bar_meta[n & 1], (uint32_t)(n >> 1) & 1u)) break;
+        {  // K bases and steps of channel pt as FP32 for the row threads: long before they ask for them
+          const uint8_t *m = sm.meta[n & 1] + 16 * (pt >> 2) + 2 * (pt & 3);
           sm.kb[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
           sm.ks[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
         }
         mbar_arrive(&sm.bar_mf);
+        if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
+        PF_MARK(0)
       }
-      // ---- Kop (free once both tiles' S of the previous pass are complete) ----
-      PF_MARK(1)
-      if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
-      PF_MARK(2)
       if (closed) {
         // (record j, lane l): token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
 #pragma unroll 1
@@ -323,7 +330,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       PF_MARK(4)
       if (closed) {
         // (record j, lane l): channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code in FP16 arithmetic
-        const uint4 vm = lds128(sm.meta + 512 + 16 * l);
+        const uint4 vm = lds128(sm.meta[n & 1] + 512 + 16 * l);
         const __half2 vb[4] = {__float2half2_rn(bf_lo(vm.x)), __float2half2_rn(bf_hi(vm.x)), __float2half2_rn(bf_lo(vm.y)), __float2half2_rn(bf_hi(vm.y))};
         const __half2 vs[4] = {__float2half2_rn(bf_lo(vm.z)), __float2half2_rn(bf_hi(vm.z)), __float2half2_rn(bf_lo(vm.w)), __float2half2_rn(bf_hi(vm.w))};
 #pragma unroll 1
