@@ -26,7 +26,10 @@ sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
 
-CFG = dict(batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002)
+CFG = dict(batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002, outliers=True,
+           name="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1])")
+# the metric's headline shape: one sequence of 131 072 tokens, plain N(0,1) inputs as in configs[2]
+LONG = dict(batch=1, q_heads=32, kv_heads=8, tokens=131072, seed=1003, outliers=False)
 METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of the four kernels of one decode step of this workload, from the ncu capture of
 # `bench.py --steps 4 --warmup 3` summarised in profiles/decode_b8_ctx16k_4p2_launches.md (coarse 152.6 MB, select 1.9 MB,
@@ -36,7 +39,7 @@ NCU_DRAM_BYTES_PER_STEP = 325745920
 
 def make_inputs(rank=0):
     from tests import datagen
-    return datagen.baseline_case(CFG["seed"] + 7919 * rank, CFG["batch"], CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=True)
+    return datagen.baseline_case(CFG["seed"] + 7919 * rank, CFG["batch"], CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=CFG["outliers"])
 
 
 def algorithmic_bytes(share):
@@ -98,7 +101,8 @@ def cpu_baseline(rows=8, repeats=3):
     """The oracle's port of the reference's host-side decode model on `rows` of the workload's batch rows, `repeats` times."""
     from oracle import fbla_oracle as orc
     from tests import datagen
-    q, k, v = datagen.baseline_case(CFG["seed"], rows, CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=True)
+    rows = min(rows, CFG["batch"])
+    q, k, v = datagen.baseline_case(CFG["seed"], rows, CFG["q_heads"], CFG["kv_heads"], CFG["tokens"], outliers=CFG["outliers"])
     cache = orc.encode(k, v, CFG["mode"])
     t0 = time.perf_counter()
     for _ in range(repeats):
@@ -123,7 +127,7 @@ def run_reference(args):
     base["value"] = v
     line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=len(vals), warmup=1, ms_per_step=1000.0 * CFG["batch"] / v,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64", data="synthetic", impl="reference",
-                config=dict(workload="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1])", **{k: CFG[k] for k in ("batch", "q_heads", "kv_heads", "tokens", "mode")}),
+                config=dict(workload=CFG["name"], **{k: CFG[k] for k in ("batch", "q_heads", "kv_heads", "tokens", "mode")}),
                 cpu_baseline=base, e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
     print(json.dumps(line))
 
@@ -225,13 +229,13 @@ def run_ours(args):
         value = world * CFG["batch"] / (per_step * 1e-3)
         line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=per_step,
                     higher_is_better=True, scaling="weak", vs_baseline=None, dtype="u8", data="synthetic",
-                    config=dict(workload="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1]); per rank", l2="two cache copies alternated, 2 x 210 MB > L2",
+                    config=dict(workload=CFG["name"] + "; per rank", l2="two cache copies alternated, together larger than L2",
                                 refined_share=share, **{k: CFG[k] for k in ("batch", "q_heads", "kv_heads", "tokens", "mode")}),
                     e2e=dict(value=world * CFG["batch"] / (ms_e2e / args.steps * 1e-3), unit=UNIT, h2d_bytes_per_step=q_host.numel() * 2,
                              d2h_bytes_per_step=out_host.numel() * 2),
                     gpu_launches=4 * args.steps,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=NCU_DRAM_BYTES_PER_STEP if abs(share - 0.776) < 0.01 else None, peak_kind=peak_kind,
+                                  traffic=NCU_DRAM_BYTES_PER_STEP if CFG["tokens"] == 16384 and abs(share - 0.776) < 0.01 else None, peak_kind=peak_kind,
                                   kernel="decode call (coarse + select + refine + merge)", algorithmic_bytes=abytes, bytes_parts=parts),
                     clocks=clocks)
         if world == 1 and not light:
@@ -438,10 +442,14 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "seqsplit_256k", "seqsplit_1m", "prefill_b4", "prefill_b1"],
-                    help="decode_b8: the headline (BASELINE configs[1]); seqsplit_*: one long sequence split over the ranks (configs[2]); "
+    ap.add_argument("--workload", default="decode_b8", choices=["decode_b8", "decode_128k_3p3", "decode_128k_4p2", "seqsplit_256k", "seqsplit_1m", "prefill_b4", "prefill_b1"],
+                    help="decode_b8: the headline (BASELINE configs[1]); decode_128k_*: one 131 072-token sequence; seqsplit_*: one long sequence split over the ranks (configs[2]); "
                          "prefill_b4: causal prefill in TFLOP/s (configs[3]); prefill_b1: one of its four sequences (profiler captures)")
     args = ap.parse_args()
+    if args.workload.startswith("decode_128k"):  # the metric's headline context length, batch 1, either format
+        mode = "3+3" if args.workload.endswith("3p3") else "4+2"
+        CFG.update(LONG, mode=mode, name=f"decode B1 32q/8kv ctx131072 {mode} (the metric's headline context)")
+        args.workload = "decode_b8"
     if args.workload.startswith("prefill") and args.impl == "ours":
         return run_prefill(args)
     if args.workload != "decode_b8" and args.impl == "ours":
