@@ -997,16 +997,19 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
   const float Rq = __ldcg(a.row_r + vh * QG + qi);
   float O = 0.f, L = 0.f;
   const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
-  for (int i0 = sl; i0 < n; i0 += 16) {
-    float m[4], l[4], o[4];
+  // (a long sequence at a small batch gives a head ~200 partial rows: MJ loads per thread in flight keep the number of
+  // dependent round trips to memory small; the summation order is fixed by the loop alone)
+  constexpr int MJ = 12;
+  for (int i0 = sl; i0 < n; i0 += 4 * MJ) {
+    float m[MJ], l[MJ], o[MJ];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < MJ; ++j) {
       const int i = min(i0 + 4 * j, n - 1);
       const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, qi) : window_slot(a, s.x0 + i - nc, vh, qi);
       m[j] = __ldcg(p + D); l[j] = __ldcg(p + D + 1); o[j] = __ldcg(p + ch);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < MJ; ++j)
       if (i0 + 4 * j < n) {
         const float e = m[j] == -FBLA_INF ? 0.f : ex2(m[j] - Rq);
         L = fmaf(e, l[j], L); O = fmaf(e, o[j], O);
