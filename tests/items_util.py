@@ -66,18 +66,20 @@ def compile_program(source, want_cubin=True):
             ("-I" + os.path.join(ROOT, "include")).encode(), ("-I" + CUDA_INCLUDE).encode()]
     err, = nvrtc.nvrtcCompileProgram(prog, len(opts), opts)
     _, n = nvrtc.nvrtcGetProgramLogSize(prog)
-    log = b" " * n
+    log = b" " * (n + 8)  # (never a one-byte object: CPython shares those, and the call writes into the buffer)
     nvrtc.nvrtcGetProgramLog(prog, log)
     if err != nvrtc.nvrtcResult.NVRTC_SUCCESS:
         raise RuntimeError("NVRTC: " + log.decode(errors="replace")[-4000:])
     if want_cubin:
         _, size = nvrtc.nvrtcGetCUBINSize(prog)
-        out = b" " * size
+        out = b" " * (size + 8)
         nvrtc.nvrtcGetCUBIN(prog, out)
+        out = out[:size]
     else:
         _, size = nvrtc.nvrtcGetPTXSize(prog)
-        out = b" " * size
+        out = b" " * (size + 8)
         nvrtc.nvrtcGetPTX(prog, out)
+        out = out[:size]
     return out
 
 

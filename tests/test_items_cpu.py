@@ -38,3 +38,32 @@ def test_every_entry_compiles_under_an_executor_policy():
     for i in range(len(ENTRIES)):
         assert f".entry k{i}(" in text
     assert "tcgen05.mma" in text and "cp.async.bulk" in text and "griddepcontrol" not in text  # no dependent-launch waits under an executor
+
+
+def test_plan_builders_reject_bad_arguments_before_touching_a_device():
+    """Validation is the stream calls' own and comes first: a bad call returns -1 with the call's message, no CUDA involved."""
+    import os
+    from tests import gpu_util as gu
+    if not os.path.exists(gu.OURS):
+        pytest.skip("library not built")
+    lib = ctypes.CDLL(gu.OURS)
+    lib.mlops_fbla_last_error.restype = ctypes.c_char_p
+    vp = ctypes.c_void_p
+    cache = gu.Cache(*([0x1000] * 7), None)
+    cfg = gu.Config(1, 4, 2, 0, 0, 0, 1, 4096, 0, 0, 0, 0, 0)
+    passes = (iu.Items * 4)()
+    # decode_at: odd q_heads / kv_heads
+    bad = gu.Config(1, 3, 2, 0, 0, 0, 1, 4096, 0, 0, 0, 0, 0)
+    assert lib.mlops_fbla_decode_at_items(ctypes.byref(bad), vp(0x1000), vp(0x1000), ctypes.byref(cache), vp(0x1000), vp(0x1000), ctypes.c_size_t(1 << 30), 0, passes, 4) == -1
+    assert b"q_heads" in lib.mlops_fbla_last_error()
+    # prefill_at: chunk beyond the capacity
+    assert lib.mlops_fbla_prefill_at_items(ctypes.byref(cfg), vp(0x1000), vp(0x1000), 5000, vp(0x1000), vp(0x1000), vp(0x1000), ctypes.byref(cache), vp(0x1000), passes, 4) == -1
+    assert b"capacity" in lib.mlops_fbla_last_error()
+    # append_at: misaligned k
+    assert lib.mlops_fbla_append_at_items(ctypes.byref(cfg), vp(0x1000), vp(0x1002), vp(0x1000), ctypes.byref(cache), passes, 4) == -1
+    assert b"aligned" in lib.mlops_fbla_last_error()
+    # qkv: a norm weight without its partner
+    tok = gu.Token(0x1000, 0x1000, 0x1000, 1024, 768, 768, 0x1000, None, 1e-6, 0x1000, 0.0, 0x1000)
+    assert lib.mlops_fbla_qkv_at_items(ctypes.byref(cfg), vp(0x1000), ctypes.byref(tok), ctypes.byref(cache), passes, 4) == -1
+    assert b"both or neither" in lib.mlops_fbla_last_error()
+    assert lib.mlops_fbla_item_access(passes, 4, 7, 0, None, 0) == -1  # pass out of range
