@@ -29,11 +29,14 @@ constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 #ifndef FBLA_RNST
 #define FBLA_RNST 2  /* refine ring stages per warp */
 #endif
+// Seven streaming warps and one window warp per CTA: eight warps leave a thread 255 registers, which the coarse loop
+// needs to run without spills. Measured on B200 (decode batch 8 x 16K 4+2 / batch 1 x 128K 3+3 / 4+2, us per step):
+// 10 + 2 warps (168 registers) 135.5 / 80.3 / 78.1; 8 + 2: 121.3 / 81.0 / 65.2; 7 + 1: 121.7 / 76.3 / 63.5; 6 + 2: 131.6 / 84.3 / 68.6.
 #ifndef FBLA_CW4
-#define FBLA_CW4 10
+#define FBLA_CW4 7
 #endif
 #ifndef FBLA_CW3
-#define FBLA_CW3 10
+#define FBLA_CW3 7
 #endif
 #ifndef FBLA_NP
 #define FBLA_NP 2

@@ -57,7 +57,9 @@ typedef struct {
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
-#define FBLA_K_WINDOW_WARPS 2 /* warps per coarse CTA that serve the BF16 sink / open windows */
+#ifndef FBLA_K_WINDOW_WARPS
+#define FBLA_K_WINDOW_WARPS 1 /* warps per coarse CTA that serve the BF16 sink / open windows */
+#endif
 
 FBLA_HOST_API(cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);)
 // out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
