@@ -32,9 +32,9 @@ CFG = dict(batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002,
 LONG = dict(batch=1, q_heads=32, kv_heads=8, tokens=131072, seed=1003, outliers=False)
 METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of the four kernels of one decode step of this workload, from the ncu capture of
-# `bench.py --steps 4 --warmup 3` summarised in profiles/decode_b8_ctx16k_4p2_launches.md (coarse 152.6 MB, select 1.9 MB,
-# refine 164.0 MB, merge 7.2 MB); reported only while the refined share is the one of that capture
-NCU_DRAM_BYTES_PER_STEP = 325745920
+# `bench.py --steps 4 --warmup 3` summarised in profiles/decode_b8_ctx16k_4p2_launches.md (coarse 153.7 MB, select 1.7 MB,
+# refine 164.7 MB, merge 6.5 MB); reported only while the refined share is the one of that capture
+NCU_DRAM_BYTES_PER_STEP = 326601984
 
 
 def make_inputs(rank=0):
