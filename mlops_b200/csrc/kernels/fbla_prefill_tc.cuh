@@ -16,11 +16,10 @@
 // once, at the end. The two FP16 roundings (relative 2^-11, zero mean) are the only deviations from the reference's
 // arithmetic; they stay far inside the 2e-3 output tolerance.
 //
-// Warps 0-3 / 4-7: tile 0 / 1, one thread per row (tensor-memory lane): qhat of the pass, softmax of S, P', output.
-// Warps 8-11: operands, shared by both tiles: unpack the group's records (bulk-copied raw into shared memory) into the
-// Kop / V' tiles. Warp 12: allocates tensor memory; its lane 0 issues the bulk copies and the products, which complete
-// on mbarriers. The two tiles run the same passes half a pass apart, so one tile's products overlap the other's
-// arithmetic. P' is written over qhat (dead once S is complete). Operand tiles are K-major with the 128-byte swizzle
+// Warps 0-15: the rows. Softmax: two threads per row (warps w and w + 8 share a tensor-memory lane quadrant; warps 0-3,
+// 8-11: tile 0); qhat: lane-per-channel-chunk over the tile's rows. Warps 16-19: operands, shared by both tiles: unpack the
+// group's records (bulk-copied raw into shared memory) into the Kop / V' tiles. Warp 20: allocates tensor memory; its
+// lane 0 issues the bulk copies and the products, which complete on mbarriers. P' is written over qhat (dead once S is complete). Operand tiles are K-major with the 128-byte swizzle
 // (8-row x 128-byte atoms, 16-byte chunk c of row r at c ^ (r % 8)).
 // What bounds it: per (row, group) the reference's semantics need ~130 exp2 and the requantisation of the row's 128
 // query channels on the CUDA cores; the tensor-core share of a pass is about as long as its exp2 share alone.
@@ -36,8 +35,12 @@ namespace tc {
 
 constexpr int ROWS = 128;                 // rows of a tile
 constexpr int CTA_ROWS = 2 * ROWS;
-constexpr int PRODUCER_WARP0 = 16, ISSUER_WARP = 20;  // warps 0-15: rows
-constexpr int THREADS = 21 * 32;
+#ifndef FBLA_PF_PRODUCERS
+#define FBLA_PF_PRODUCERS 4  /* operand warps. Measured: 4 (21 warps, 80 registers, 28 bytes of spills) 336.5 TFLOP/s; 3 (96 registers, none) 324.8 */
+#endif
+constexpr int PRODUCERS = FBLA_PF_PRODUCERS, PT = 32 * PRODUCERS;  // operand warps and threads
+constexpr int PRODUCER_WARP0 = 16, ISSUER_WARP = 16 + PRODUCERS;  // warps 0-15: rows
+constexpr int THREADS = (17 + PRODUCERS) * 32;
 constexpr int SLAB = ROWS * 128;          // bytes of one K slab (128 rows x 128 bytes): 64 FP16 / BF16 of the K extent
 constexpr int TILE = 2 * SLAB;            // a [128 x 128] 16-bit operand tile: 32 KiB
 constexpr int RAW = 8 * 3072;              // a raw group: 8 coarse + 8 fine records, 3072 bytes per pair in both formats
@@ -202,7 +205,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   };
 
   if (tid == 0) {
-    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_meta[0], 1); mbar_init(&sm.bar_meta[1], 1); mbar_init(&sm.bar_mf, 128); mbar_init(&sm.bar_k, 128); mbar_init(&sm.bar_v, 128);
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_meta[0], 1); mbar_init(&sm.bar_meta[1], 1); mbar_init(&sm.bar_mf, PT); mbar_init(&sm.bar_k, PT); mbar_init(&sm.bar_v, PT);
     for (int x = 0; x < 2; ++x) { mbar_init(&sm.bar_q[x], 256); mbar_init(&sm.bar_s[x], 1); mbar_init(&sm.bar_p[x], 256); mbar_init(&sm.bar_o[x], 1); }
     sm.abort = 0;
     mbar_init_fence();
@@ -275,7 +278,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     }
   } else if (warp >= PRODUCER_WARP0) {
     // ================= operand producers =================
-    const int pt = tid - 32 * PRODUCER_WARP0;  // 0 .. 127
+    const int pt = tid - 32 * PRODUCER_WARP0;  // 0 .. PT - 1
     const int l = pt & 31;
     int raw_uses = 0;
     PF_DECL
@@ -290,10 +293,12 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       PF_MARK(2)
       if (closed) {
         if (!wait(sm, &sm.bar_meta[n & 1], (uint32_t)(n >> 1) & 1u)) break;
-        {  // K bases and steps of channel pt as FP32 for the row threads: long before they ask for them
-          const uint8_t *m = sm.meta[n & 1] + 16 * (pt >> 2) + 2 * (pt & 3);
-          sm.kb[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
-          sm.ks[pt] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
+        {  // K bases and steps as FP32 for the row threads: long before they ask for them
+          for (int ch = pt; ch < D; ch += PT) {
+            const uint8_t *m = sm.meta[n & 1] + 16 * (ch >> 2) + 2 * (ch & 3);
+            sm.kb[ch] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
+            sm.ks[ch] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
+          }
         }
         mbar_arrive(&sm.bar_mf);
         if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
@@ -302,8 +307,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       if (closed) {
         // (record j, lane l): token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
 #pragma unroll 1
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = (pt >> 5) + 4 * jj;
+        for (int j = pt >> 5; j < SBG; j += PRODUCERS) {
           uint32_t Wc[2 * CB], Wf[2 * FB];
           lane_words<CB>(sm.raw + j * RC, 0, l, Wc);
           lane_words<FB>(sm.raw + SBG * RC + j * RF, 0, l, Wf);
@@ -316,7 +320,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           }
         }
       } else {
-        for (int e = pt; e < G * 16; e += 128) {  // BF16 group g: K rows as they are
+        for (int e = pt; e < G * 16; e += PT) {  // BF16 group g: K rows as they are
           const int tk = e >> 4, c = e & 15, tp = g * G + tk;
           const uint4 kw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.k, a.c.sink_k, a.c.open_k)) + c) : make_uint4(0u, 0u, 0u, 0u);
           *reinterpret_cast<uint4 *>(chunk_at(sm.k, tk, 8 * c)) = kw;
@@ -334,8 +338,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
         const __half2 vb[4] = {__float2half2_rn(bf_lo(vm.x)), __float2half2_rn(bf_hi(vm.x)), __float2half2_rn(bf_lo(vm.y)), __float2half2_rn(bf_hi(vm.y))};
         const __half2 vs[4] = {__float2half2_rn(bf_lo(vm.z)), __float2half2_rn(bf_hi(vm.z)), __float2half2_rn(bf_lo(vm.w)), __float2half2_rn(bf_hi(vm.w))};
 #pragma unroll 1
-        for (int jj = 0; jj < 2; ++jj) {
-          const int j = (pt >> 5) + 4 * jj;
+        for (int j = pt >> 5; j < SBG; j += PRODUCERS) {
           uint32_t Wc[2 * CB], Wf[2 * FB];
           lane_words<CB>(sm.raw + j * RC, 1, l, Wc);
           lane_words<FB>(sm.raw + SBG * RC + j * RF, 1, l, Wf);
@@ -353,7 +356,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           }
         }
       } else {
-        for (int e = pt; e < G * 16; e += 128) {  // V rows converted to FP16 and transposed (tokens along the K extent)
+        for (int e = pt; e < G * 16; e += PT) {  // V rows converted to FP16 and transposed (tokens along the K extent)
           const int tk = e >> 4, c = e & 15, tp = g * G + tk;
           const uint4 vw = tp < n1 ? __ldcg(reinterpret_cast<const uint4 *>(token_row(tp, a.v, a.c.sink_v, a.c.open_v)) + c) : make_uint4(0u, 0u, 0u, 0u);
           const uint32_t w4[4] = {vw.x, vw.y, vw.z, vw.w};
