@@ -289,23 +289,16 @@ def run_seqsplit(args):
     for _ in range(max(args.warmup, 3)):
         out = sharded.decode(qd, shard, group)
     torch.cuda.synchronize()
-    # one decode step (both passes and both exchanges) as a CUDA graph: the step is a handful of ~30 us kernels, so
-    # host launch overhead would otherwise be what is measured
+    # the step's local segments as CUDA graphs, the two exchanges as ordinary NCCL calls between them: the step is a
+    # handful of ~30 us kernels, so host launch overhead would otherwise be what is measured
     graph, mode_ = None, "eager"
     try:
-        if world > 1:  # the exchanges are NCCL calls: left out of graphs here (a rank that failed to capture would desynchronise the others)
-            raise RuntimeError("multi-rank steps are launched eagerly")
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                out = sharded.decode(qd, shard, group)
-        torch.cuda.current_stream().wait_stream(side)
-        g.replay()
+        graph = sharded.GraphedDecode(qd, shard, group)
+        out = graph()
         torch.cuda.synchronize()
-        graph, mode_ = g, "cuda graph"
+        mode_ = "cuda graphs around eager exchanges" if world > 1 else "cuda graphs"
     except Exception as exc:  # noqa: BLE001
+        graph = None
         print(f"graph capture unavailable ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
     if world > 1:
         dist.barrier()
@@ -316,7 +309,7 @@ def run_seqsplit(args):
     ev0.record(stream)
     for _ in range(args.steps):
         if graph is not None:
-            graph.replay()
+            out = graph()
         else:
             out = sharded.decode(qd, shard, group)
     ev1.record(stream)

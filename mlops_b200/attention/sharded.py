@@ -175,3 +175,43 @@ def decode(q: torch.Tensor, s: SequenceShard, group=None, *, scale: float = 0.0,
     if s.plan.world > 1:
         exchange_partial(s.partial, group)                                  # exchange B: 528 B per row
     return combine(s.partial, q)
+
+
+class GraphedDecode:
+    """The same decode step with its three local segments (mass pass; total mass + partial pass; combine) replayed from
+    CUDA graphs and the two exchanges launched between them as ordinary NCCL calls (collectives are never captured): at
+    a few KB per exchange the step is bound by launches, and the graphs remove most of the host's share. q and the
+    shard's buffers must stay where they are; the output tensor is reused by every call."""
+
+    def __init__(self, q: torch.Tensor, s: SequenceShard, group=None, *, scale: float = 0.0, tau: float = 0.0):
+        self.q, self.s, self.group, self.world = q, s, group, s.plan.world
+        rows = q.shape[0] * q.shape[1]
+        decode(q, s, group, scale=scale, tau=tau)  # eagerly once: per-device kernel configuration happens here, not under capture
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.g_mass = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_mass, stream=side):
+                local_mass(q, s, scale, tau)
+                if self.world == 1:
+                    total_mass(s.mass, 1, rows, s.total)
+            self.g_partial = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_partial, stream=side):
+                if self.world > 1:
+                    total_mass(s.gathered, self.world, rows, s.total)
+                local_partial(q, s, s.total, scale, tau)
+            self.g_combine = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.g_combine, stream=side):
+                self.out = combine(s.partial, q)
+        torch.cuda.current_stream().wait_stream(side)
+
+    def __call__(self) -> torch.Tensor:
+        self.g_mass.replay()
+        if self.world > 1:
+            exchange_mass(self.s.mass, self.s.gathered, self.group)
+        self.g_partial.replay()
+        if self.world > 1:
+            exchange_partial(self.s.partial, self.group)
+        self.g_combine.replay()
+        return self.out

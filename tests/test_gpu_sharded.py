@@ -38,3 +38,15 @@ def test_sharded_decode_matches_oracle(oracle, mode, QH, KH, N, world, seed, gen
     single = datagen.bf16_to_f32(gu.bits_of(lib.decode(lib.encode(kd, vd, mode), qd, tau=1e-3))).astype(np.float64)
     got = datagen.bf16_to_f32(gu.bits_of(out)).astype(np.float64)
     assert (np.abs(got - single) <= 2e-3 * np.abs(single).max() + gu.bf16_ulp(single)).all()
+
+
+def test_graphed_decode_equals_eager_decode():
+    """The step replayed from CUDA graphs (one rank: no exchange) gives the eager step's bits, call after call."""
+    from mlops_b200.attention import sharded
+    q, k, v = datagen.baseline_case(77, 1, 8, 2, 5000)
+    qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
+    shard = sharded.encode_shard(kd, vd, "4+2", sharded.plan_shards(5000, 1)[0])
+    want = sharded.decode(qd, shard).clone()
+    step = sharded.GraphedDecode(qd, shard)
+    for _ in range(3):
+        assert torch.equal(step(), want)
