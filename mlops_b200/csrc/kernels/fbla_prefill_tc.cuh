@@ -192,7 +192,8 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   const int bh = FBLA_POS::y(), b = bh / a.kv_heads, kh = bh - b * a.kv_heads, qg = a.q_heads / a.kv_heads;
   const int n0 = (a.length ? FBLA_POS::ro(a.length + (a.lstride ? b : 0)) : 0) + a.n0;
   const int count = a.dcount ? FBLA_POS::ro(a.dcount) : a.count, n1 = n0 + count;
-  const int rows = count * qg, r0 = FBLA_POS::x() * CTA_ROWS;
+  // the last tiles attend to the most groups: they are taken first, so that the grid's tail is made of short CTAs
+  const int rows = count * qg, r0 = (FBLA_POS::nx() - 1 - FBLA_POS::x()) * CTA_ROWS;
   if (r0 >= rows) return;  // (CTA-uniform)
   const int last_row = min(r0 + CTA_ROWS, rows) - 1;
   const int own_min = (n0 + r0 / qg) / G, own_max = (n0 + last_row / qg) / G;
