@@ -65,7 +65,9 @@ bool decode_layout(const mlops_fbla_config *c, long long tokens, const fbla_k_de
   L.nblocks = (int)(groups * SBG);
   L.nslices = (int)((L.nblocks + FBLA_K_SLICE - 1) / FBLA_K_SLICE);
   if (L.nslices < 1) L.nslices = 1;
-  const size_t tw = (size_t)shape.coarse_ctas * shape.coarse_warps, xw = (size_t)shape.coarse_ctas * FBLA_K_WINDOW_WARPS;
+  // (shape.coarse_warps: the streaming warps of the fixed 7 + 1 split; a CTA has one warp more, and the split by the
+  // lengths can put all but one of them on either kind of work)
+  const size_t tw = (size_t)shape.coarse_ctas * (shape.coarse_warps + 1), xw = tw;
   const size_t rw = (size_t)shape.refine_ctas * shape.refine_warps;
   const size_t row = (size_t)qg * FBLA_K_PSTRIDE * sizeof(float);
   L.lse = 0;
@@ -146,6 +148,7 @@ mlops_fbla_status prepare_decode(const char *fn, const mlops_fbla_config *c, con
   a.hs = c->head_stride ? c->head_stride : (int)((cap + G - 1) / G);
   a.gs = c->group_stride ? c->group_stride : 1;
   a.sl = scale_log2(c);
+  fbla_k_decode_split(&a, lc.tokens);
   const float tau = c->tau != 0.f ? c->tau : c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f;
   a.log2_tau = log2f(tau);
   return MLOPS_FBLA_OK;

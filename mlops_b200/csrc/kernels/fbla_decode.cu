@@ -3,10 +3,10 @@
 #include <stdio.h>
 
 namespace fbla {
-template <int CB, int FB, int QG>
-__global__ void __launch_bounds__(32 * (CoarseShape<CB>::WARPS + XWARPS), 1) coarse_kernel(const fbla_k_decode a) {
+template <int CB, int FB, int QG, bool DYN>
+__global__ void __launch_bounds__(32 * CoarseShape<CB>::TOTAL, 1) coarse_kernel(const fbla_k_decode a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  coarse_item<CB, FB, QG>(a, smem_raw);
+  coarse_item<CB, FB, QG, DYN>(a, smem_raw);
 }
 
 template <int QG>
@@ -57,7 +57,8 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(refine_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, REFINE_SMEM_MAX);
     if (e != cudaSuccess) return e;
@@ -66,7 +67,8 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
   if (a.phase != 2) {
-    coarse_kernel<CB, FB, QG><<<a.coarse_ctas, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, stream>>>(a);
+    if (a.coarse_warps == CoarseShape<CB>::TOTAL) coarse_kernel<CB, FB, QG, true><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+    else coarse_kernel<CB, FB, QG, false><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
     e = cudaGetLastError();
     if (e == cudaSuccess) e = launch_dependent(select_kernel<QG>, dim3(a.phase == 1 ? 1 : a.nslices, vheads), dim3(256), 0, stream, a);
     if (a.phase == 1) return e;
@@ -85,8 +87,10 @@ template <int CB, int FB, int QG> cudaError_t passes_of(const fbla_k_decode &a, 
   const size_t rsm = sizeof(RefineWarp<CB, FB>) * RefineShape<CB, FB>::WARPS + sizeof(int) * ((size_t)vheads * a.nslices + 1) + 128;
   if (rsm - 128 > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   char e[96];
-  snprintf(e, sizeof e, "fbla::coarse_item<%d, %d, %d>", CB, FB, QG);
-  cudaError_t st = pass_of(coarse_kernel<CB, FB, QG>, a.coarse_ctas, 1, 32 * (CoarseShape<CB>::WARPS + XWARPS), csm, e, p + 0);
+  const bool dyn = a.coarse_warps == CoarseShape<CB>::TOTAL;
+  snprintf(e, sizeof e, "fbla::coarse_item<%d, %d, %d, %s>", CB, FB, QG, dyn ? "true" : "false");
+  cudaError_t st = dyn ? pass_of(coarse_kernel<CB, FB, QG, true>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0)
+                       : pass_of(coarse_kernel<CB, FB, QG, false>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0);
   snprintf(e, sizeof e, "fbla::select_item<%d>", QG);
   if (st == cudaSuccess) st = pass_of(select_kernel<QG>, a.nslices, vheads, 256, 0, e, p + 1);
   snprintf(e, sizeof e, "fbla::refine_item<%d, %d, %d>", CB, FB, QG);
@@ -136,6 +140,16 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   a->refine_ctas = sms;
   a->refine_warps = fbla::RefineShape<4, 2>::WARPS;
   return cudaSuccess;
+}
+
+// The split of the coarse CTAs' warps (coarse_warps, see split_of): by the lengths when, at `tokens` per row, the BF16
+// windows would get three or more of a CTA's warps -- contexts up to about 4 600 tokens; else the fixed one.
+extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
+  const int total = (a->cb == 4 ? fbla::CoarseShape<4>::TOTAL : fbla::CoarseShape<3>::TOTAL);
+  const long long groups = (tokens + fbla::G - 1) / fbla::G, S = groups > 2 ? groups - 2 : 0;
+  const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : fbla::SBG + (tokens - fbla::G * (groups - 1) + fbla::S - 1) / fbla::S;
+  const bool dyn = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
+  a->coarse_warps = dyn ? total : total - 1;
 }
 
 extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream) {

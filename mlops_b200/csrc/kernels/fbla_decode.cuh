@@ -29,9 +29,10 @@ constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 #ifndef FBLA_RNST
 #define FBLA_RNST 2  /* refine ring stages per warp */
 #endif
-// Seven streaming warps and one window warp per CTA: eight warps leave a thread 255 registers, which the coarse loop
-// needs to run without spills. Measured on B200 (decode batch 8 x 16K 4+2 / batch 1 x 128K 3+3 / 4+2, us per step):
+// Eight warps per CTA leave a thread 255 registers, which the coarse loop needs to run without spills. Measured on B200
+// with streaming + window warps (decode batch 8 x 16K 4+2 / batch 1 x 128K 3+3 / 4+2, us per step):
 // 10 + 2 warps (168 registers) 135.5 / 80.3 / 78.1; 8 + 2: 121.3 / 81.0 / 65.2; 7 + 1: 121.7 / 76.3 / 63.5; 6 + 2: 131.6 / 84.3 / 68.6.
+// FBLA_CW*: the streaming warps of that fixed split; a CTA has one warp more (CoarseShape::TOTAL).
 #ifndef FBLA_CW4
 #define FBLA_CW4 7
 #endif
@@ -45,7 +46,7 @@ constexpr int SLICE = FBLA_K_SLICE;      // sub-blocks per select slice
 #define FBLA_PPC 2  // record pairs per chunk (one bulk copy, one barrier wait)
 #endif
 template <int CB> struct CoarseShape {
-  static constexpr int WARPS = CB == 4 ? FBLA_CW4 : FBLA_CW3;
+  static constexpr int WARPS = CB == 4 ? FBLA_CW4 : FBLA_CW3, TOTAL = WARPS + 1;
   static constexpr int NP = FBLA_NP;
   static constexpr int PPC = FBLA_PPC, CPG = 4 / FBLA_PPC;  // pairs per chunk, chunks per group
   static constexpr int PAIR_BYTES = 2 * record_bytes(CB), CHUNK_BYTES = FBLA_PPC * PAIR_BYTES;
@@ -174,11 +175,35 @@ struct __align__(16) ExactWarp {
   float q[4][D];
   uint8_t pst[4][16];
 };
-constexpr int XWARPS = FBLA_K_WINDOW_WARPS;
-template <int CB> struct CoarseSmem {
-  StreamWarp<CB> w[CoarseShape<CB>::WARPS];
-  ExactWarp x[XWARPS];
+// (a warp streams or serves windows, never both, and the last warp never streams)
+template <int CB> union CoarseWarp {
+  StreamWarp<CB> w;
+  ExactWarp x;
 };
+template <int CB> struct CoarseSmem {
+  CoarseWarp<CB> warp[CoarseShape<CB>::WARPS];
+  ExactWarp last;
+};
+
+// ---- the coarse pass's work, split over its warps --------------------------------------------------------------------------
+// Streaming units are the closed groups of all virtual heads, flattened; window units the 16-token sub-blocks of the
+// BF16 sink / open windows, flattened. Of a CTA's warps the last xw serve windows and the others stream. Each kind's
+// units are dealt in equal contiguous runs over its warps of all CTAs, so the split depends on the lengths alone and no
+// warp between two that serve a head is empty: the readers (slots_of) take every slot from the first to the last warp
+// of a head as written.
+// a.coarse_warps names the split. WARPS (the default): the fixed WARPS + 1, the measured optimum of long contexts.
+// TOTAL: xw follows the lengths -- the windows' share of all units (one unit of either kind costs a warp about the same
+// time), at least one warp for the windows (the last warp has no streaming buffers) and one for the groups if there are
+// any. The host asks for it when the windows are a large part of the work: short contexts at large batch
+// (batch 256 x 512 tokens: 638 -> 352 us per step, batch 32 x 4096: 182 -> 166).
+struct Split { int sw, xw; };  // streaming / window warps per CTA
+__device__ __forceinline__ Split split_of(const fbla_k_decode &a, int hpr) {
+  const int total = (a.cb == 4 ? FBLA_CW4 : FBLA_CW3) + 1;
+  if (a.coarse_warps < total) return Split{a.coarse_warps, 1};
+  const long long S = total_units<false>(a, hpr), W = total_units<true>(a, hpr);
+  const int xw = S == 0 ? total : max(1, min(total - 1, (int)((2 * total * W + S + W) / (2 * (S + W)))));
+  return Split{total - xw, xw};
+}
 
 // Programmatic dependent launch: the next pass of a decode is launched while this one still runs (hiding its launch
 // latency) and waits here until the previous pass has completed and its writes are visible.
@@ -189,7 +214,7 @@ __device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
   if (a.status) { atomicCAS(a.status, 0, pass); a.status[1] = FBLA_POS::x(); }
 }
 
-// ---- the BF16 windows: one warp per CTA ----------------------------------------------------------------------------------
+// ---- the BF16 windows ---------------------------------------------------------------------------------------------------
 // Unit = one 16-token sub-block of the sink (first) or the open window. Scores s = sl * (q . k) in FP32, the same
 // integer P block, values in FP32. Lane (t = lane % 16, h = lane / 16) scores token t over channels 64 h .. 64 h + 63;
 // for the values lane l owns channels 4 l .. 4 l + 3.
@@ -566,7 +591,7 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
 }
 
 
-template <int CB, int FB, int QG>
+template <int CB, int FB, int QG, bool DYN>
 __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *smem_raw) {
   using Sh = CoarseShape<CB>;
   allow_next_pass();
@@ -574,17 +599,19 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = FBLA_POS::tid() & 31, warp = FBLA_POS::tid() >> 5;
   if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
-  if (warp >= Sh::WARPS) {
-#ifdef FBLA_NOWINDOW  // tuning builds only
-    return;
+  const int hpr = a.kv_heads * a.vg;
+  int sw = Sh::WARPS, xw = 1;  // streaming / window warps of this CTA
+  if (DYN) { const Split sp = split_of(a, hpr); sw = sp.sw; xw = sp.xw; }
+  if (warp >= sw) {
+#ifndef FBLA_NOWINDOW  // tuning builds only
+    exact_warp<QG>(a, !DYN || warp == Sh::WARPS ? sm.last : sm.warp[warp].x, lane, FBLA_POS::x() * xw + (warp - sw), FBLA_POS::nx() * xw);
 #endif
-    exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, FBLA_POS::x() * XWARPS + (warp - Sh::WARPS), FBLA_POS::nx() * XWARPS);
     return;
   }
 #ifdef FBLA_NOSTREAM  // tuning builds only
   return;
 #endif
-  StreamWarp<CB> &w = sm.w[warp];
+  StreamWarp<CB> &w = sm.warp[warp].w;
   for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
   reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
   if (lane == 0) {
@@ -596,9 +623,8 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   }
   __syncwarp();
 
-  const int hpr = a.kv_heads * a.vg;
-  const long long total = total_units<false>(a, hpr), tw = (long long)FBLA_POS::nx() * Sh::WARPS, per = ceil_div(total, tw);
-  const long long gw = (long long)FBLA_POS::x() * Sh::WARPS + warp, lo = gw * per, hi = min(total, lo + per);
+  const long long total = total_units<false>(a, hpr), tw = (long long)FBLA_POS::nx() * sw, per = ceil_div(total, tw);
+  const long long gw = (long long)FBLA_POS::x() * sw + warp, lo = gw * per, hi = min(total, lo + per);
   if (lo >= hi) return;
   Cursor cc = locate<false>(a, hpr, lo);
   Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(Sh::CPG * (hi - lo)), nullptr, nullptr};
@@ -634,11 +660,11 @@ __device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
   const int hpr = a.kv_heads * a.vg;
   Slots s{0, -1, 0, -1};
   int n;
-  const long long tw = (long long)a.coarse_ctas * a.coarse_warps;
+  const Split sp = split_of(a, hpr);
   long long off = head_offset<false>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), tw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
+  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
   off = head_offset<true>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * XWARPS); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
+  if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * sp.xw); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
   return s;
 }
 __device__ __forceinline__ const float *coarse_slot(const fbla_k_decode &a, int w, int vh, int qi) {

@@ -23,8 +23,8 @@ typedef struct {
 // queries each (virtual head vh = kv_head_linear * vg + j owns queries j * qg .. j * qg + qg - 1 of its KV head).
 // Scratch arrays (all written before they are read; no initial contents needed):
 //   lse    [VH][nblocks][qg]  float  log2 mass of every closed sub-block under the coarse scores
-//   part   [TW + XW + 2 VH][qg][132] float  (o[128], m, l) partials: slot w + vh for coarse warp w, TW + VH + x + vh for window warp x
-//          (XW = coarse_ctas * FBLA_K_WINDOW_WARPS)
+//   part   [2 TW + 2 VH][qg][132] float  (o[128], m, l) partials: slot w + vh for streaming warp w, coarse_ctas * coarse_warps + VH + x + vh
+//          for window warp x
 //   dpart  [RW + VH][qg][129] float  (dl, do[128]) corrections of refine warp w at slot w + vh
 //   row_r  [VH][qg]           float  log2 of the row's total coarse mass
 //   counts [VH][nslices]      int    selected sub-blocks per slice of 1024 sub-blocks
@@ -44,7 +44,8 @@ typedef struct {
   int hs, gs;            // units between KV heads and between groups
   int qg, vg;            // queries per virtual head, virtual heads per KV head
   int cb, fb;            // plane bits
-  int coarse_ctas, coarse_warps;  // persistent coarse CTAs and warps per CTA (TW = coarse_ctas * coarse_warps)
+  int coarse_ctas, coarse_warps;  // persistent coarse CTAs; coarse_warps: 7 = seven streaming warps + one window warp per CTA,
+                                  // 8 = the CTA's eight warps split by the lengths (TW = 8 coarse_ctas bounds both kinds)
   int refine_ctas, refine_warps;  // RW = refine_ctas * refine_warps
   float sl, log2_tau;
   // Sequence shards (one GPU's part of a long context); shard_on 0: the whole cache. A shard processes the closed groups
@@ -57,11 +58,10 @@ typedef struct {
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
-#ifndef FBLA_K_WINDOW_WARPS
-#define FBLA_K_WINDOW_WARPS 1 /* warps per coarse CTA that serve the BF16 sink / open windows */
-#endif
 
 FBLA_HOST_API(cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);)
+// chooses the split of the coarse CTAs' warps for rows of about `tokens` tokens (after fbla_k_decode_shape; the scratch layout holds either)
+FBLA_HOST_API(void fbla_k_decode_split(fbla_k_decode *a, long long tokens);)
 // out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
 // total[i] = log2 sum over shards of 2^mass[s][i]
 FBLA_HOST_API(cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);)
