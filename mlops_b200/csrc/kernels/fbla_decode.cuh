@@ -175,15 +175,13 @@ struct __align__(16) ExactWarp {
   float q[4][D];
   uint8_t pst[4][16];
 };
-// (a warp streams or serves windows, never both, and the last warp never streams)
-template <int CB> union CoarseWarp {
-  StreamWarp<CB> w;
-  ExactWarp x;
-};
+// (a warp streams or serves windows, never both, and the last warp never streams: when the split follows the lengths, a
+// window warp other than the last keeps its ExactWarp in the streaming buffers it does not use)
 template <int CB> struct CoarseSmem {
-  CoarseWarp<CB> warp[CoarseShape<CB>::WARPS];
-  ExactWarp last;
+  StreamWarp<CB> w[CoarseShape<CB>::WARPS];
+  ExactWarp x[1];
 };
+static_assert(sizeof(ExactWarp) <= sizeof(StreamWarp<3>) && sizeof(ExactWarp) <= sizeof(StreamWarp<4>), "a window warp's state fits a streaming warp's");
 
 // ---- the coarse pass's work, split over its warps --------------------------------------------------------------------------
 // Streaming units are the closed groups of all virtual heads, flattened; window units the 16-token sub-blocks of the
@@ -599,19 +597,29 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = FBLA_POS::tid() & 31, warp = FBLA_POS::tid() >> 5;
   if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
-  const int hpr = a.kv_heads * a.vg;
-  int sw = Sh::WARPS, xw = 1;  // streaming / window warps of this CTA
-  if (DYN) { const Split sp = split_of(a, hpr); sw = sp.sw; xw = sp.xw; }
-  if (warp >= sw) {
-#ifndef FBLA_NOWINDOW  // tuning builds only
-    exact_warp<QG>(a, !DYN || warp == Sh::WARPS ? sm.last : sm.warp[warp].x, lane, FBLA_POS::x() * xw + (warp - sw), FBLA_POS::nx() * xw);
+  if (!DYN) {
+    if (warp >= Sh::WARPS) {
+#ifdef FBLA_NOWINDOW  // tuning builds only
+      return;
 #endif
-    return;
+      exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, FBLA_POS::x() + (warp - Sh::WARPS), FBLA_POS::nx());
+      return;
+    }
+  }
+  const int hpr = a.kv_heads * a.vg;
+  int sw = Sh::WARPS;  // streaming warps of this CTA
+  if (DYN) {
+    const Split sp = split_of(a, hpr);
+    sw = sp.sw;
+    if (warp >= sw) {
+      exact_warp<QG>(a, warp == Sh::WARPS ? sm.x[0] : *reinterpret_cast<ExactWarp *>(&sm.w[warp]), lane, FBLA_POS::x() * sp.xw + (warp - sw), FBLA_POS::nx() * sp.xw);
+      return;
+    }
   }
 #ifdef FBLA_NOSTREAM  // tuning builds only
   return;
 #endif
-  StreamWarp<CB> &w = sm.warp[warp].w;
+  StreamWarp<CB> &w = sm.w[warp];
   for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
   reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
   if (lane == 0) {
