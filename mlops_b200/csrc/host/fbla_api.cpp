@@ -148,7 +148,9 @@ mlops_fbla_status prepare_decode(const char *fn, const mlops_fbla_config *c, con
   a.hs = c->head_stride ? c->head_stride : (int)((cap + G - 1) / G);
   a.gs = c->group_stride ? c->group_stride : 1;
   a.sl = scale_log2(c);
-  fbla_k_decode_split(&a, lc.tokens);
+  // (by the cache's capacity where it has one, for host and device lengths alike: the two calls then run the same
+  // kernels on the same cache and give bit-identical outputs)
+  fbla_k_decode_split(&a, c->capacity ? c->capacity : c->tokens);
   const float tau = c->tau != 0.f ? c->tau : c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f;
   a.log2_tau = log2f(tau);
   return MLOPS_FBLA_OK;

@@ -38,6 +38,23 @@ def test_decode_at_equals_decode(ours, mode, B, QH, KH, N, tau, seed):
 
 
 @pytest.mark.parametrize("mode", MODES)
+def test_decode_at_equals_decode_under_a_large_capacity(ours, mode):
+    """Rows far shorter than the cache's capacity: the coarse pass picks how its warps are split from the capacity for
+    both calls, so host-length and device-length decodes still run the same kernels and agree bit for bit."""
+    B, QH, KH, N = 2, 8, 2, 700
+    q, k, v = datagen.uneven_case(47, B, QH, KH, N)
+    qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
+    c = ours.encode(kd, vd, mode, capacity=8192)
+    want = ours.decode(c, qd, tau=1e-3)
+    got = ours.decode_at(c, qd, _i32(N), tau=1e-3)
+    small = ours.decode(ours.encode(kd, vd, mode, capacity=1024), qd, tau=1e-3)  # (the split by the lengths)
+    torch.cuda.synchronize()
+    assert torch.equal(want, got)
+    scale = float(want.float().abs().max())
+    assert float((want.float() - small.float()).abs().max()) <= 2e-3 * scale
+
+
+@pytest.mark.parametrize("mode", MODES)
 def test_append_at_graph_replay(ours, oracle, mode):
     """One CUDA graph holding (append_at, decode_at), replayed per token while the device length advances; the cache
     ends bit-identical to a one-shot encode and every step's output equals the host-length decode of that prefix."""
