@@ -143,11 +143,11 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
 }
 
 // The split of the coarse CTAs' warps (coarse_warps, see split_of): by the lengths when, at `tokens` per row, the BF16
-// windows would get three or more of a CTA's warps -- contexts up to about 4 600 tokens; else the fixed one.
+// windows would get three or more of a CTA's warps -- contexts up to about 4 700 tokens; else the fixed one.
 extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
   const int total = (a->cb == 4 ? fbla::CoarseShape<4>::TOTAL : fbla::CoarseShape<3>::TOTAL);
   const long long groups = (tokens + fbla::G - 1) / fbla::G, S = groups > 2 ? groups - 2 : 0;
-  const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : fbla::SBG + (tokens - fbla::G * (groups - 1) + fbla::S - 1) / fbla::S;
+  const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : 2 * fbla::SBG;  // (a full open window: the choice is monotone in tokens)
   const bool dyn = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
   a->coarse_warps = dyn ? total : total - 1;
 }
