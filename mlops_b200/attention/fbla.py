@@ -1,7 +1,11 @@
-"""The `mlops.attention` Python interface (reference: attention/python/mlops/attention/fbla.py:43-150), same names,
-signatures and error behaviour: ``empty(batch, kv_heads, capacity, "4+2")`` or ``encode(k, v, "4+2", capacity)``,
-``prefill(q, k, v, cache)`` (a chunk: q [B, Hq, n, 128], k / v [B, Hkv, n, 128] BF16; appends), ``append(cache, k, v)``,
-``decode(q, cache)`` (one query per head). Every cache write and every attention runs in the CUDA library."""
+"""The `mlops.attention` Python interface over the CUDA library.
+
+The public surface is the reference's (attention/python/mlops/attention/fbla.py:43-150): the ``FBLACache`` record and
+``empty / encode / append / prefill / decode`` with the same argument names, defaults and exception types, so code
+written against `mlops.attention` runs unchanged. Shapes: K / V chunks ``[B, Hkv, n, 128]``, prefill queries
+``[B, Hq, n, 128]``, decode queries ``[B, Hq, 128]``, all BF16 on one CUDA device. Everything that touches cache bytes
+or computes attention happens inside libmlops_attention.so; this module only allocates tensors and forwards.
+"""
 from dataclasses import dataclass
 from typing import Optional
 
@@ -9,114 +13,136 @@ import torch
 
 from . import _C
 
-_MODES = {"3+3": (3, 3, 0), "4+2": (4, 2, 1)}
+GROUP = 128      # tokens per quantisation group
+HEAD_DIM = 128
+# mode string -> (coarse bits, fine bits, value of mlops_fbla_format)
+_PLANES = {"3+3": (3, 3, 0), "4+2": (4, 2, 1)}
 
 
 @dataclass
 class FBLACache:
-    coarse: torch.Tensor  # [B, H, capacity_groups * 8, 2 CB 256] uint8
-    fine: torch.Tensor    # [B, H, capacity_groups * 8, 2 FB 256] uint8
-    meta: torch.Tensor    # [B, H, capacity_groups, 512] bfloat16
-    sink_k: torch.Tensor
+    coarse: torch.Tensor  # uint8  [B, Hkv, 8 * groups, 512 * coarse bits]: the coarse plane's records
+    fine: torch.Tensor    # uint8  [B, Hkv, 8 * groups, 512 * fine bits]
+    meta: torch.Tensor    # bf16   [B, Hkv, groups, 512]: per-channel base / step of K and V
+    sink_k: torch.Tensor  # bf16   [B, Hkv, 128, 128]: the first group, kept exact
     sink_v: torch.Tensor
-    open_k: torch.Tensor
+    open_k: torch.Tensor  # bf16   [B, Hkv, 128, 128]: the group still being filled
     open_v: torch.Tensor
     tokens: int
     capacity: int
     format: int
-    images: Optional[torch.Tensor] = None  # always None here: this library keeps no prefill images
+    images: Optional[torch.Tensor] = None  # the reference's persistent prefill images; this library has none
 
 
-def _check_kv(k, v):
-    if k.shape != v.shape or k.ndim != 4 or k.shape[-1] != 128:
-        raise ValueError(f"k and v must have the same [B, H, N, 128] shape, got {tuple(k.shape)} and {tuple(v.shape)}")
-    if not k.is_cuda or k.device != v.device:
-        raise ValueError("k and v must be CUDA tensors on the same device")
+def _require_kv(k, v):
+    """K and V of one chunk: equal 4-D shapes with a head dimension of 128, on one CUDA device."""
+    same = k.ndim == 4 and tuple(k.shape) == tuple(v.shape) and k.shape[-1] == HEAD_DIM
+    if not same:
+        raise ValueError(f"expected k and v of one shape [B, Hkv, n, {HEAD_DIM}]; k is {tuple(k.shape)}, v is {tuple(v.shape)}")
+    if not (k.is_cuda and v.is_cuda and k.device == v.device):
+        raise ValueError(f"k and v have to live on the same CUDA device (k: {k.device}, v: {v.device})")
 
 
 def empty(batch: int, kv_heads: int, capacity: int, mode: str = "3+3", device="cuda") -> FBLACache:
-    """An empty cache laid out for ``capacity`` tokens (zero-filled: 0 tokens)."""
-    if mode not in _MODES:
-        raise ValueError(f"mode must be '3+3' or '4+2', got {mode!r}")
-    cb, fb, fmt = _MODES[mode]
-    cg = (capacity + 127) // 128
-    u8 = dict(device=device, dtype=torch.uint8)
-    bf = dict(device=device, dtype=torch.bfloat16)
-    ex = [torch.zeros((batch, kv_heads, 128, 128), **bf) for _ in range(4)]
+    """A cache with room for ``capacity`` tokens and none stored. All arrays start as zeros."""
+    planes = _PLANES.get(mode)
+    if planes is None:
+        raise ValueError(f"unknown mode {mode!r}: choose '3+3' or '4+2'")
+    coarse_bits, fine_bits, fmt = planes
+    groups = -(-capacity // GROUP)
+
+    def zeros(shape, dtype):
+        return torch.zeros(shape, dtype=dtype, device=device)
+
+    records = 8 * groups
+    windows = [zeros((batch, kv_heads, GROUP, HEAD_DIM), torch.bfloat16) for _ in ("sink_k", "sink_v", "open_k", "open_v")]
     with torch.cuda.device(torch.device(device)):
-        nimg = _C.images_bytes(batch, kv_heads, cg * 128)
-    images = torch.zeros(nimg, **u8) if nimg else None
-    return FBLACache(torch.zeros((batch, kv_heads, cg * 8, 2 * cb * 256), **u8),
-                     torch.zeros((batch, kv_heads, cg * 8, 2 * fb * 256), **u8),
-                     torch.zeros((batch, kv_heads, cg, 512), **bf), ex[0], ex[1], ex[2], ex[3], 0, capacity, fmt, images)
+        image_bytes = _C.images_bytes(batch, kv_heads, groups * GROUP)
+    return FBLACache(coarse=zeros((batch, kv_heads, records, 512 * coarse_bits), torch.uint8),
+                     fine=zeros((batch, kv_heads, records, 512 * fine_bits), torch.uint8),
+                     meta=zeros((batch, kv_heads, groups, 512), torch.bfloat16),
+                     sink_k=windows[0], sink_v=windows[1], open_k=windows[2], open_v=windows[3],
+                     tokens=0, capacity=capacity, format=fmt,
+                     images=zeros((image_bytes,), torch.uint8) if image_bytes > 0 else None)
 
 
-def _prefill(q, cache, k, v, scale):
-    _check_kv(k, v)
-    c = cache
-    if k.shape[:2] != c.meta.shape[:2]:
-        raise ValueError(f"k / v heads {tuple(k.shape[:2])} do not match the cache's {tuple(c.meta.shape[:2])}")
-    n = k.shape[2]
-    if c.tokens + n > c.capacity:
-        raise ValueError(f"cache full: {c.tokens} + {n} tokens > capacity {c.capacity}")
-    out = _C.prefill(q, k.to(torch.bfloat16).contiguous(), v.to(torch.bfloat16).contiguous(), c.coarse, c.fine,
-                     c.meta, c.sink_k, c.sink_v, c.open_k, c.open_v, c.tokens, c.capacity,
-                     q.shape[1] if q is not None else k.shape[1], c.format, scale, c.images)
-    c.tokens += n
-    return out
+def _extend(cache, k, v, q=None, scale=0.0):
+    """One library call: store the chunk (k, v) behind the cache's tokens and, given q, attend from its positions."""
+    _require_kv(k, v)
+    held = tuple(cache.meta.shape[:2])
+    if tuple(k.shape[:2]) != held:
+        raise ValueError(f"the chunk is [batch, kv_heads] = {tuple(k.shape[:2])} but the cache was built for {held}")
+    added = int(k.shape[2])
+    if cache.tokens + added > cache.capacity:
+        raise ValueError(f"{added} more tokens do not fit: the cache holds {cache.tokens} of {cache.capacity}")
+    q_heads = int(q.shape[1]) if q is not None else int(k.shape[1])
+    result = _C.prefill(q, k.to(torch.bfloat16).contiguous(), v.to(torch.bfloat16).contiguous(),
+                        cache.coarse, cache.fine, cache.meta, cache.sink_k, cache.sink_v, cache.open_k, cache.open_v,
+                        cache.tokens, cache.capacity, q_heads, cache.format, scale, cache.images)
+    cache.tokens += added
+    return result
 
 
 @torch.no_grad()
 def encode(k: torch.Tensor, v: torch.Tensor, mode: str = "3+3", capacity: Optional[int] = None) -> FBLACache:
-    """Encode dense ``[B, Hkv, N, 128]`` K / V into an :class:`FBLACache` laid out for ``capacity`` tokens."""
-    _check_kv(k, v)
-    B, H, N, _ = k.shape
-    capacity = N if capacity is None else capacity
-    if capacity < N:
-        raise ValueError(f"capacity {capacity} < tokens {N}")
-    cache = empty(B, H, capacity, mode, k.device)
-    _prefill(None, cache, k, v, 0.0)
+    """Quantise dense K / V ``[B, Hkv, N, 128]`` into a new cache (room for ``capacity`` tokens, default N)."""
+    _require_kv(k, v)
+    batch, kv_heads, n = (int(x) for x in k.shape[:3])
+    room = n if capacity is None else int(capacity)
+    if room < n:
+        raise ValueError(f"a capacity of {room} tokens cannot hold the {n} given")
+    cache = empty(batch, kv_heads, room, mode, k.device)
+    _extend(cache, k, v)
     return cache
 
 
 @torch.no_grad()
 def append(cache: FBLACache, k: torch.Tensor, v: torch.Tensor) -> FBLACache:
-    """Append ``[B, Hkv, n, 128]`` K / V to ``cache`` in place. New tokens go to the open group (BF16); a full open
-    group is quantized into its records and metadata when the next token arrives, exactly as :func:`encode` would."""
-    _prefill(None, cache, k, v, 0.0)
+    """Store ``[B, Hkv, n, 128]`` more K / V in ``cache`` (in place; also returned). Tokens land in the BF16 open
+    group; once a group is full it is quantised when the following token arrives, so growing a cache token by token
+    ends in the same bytes as :func:`encode` of the whole sequence."""
+    _extend(cache, k, v)
     return cache
 
 
 @torch.no_grad()
 def prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cache: FBLACache, *, scale: float = 0.0) -> torch.Tensor:
-    """Append a chunk ``k, v [B, Hkv, n, 128]`` to ``cache`` and return the attention of its queries
-    ``q [B, Hq, n, 128]`` (BF16): position ``cache.tokens + i`` attends to the tokens up to itself."""
-    if q.dtype != torch.bfloat16 or q.ndim != 4 or q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
-        raise ValueError(f"q must be BF16 [B, Hq, n, 128] matching k {tuple(k.shape)}, got {q.dtype} {tuple(q.shape)}")
-    return _prefill(q.contiguous(), cache, k, v, scale)
+    """Causal attention of a chunk. ``k, v [B, Hkv, n, 128]`` are stored in ``cache`` first; the query of chunk
+    position i (absolute position ``tokens + i``) sees every token up to its own. Returns ``[B, Hq, n, 128]`` BF16."""
+    fits = q.dtype == torch.bfloat16 and q.ndim == 4 and q.shape[0] == k.shape[0] and q.shape[2] == k.shape[2]
+    if not fits:
+        raise ValueError(f"q has to be a bfloat16 [B, Hq, n, {HEAD_DIM}] tensor with the batch and length of k {tuple(k.shape)}; "
+                         f"it is {q.dtype} {tuple(q.shape)}")
+    return _extend(cache, k, v, q.contiguous(), scale)
 
 
-_SCRATCH = {}  # (device, batch * kv_heads) -> allocated once, reused
+class _ScratchPool:
+    """Decode scratch, one buffer per (device, batch x KV heads), grown on demand and kept for later calls."""
+
+    def __init__(self):
+        self._buffers = {}
+
+    def get(self, device, heads, nbytes):
+        held = self._buffers.get((device, heads))
+        if held is not None and held.numel() >= nbytes:
+            return held
+        fresh = torch.empty((nbytes,), dtype=torch.uint8, device=device)  # the library needs no initial contents
+        self._buffers[(device, heads)] = fresh
+        return fresh
 
 
-def _scratch(device, heads, nbytes):
-    key = (device, heads)
-    s = _SCRATCH.get(key)
-    if s is None or s.numel() < nbytes:
-        s = torch.full((nbytes,), 0xFF, dtype=torch.uint8, device=device)
-        _SCRATCH[key] = s
-    return s
+_pool = _ScratchPool()
 
 
 def decode(q: torch.Tensor, cache: FBLACache, *, scale: float = 0.0, tau: float = 0.0) -> torch.Tensor:
-    """One decode query per q head ``[B, Hq, 128]`` BF16 against ``cache``; scale 0 = 1/sqrt(128), tau 0 = the
-    format's default."""
+    """Attention of one new query per head, ``q [B, Hq, 128]`` BF16, over everything in ``cache``.
+    ``scale`` 0 selects 1/sqrt(128); ``tau`` 0 selects the format's refinement threshold."""
     if q.dtype != torch.bfloat16:
-        raise TypeError(f"q must be bfloat16, got {q.dtype}")
-    c = cache
-    kv_heads = c.meta.shape[1]
+        raise TypeError(f"decode takes bfloat16 queries, not {q.dtype}")
+    batch, q_heads = int(q.shape[0]), int(q.shape[1])
+    kv_heads = int(cache.meta.shape[1])
     with torch.cuda.device(q.device):
-        nbytes = _C.scratch_bytes(q.shape[0], q.shape[1], kv_heads, c.tokens, c.format, c.capacity)
-    scratch = _scratch(q.device, q.shape[0] * kv_heads, nbytes)
-    return _C.decode(q.contiguous(), c.coarse, c.fine, c.meta, c.sink_k, c.sink_v, c.open_k, c.open_v, scratch,
-                     c.tokens, c.capacity, kv_heads, c.format, scale, tau)
+        need = _C.scratch_bytes(batch, q_heads, kv_heads, cache.tokens, cache.format, cache.capacity)
+    scratch = _pool.get(q.device, batch * kv_heads, need)
+    return _C.decode(q.contiguous(), cache.coarse, cache.fine, cache.meta, cache.sink_k, cache.sink_v, cache.open_k,
+                     cache.open_v, scratch, cache.tokens, cache.capacity, kv_heads, cache.format, scale, tau)

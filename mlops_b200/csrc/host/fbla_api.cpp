@@ -1,9 +1,10 @@
-// Host layer of the FBLA library: argument validation, cache / scratch geometry and dispatch to the CUDA passes.
-// It mirrors the accept / reject behaviour and the status codes of the reference's host code
-// (attention/fbla/src/fbla.cu:16-20 error text, :62-80 shape rules, :90-138 decode preparation, :193-268 prefill
-// rules, :408-430 size queries) behind the same C interface (include/mlops_fbla.h). It allocates nothing, never
-// synchronises, and keeps only per-thread state (last error, device attribute cache), so calls may come from many
-// host threads at once.
+// Host layer of the FBLA library: checks a call's arguments, lays out the decode scratch, fills the kernels' plain
+// argument structures and enqueues the passes on the caller's stream. It accepts and rejects what the reference's host
+// code accepts and rejects and returns the same status codes (attention/fbla/src/fbla.cu:62-80 shape rules, :90-138
+// decode, :193-268 prefill, :307-382 fused QKV step, :408-430 size queries) behind the same C interface
+// (include/mlops_fbla.h); the wording of the messages is this library's own. Nothing here allocates or synchronises;
+// the only state is per host thread (the last message, a per-device cache of launch attributes), so any number of
+// host threads may call in at once.
 #include "../../../include/mlops_fbla.h"
 #include "../../../include/mlops_fbla_shard.h"
 #include "../../../include/mlops_fbla_items.h"
@@ -16,219 +17,277 @@
 
 namespace {
 
-constexpr int G = MLOPS_FBLA_GROUP, SBG = MLOPS_FBLA_GROUP / MLOPS_FBLA_SUBBLOCK, D = MLOPS_FBLA_HEAD_DIM;
-constexpr long long MAX_TOKENS = 1ll << 26;
+constexpr int kGroup = MLOPS_FBLA_GROUP, kBlocksPerGroup = MLOPS_FBLA_GROUP / MLOPS_FBLA_SUBBLOCK, kHeadDim = MLOPS_FBLA_HEAD_DIM;
+constexpr long long kTokenLimit = 1ll << 26;
 
-thread_local char error_buf[256] = {0};
-mlops_fbla_status fail(mlops_fbla_status st, const char *fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(error_buf, sizeof(error_buf) - 1, fmt, ap);
-  va_end(ap);
-  return st;
+// ---- the calling thread's last message ------------------------------------------------------------------------------------
+thread_local char g_message[256] = "";
+
+// "<function>: <what is wrong>", status INVALID_VALUE
+mlops_fbla_status refuse(const char *function, const char *format, ...) {
+  const int used = snprintf(g_message, sizeof g_message, "%s: ", function);
+  va_list args;
+  va_start(args, format);
+  if (used >= 0 && (size_t)used < sizeof g_message) vsnprintf(g_message + used, sizeof g_message - (size_t)used, format, args);
+  va_end(args);
+  return MLOPS_FBLA_INVALID_VALUE;
 }
-mlops_fbla_status ok() { error_buf[0] = 0; return MLOPS_FBLA_OK; }
-bool aligned(const void *p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
-size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
-bool valid_format(const mlops_fbla_config *c) { return c->format == MLOPS_FBLA_3P3 || c->format == MLOPS_FBLA_4P2; }
-bool valid_strides(const mlops_fbla_config *c) {
-  return (c->head_stride == 0 && c->group_stride == 0) || (c->head_stride > 0 && c->group_stride > 0);
+mlops_fbla_status device_failure(const char *function, cudaError_t error) {
+  snprintf(g_message, sizeof g_message, "%s: CUDA reports \"%s\"", function, cudaGetErrorString(error));
+  return MLOPS_FBLA_CUDA_ERROR;
 }
-bool valid_out_layout(const mlops_fbla_config *c) {
-  if (c->out_head_stride == 0 && c->out_token_stride == 0) return true;
-  return c->out_head_stride > 0 && c->out_token_stride > 0 && c->out_token_stride < (1ll << 30) && c->out_head_stride % 8 == 0 &&
-         c->out_token_stride % 8 == 0 && c->batch == 1;
+mlops_fbla_status accepted() {
+  g_message[0] = '\0';
+  return MLOPS_FBLA_OK;
 }
-// queries served together per virtual KV head for r queries per KV head: r for 1, 2, 4, else the largest of 4, 2, 1 dividing r
-int decode_group(int r) { return r == 1 || r == 2 || r == 4 ? r : r % 4 == 0 ? 4 : r % 2 == 0 ? 2 : 1; }
-float scale_log2(const mlops_fbla_config *c) {
-  const float scale = c->scale == 0.f ? 1.f / sqrtf((float)D) : c->scale;
-  return scale * 1.4426950408889634f;
+
+// ---- small predicates ---------------------------------------------------------------------------------------------------------
+bool on_boundary(const void *pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; }
+template <size_t N> bool all_on_boundary(const void *const (&pointers)[N], uintptr_t bytes) {
+  for (const void *p : pointers)
+    if (!on_boundary(p, bytes)) return false;
+  return true;
 }
-bool cache_complete(const mlops_fbla_cache *k) {
-  return k->coarse && k->fine && k->meta && k->exact_sink_k && k->exact_sink_v && k->exact_open_k && k->exact_open_v;
+size_t padded(size_t bytes) { return (bytes + 255) / 256 * 256; }  // scratch arrays start on 256-byte boundaries
+bool known_format(const mlops_fbla_config *c) { return c->format == MLOPS_FBLA_3P3 || c->format == MLOPS_FBLA_4P2; }
+int coarse_bits(const mlops_fbla_config *c) { return c->format == MLOPS_FBLA_3P3 ? 3 : 4; }
+int fine_bits(const mlops_fbla_config *c) { return c->format == MLOPS_FBLA_3P3 ? 3 : 2; }
+// unit strides: give both or neither
+bool unit_strides_consistent(const mlops_fbla_config *c) {
+  const bool none = c->head_stride == 0 && c->group_stride == 0, both = c->head_stride > 0 && c->group_stride > 0;
+  return none || both;
 }
-fbla_k_cache kcache(const mlops_fbla_cache *k) {
+// output strides: neither, or both as positive multiples of 8 elements (16-byte rows) for a single batch row
+bool output_strides_usable(const mlops_fbla_config *c) {
+  const long long hs = c->out_head_stride, ts = c->out_token_stride;
+  if (hs == 0 && ts == 0) return true;
+  if (hs <= 0 || ts <= 0 || c->batch != 1) return false;
+  return hs % 8 == 0 && ts % 8 == 0 && ts < (1ll << 30);
+}
+bool heads_consistent(const mlops_fbla_config *c) {
+  return c->batch > 0 && c->q_heads > 0 && c->kv_heads > 0 && c->q_heads % c->kv_heads == 0;
+}
+// A KV head with `ratio` queries is served as virtual heads of 4, 2 or 1 queries: the ratio itself up to 4 (3 -> 1),
+// beyond that the largest of 4, 2, 1 that divides it.
+int queries_per_virtual_head(int ratio) {
+  if (ratio == 1 || ratio == 2 || ratio == 4) return ratio;
+  return ratio % 4 == 0 ? 4 : ratio % 2 == 0 ? 2 : 1;
+}
+// softmax scale times log2(e): scores live in the log2 domain
+float log2_scale(const mlops_fbla_config *c) {
+  const float natural = c->scale == 0.f ? 1.f / sqrtf((float)kHeadDim) : c->scale;
+  return natural * 1.4426950408889634f;
+}
+bool all_cache_arrays_given(const mlops_fbla_cache *k) {
+  const void *const arrays[] = {k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
+  for (const void *p : arrays)
+    if (!p) return false;
+  return true;
+}
+fbla_k_cache kernel_cache(const mlops_fbla_cache *k) {
   return fbla_k_cache{k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
 }
+long long groups_of(long long tokens) { return (tokens + kGroup - 1) / kGroup; }
 
-// ---- decode scratch ------------------------------------------------------------------------------------------------
-struct Layout {
+// ---- decode scratch ------------------------------------------------------------------------------------------------------------
+// Byte offsets of the arrays fbla_kernels.h describes, in this order, inside the caller's scratch.
+struct ScratchMap {
   size_t lse, part, dpart, row_r, counts, items, item_off, status, bytes;
   int nblocks, nslices;
 };
-// shape: the launch shape of the current device (fbla_k_decode_shape); tokens: the layout's token count
-bool decode_layout(const mlops_fbla_config *c, long long tokens, const fbla_k_decode &shape, Layout &L) {
-  const int r = c->q_heads / c->kv_heads, qg = decode_group(r), vg = r / qg;
-  const size_t vheads = (size_t)c->batch * c->kv_heads * vg;
-  const long long groups = (tokens + G - 1) / G;
-  L.nblocks = (int)(groups * SBG);
-  L.nslices = (int)((L.nblocks + FBLA_K_SLICE - 1) / FBLA_K_SLICE);
-  if (L.nslices < 1) L.nslices = 1;
-  // (shape.coarse_warps: the streaming warps of the fixed 7 + 1 split; a CTA has one warp more, and the split by the
-  // lengths can put all but one of them on either kind of work)
-  const size_t tw = (size_t)shape.coarse_ctas * (shape.coarse_warps + 1), xw = tw;
-  const size_t rw = (size_t)shape.refine_ctas * shape.refine_warps;
-  const size_t row = (size_t)qg * FBLA_K_PSTRIDE * sizeof(float);
-  L.lse = 0;
-  L.part = L.lse + up256(vheads * L.nblocks * qg * sizeof(float));
-  L.dpart = L.part + up256((tw + xw + 2 * vheads) * row);
-  L.row_r = L.dpart + up256((rw + vheads) * row);
-  L.counts = L.row_r + up256(vheads * qg * sizeof(float));
-  L.items = L.counts + up256(vheads * L.nslices * sizeof(int));
-  L.item_off = L.items + up256(vheads * L.nslices * FBLA_K_SLICE * sizeof(int));
-  L.status = L.item_off + up256((vheads + 1) * sizeof(int));
-  L.bytes = L.status + 256;
-  return true;
+// `shape`: the launch shape on the current device; `tokens`: what the layout has room for; extra_rows: partial rows per
+// virtual head beyond the shape's own (the per_head of the size query)
+ScratchMap map_scratch(const mlops_fbla_config *c, long long tokens, const fbla_k_decode &shape, int extra_rows) {
+  ScratchMap m{};
+  const int ratio = c->q_heads / c->kv_heads, qg = queries_per_virtual_head(ratio);
+  const size_t vheads = (size_t)c->batch * c->kv_heads * (ratio / qg);
+  m.nblocks = (int)(groups_of(tokens) * kBlocksPerGroup);
+  m.nslices = (m.nblocks + FBLA_K_SLICE - 1) / FBLA_K_SLICE;
+  if (m.nslices < 1) m.nslices = 1;
+  const size_t row_bytes = (size_t)qg * FBLA_K_PSTRIDE * sizeof(float);
+  // partial rows: coarse slot (writer + virtual head) for up to coarse_warps writers per CTA, the same again for the
+  // window warps; corrections: refine slot (warp + virtual head)
+  const size_t coarse_rows = 2 * ((size_t)shape.coarse_ctas * shape.coarse_warps + vheads) + (size_t)extra_rows * vheads;
+  const size_t refine_rows = (size_t)shape.refine_ctas * shape.refine_warps + vheads;
+  size_t at = 0;
+  auto take = [&at](size_t bytes) { const size_t here = at; at += padded(bytes); return here; };
+  m.lse = take(vheads * m.nblocks * qg * sizeof(float));
+  m.part = take(coarse_rows * row_bytes);
+  m.dpart = take(refine_rows * row_bytes);
+  m.row_r = take(vheads * qg * sizeof(float));
+  m.counts = take(vheads * m.nslices * sizeof(int));
+  m.items = take(vheads * m.nslices * FBLA_K_SLICE * sizeof(int));
+  m.item_off = take((vheads + 1) * sizeof(int));
+  m.status = take(16);
+  m.bytes = at;
+  return m;
 }
-bool valid_decode_shape(const mlops_fbla_config *c) {  // c->tokens: the layout's
-  if (!c || c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->tokens <= 0 || !valid_strides(c)) return false;
-  if (c->q_heads % c->kv_heads) return false;
-  if (c->capacity != 0 && c->capacity < c->tokens) return false;
-  return c->tokens <= MAX_TOKENS;
+// c->tokens here is the token count the LAYOUT is made for
+bool decode_shape_acceptable(const mlops_fbla_config *c) {
+  if (!c || !heads_consistent(c) || !unit_strides_consistent(c)) return false;
+  if (c->tokens <= 0 || c->tokens > kTokenLimit) return false;
+  return c->capacity == 0 || c->capacity >= c->tokens;
 }
-size_t scratch_bytes_of(const mlops_fbla_config *lc) {
+size_t scratch_size(const mlops_fbla_config *layout, int extra_rows) {
   fbla_k_decode shape{};
-  shape.cb = lc->format == MLOPS_FBLA_3P3 ? 3 : 4;
+  shape.cb = coarse_bits(layout);
   if (fbla_k_decode_shape(&shape) != cudaSuccess) return 0;
-  Layout L;
-  decode_layout(lc, lc->tokens, shape, L);
-  return L.bytes;
+  return map_scratch(layout, layout->tokens, shape, extra_rows).bytes;
 }
 
-// validates a decode and fills the kernels' arguments (out may be null when need_out is false: the shard passes)
-mlops_fbla_status prepare_decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
-                                 uint16_t *out, bool need_out, void *scratch, size_t scratch_bytes, fbla_k_decode &a) {
-  const bool by_capacity = length != nullptr;
-  if (!c || !k || !q || (need_out && !out) || !scratch) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
-  mlops_fbla_config lc = *c;
-  if (by_capacity) lc.tokens = c->capacity;
-  if (!valid_decode_shape(&lc) || (by_capacity && c->tokens < 0))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads and tokens must be positive (device length: capacity positive, tokens >= 0), "
-                "q_heads a multiple of kv_heads, tokens <= 2^26, capacity 0 or >= tokens, strides both 0 or both positive", fn);
-  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
-  if (!(c->scale >= 0.f) || !(c->tau >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scale and tau must be nonnegative", fn);
-  if (!cache_complete(k)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
-  const void *ptrs[] = {q, out, scratch, k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
-  for (const void *p : ptrs)
-    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: pointers must be 16-byte aligned", fn);
-  if (!aligned(length, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length must be 4-byte aligned", fn);
-  if ((c->length_stride != 0 && c->length_stride != 1) || (c->length_stride && !length))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0, or 1 with a device length", fn);
+// Checks a decode and fills the kernels' arguments. `length` non-null: a device-length call, laid out by cfg->capacity.
+// `out` may be null when the caller is one of the shard passes (wants_output false).
+mlops_fbla_status make_decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                              uint16_t *out, bool wants_output, void *scratch, size_t scratch_bytes, fbla_k_decode &a) {
+  if (!c || !q || !k || !scratch || (wants_output && !out)) return refuse(fn, "a required pointer is null");
+  const bool device_length = length != nullptr;
+  mlops_fbla_config layout = *c;
+  if (device_length) layout.tokens = c->capacity;
+  if (!decode_shape_acceptable(&layout) || (device_length && c->tokens < 0))
+    return refuse(fn, "needs batch, q_heads, kv_heads > 0 with kv_heads dividing q_heads; %s; at most 2^26 tokens; capacity 0 or no "
+                      "smaller than tokens; head_stride and group_stride given together or not at all",
+                  device_length ? "capacity > 0 and a token offset >= 0" : "tokens > 0");
+  if (!known_format(c)) return refuse(fn, "format %d is neither MLOPS_FBLA_3P3 nor MLOPS_FBLA_4P2", (int)c->format);
+  if (!(c->scale >= 0.f) || !(c->tau >= 0.f)) return refuse(fn, "scale and tau may not be negative or NaN");
+  if (!all_cache_arrays_given(k)) return refuse(fn, "the cache lacks one of its seven arrays");
+  const void *const wide[] = {q, out, scratch, k->coarse, k->fine, k->meta, k->exact_sink_k, k->exact_sink_v, k->exact_open_k, k->exact_open_v};
+  if (!all_on_boundary(wide, 16)) return refuse(fn, "q, output, scratch and the cache arrays have to start on 16-byte boundaries");
+  if (!on_boundary(length, 4)) return refuse(fn, "the device length has to start on a 4-byte boundary");
+  if (c->length_stride != 0 && !(c->length_stride == 1 && device_length))
+    return refuse(fn, "length_stride %d: only 0, or 1 together with a device length", c->length_stride);
 
   a = fbla_k_decode{};
-  a.cb = c->format == MLOPS_FBLA_3P3 ? 3 : 4;
-  a.fb = c->format == MLOPS_FBLA_3P3 ? 3 : 2;
-  cudaError_t e = fbla_k_decode_shape(&a);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
-  Layout L;
-  decode_layout(&lc, lc.tokens, a, L);
-  if (scratch_bytes < L.bytes) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scratch has %zu bytes, need %zu", fn, scratch_bytes, L.bytes);
-  const int r = c->q_heads / c->kv_heads;
-  a.qg = decode_group(r);
-  a.vg = r / a.qg;
-  if ((long long)c->batch * c->kv_heads * a.vg * L.nslices > 36000)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch * kv_heads * virtual heads * slices of 16384 tokens exceeds 36000 (split the batch)", fn);
-  a.c = kcache(k);
-  a.q = q; a.out = out;
-  char *base = static_cast<char *>(scratch);
-  a.lse = reinterpret_cast<float *>(base + L.lse);
-  a.part = reinterpret_cast<float *>(base + L.part);
-  a.dpart = reinterpret_cast<float *>(base + L.dpart);
-  a.row_r = reinterpret_cast<float *>(base + L.row_r);
-  a.counts = reinterpret_cast<int *>(base + L.counts);
-  a.items = reinterpret_cast<int *>(base + L.items);
-  a.item_off = reinterpret_cast<int *>(base + L.item_off);
-  a.status = reinterpret_cast<int *>(base + L.status);
+  a.cb = coarse_bits(c);
+  a.fb = fine_bits(c);
+  const cudaError_t shape_error = fbla_k_decode_shape(&a);
+  if (shape_error != cudaSuccess) return device_failure(fn, shape_error);
+  const ScratchMap m = map_scratch(&layout, layout.tokens, a, 0);
+  if (scratch_bytes < m.bytes) return refuse(fn, "the scratch is %zu bytes but this decode takes %zu", scratch_bytes, m.bytes);
+  const int ratio = c->q_heads / c->kv_heads;
+  a.qg = queries_per_virtual_head(ratio);
+  a.vg = ratio / a.qg;
+  // the refine pass keeps one prefix entry per (virtual head, slice of 16 384 tokens) in shared memory
+  const long long entries = (long long)c->batch * c->kv_heads * a.vg * m.nslices, entry_limit = fbla_k_refine_entry_limit(a.cb);
+  if (entries > entry_limit)
+    return refuse(fn, "batch * kv_heads * virtual heads * slices of 16384 tokens = %lld is more than the %lld one call handles: split the batch",
+                  entries, entry_limit);
+  a.c = kernel_cache(k);
+  a.q = q;
+  a.out = out;
+  char *const base = static_cast<char *>(scratch);
+  a.lse = reinterpret_cast<float *>(base + m.lse);
+  a.part = reinterpret_cast<float *>(base + m.part);
+  a.dpart = reinterpret_cast<float *>(base + m.dpart);
+  a.row_r = reinterpret_cast<float *>(base + m.row_r);
+  a.counts = reinterpret_cast<int *>(base + m.counts);
+  a.items = reinterpret_cast<int *>(base + m.items);
+  a.item_off = reinterpret_cast<int *>(base + m.item_off);
+  a.status = reinterpret_cast<int *>(base + m.status);
   a.length = length;
   a.lstride = c->length_stride;
-  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads; a.tokens = c->tokens;
-  a.nblocks = L.nblocks; a.nslices = L.nslices;
-  const long long cap = c->capacity ? c->capacity : c->tokens;
-  a.hs = c->head_stride ? c->head_stride : (int)((cap + G - 1) / G);
+  a.batch = c->batch;
+  a.q_heads = c->q_heads;
+  a.kv_heads = c->kv_heads;
+  a.tokens = c->tokens;
+  a.nblocks = m.nblocks;
+  a.nslices = m.nslices;
+  const long long room = c->capacity ? c->capacity : c->tokens;
+  a.hs = c->head_stride ? c->head_stride : (int)groups_of(room);
   a.gs = c->group_stride ? c->group_stride : 1;
-  a.sl = scale_log2(c);
-  // (by the cache's capacity where it has one, for host and device lengths alike: the two calls then run the same
-  // kernels on the same cache and give bit-identical outputs)
-  fbla_k_decode_split(&a, c->capacity ? c->capacity : c->tokens);
-  const float tau = c->tau != 0.f ? c->tau : c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f;
-  a.log2_tau = log2f(tau);
+  a.sl = log2_scale(c);
+  // Which coarse kernel runs is decided by the cache's room where it has one, for host and device lengths alike: both
+  // calls on one cache then run the same kernels and return the same bits.
+  fbla_k_decode_split(&a, room);
+  const float threshold = c->tau != 0.f ? c->tau : (c->format == MLOPS_FBLA_3P3 ? 3e-4f : 1e-3f);
+  a.log2_tau = log2f(threshold);
   return MLOPS_FBLA_OK;
 }
-mlops_fbla_status launch_decode(const char *fn, const fbla_k_decode &a, cudaStream_t stream) {
+mlops_fbla_status enqueue_decode(const char *fn, fbla_k_decode &a, cudaStream_t stream) {
+  a.status_cleared = 1;  // the launcher zeroes the status word on the stream, ahead of the first pass
   const cudaError_t e = fbla_k_decode_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure(fn, e);
 }
-mlops_fbla_status decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
-                         uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+mlops_fbla_status run_decode(const char *fn, const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
+                             uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
   fbla_k_decode a;
-  const mlops_fbla_status st = prepare_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a);
-  return st != MLOPS_FBLA_OK ? st : launch_decode(fn, a, stream);
+  const mlops_fbla_status st = make_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a);
+  return st == MLOPS_FBLA_OK ? enqueue_decode(fn, a, stream) : st;
 }
 
-// ---- prefill ------------------------------------------------------------------------------------------------------------
-mlops_fbla_status prefill_common(const char *fn, const mlops_fbla_config *c, const uint16_t *q, const uint16_t *k, const uint16_t *v,
-                                 const mlops_fbla_cache *x, uint16_t *out) {
-  if (!valid_out_layout(c))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: out_head_stride and out_token_stride both positive multiples of 8 (batch 1) or both 0", fn);
-  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
-  if (!(c->scale >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: scale must be nonnegative", fn);
-  if (!cache_complete(x)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
-  const void *ptrs[] = {k, v, q, out, x->coarse, x->fine, x->meta, x->exact_sink_k, x->exact_sink_v, x->exact_open_k, x->exact_open_v};
-  for (const void *p : ptrs)
-    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: pointers must be 16-byte aligned", fn);
-  if (!aligned(x->tc_images, 128)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: tc_images must be 128-byte aligned", fn);
+// ---- prefill family ---------------------------------------------------------------------------------------------------------------
+// what every chunk call checks after its shape: layout options, format, scale, the cache, alignments
+mlops_fbla_status check_chunk_operands(const char *fn, const mlops_fbla_config *c, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                       const mlops_fbla_cache *cache, uint16_t *out) {
+  if (!output_strides_usable(c))
+    return refuse(fn, "out_head_stride / out_token_stride: leave both 0, or give both as positive multiples of 8 (token stride below 2^30) "
+                      "with batch 1");
+  if (!known_format(c)) return refuse(fn, "format %d is neither MLOPS_FBLA_3P3 nor MLOPS_FBLA_4P2", (int)c->format);
+  if (!(c->scale >= 0.f)) return refuse(fn, "scale may not be negative or NaN");
+  if (!all_cache_arrays_given(cache)) return refuse(fn, "the cache lacks one of its seven arrays");
+  const void *const wide[] = {q, k, v, out, cache->coarse, cache->fine, cache->meta, cache->exact_sink_k, cache->exact_sink_v,
+                              cache->exact_open_k, cache->exact_open_v};
+  if (!all_on_boundary(wide, 16)) return refuse(fn, "q, k, v, output and the cache arrays have to start on 16-byte boundaries");
+  if (!on_boundary(cache->tc_images, 128)) return refuse(fn, "tc_images has to start on a 128-byte boundary");
   return MLOPS_FBLA_OK;
 }
-void fill_prefill(const mlops_fbla_config *c, int count, long long capacity, const uint16_t *q, const uint16_t *k, const uint16_t *v,
-                  const mlops_fbla_cache *x, uint16_t *out, fbla_k_prefill &a) {
-  a.c = kcache(x);
-  a.q = q; a.k = k; a.v = v; a.out = out;
-  a.out_hs = c->out_head_stride ? c->out_head_stride : (int64_t)count * D;
-  a.out_ts = c->out_token_stride ? (int)c->out_token_stride : D;
-  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads;
-  a.n0 = c->tokens; a.count = count;
-  a.hs = c->head_stride ? c->head_stride : (int)((capacity + G - 1) / G);
+void fill_chunk(const mlops_fbla_config *c, int count, long long room, const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                const mlops_fbla_cache *cache, uint16_t *out, fbla_k_prefill &a) {
+  a.c = kernel_cache(cache);
+  a.q = q;
+  a.k = k;
+  a.v = v;
+  a.out = out;
+  a.out_hs = c->out_head_stride ? c->out_head_stride : (int64_t)count * kHeadDim;  // default: [batch, q_heads, count, 128]
+  a.out_ts = c->out_token_stride ? (int)c->out_token_stride : kHeadDim;
+  a.batch = c->batch;
+  a.q_heads = c->q_heads;
+  a.kv_heads = c->kv_heads;
+  a.n0 = c->tokens;
+  a.count = count;
+  a.hs = c->head_stride ? c->head_stride : (int)groups_of(room);
   a.gs = c->group_stride ? c->group_stride : 1;
-  a.cb = c->format == MLOPS_FBLA_3P3 ? 3 : 4;
-  a.fb = c->format == MLOPS_FBLA_3P3 ? 3 : 2;
-  a.sl = scale_log2(c);
+  a.cb = coarse_bits(c);
+  a.fb = fine_bits(c);
+  a.sl = log2_scale(c);
 }
-mlops_fbla_status run_prefill(const char *fn, const fbla_k_prefill &a, int close_blocks, cudaStream_t stream) {
-  // order: close reads the old windows, the attention reads them too, finish overwrites them last
-  cudaError_t e = fbla_k_close_launch(&a, close_blocks, stream);
+// The passes in the order that keeps them correct: closing groups reads the windows as they were, the attention reads
+// them too, and only then are the windows rewritten.
+mlops_fbla_status enqueue_chunk(const char *fn, const fbla_k_prefill &a, int closable_groups, cudaStream_t stream) {
+  cudaError_t e = fbla_k_close_launch(&a, closable_groups, stream);
   if (e == cudaSuccess && a.q) e = fbla_k_attend_launch(&a, stream);
   if (e == cudaSuccess) e = fbla_k_finish_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure(fn, e);
 }
-mlops_fbla_status prefill_at_prepare(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
-                             const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
-                             fbla_k_prefill &a) {
-  if (!c || !length || !cache || !k || !v) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
-  if (q && !out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q needs output", fn);
-  if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 ||
-      (long long)c->tokens + max_count > c->capacity || max_count <= 0 || c->capacity > MAX_TOKENS || !valid_strides(c))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads, max_count and capacity must be positive, tokens >= 0, tokens + max_count <= "
-                "capacity <= 2^26, q_heads a multiple of kv_heads, strides both 0 or both positive", fn);
-  if ((c->length_stride != 0 && c->length_stride != 1) || (c->length_stride && (q || dcount)))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0 (1 only for the one-token append)", fn);
-  const mlops_fbla_status st = prefill_common(fn, c, q, k, v, cache, out);
+// device-length chunk (prefill_at, append_at and their plans)
+mlops_fbla_status make_chunk_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *device_count, int max_count,
+                                const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
+                                fbla_k_prefill &a) {
+  if (!c || !length || !cache || !k || !v) return refuse(fn, "a required pointer is null");
+  if (q && !out) return refuse(fn, "queries were given but no output to write their attention to");
+  const bool shape_ok = heads_consistent(c) && unit_strides_consistent(c) && c->tokens >= 0 && max_count > 0 && c->capacity > 0 &&
+                        c->capacity <= kTokenLimit && (long long)c->tokens + max_count <= c->capacity;
+  if (!shape_ok)
+    return refuse(fn, "needs batch, q_heads, kv_heads > 0 with kv_heads dividing q_heads; a token offset >= 0; max_count > 0; "
+                      "offset + max_count within a capacity of at most 2^26; head_stride and group_stride given together or not at all");
+  if (c->length_stride != 0 && !(c->length_stride == 1 && !q && !device_count))
+    return refuse(fn, "length_stride %d: per-row lengths (1) exist for the one-token append only", c->length_stride);
+  const mlops_fbla_status st = check_chunk_operands(fn, c, q, k, v, cache, out);
   if (st != MLOPS_FBLA_OK) return st;
-  if (!aligned(length, 4) || !aligned(dcount, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length and count must be 4-byte aligned", fn);
+  if (!on_boundary(length, 4) || !on_boundary(device_count, 4)) return refuse(fn, "the device length and count have to start on 4-byte boundaries");
   a = fbla_k_prefill{};
-  fill_prefill(c, max_count, c->capacity, q, k, v, cache, out, a);
-  a.length = length; a.dcount = dcount; a.lstride = c->length_stride;
+  fill_chunk(c, max_count, c->capacity, q, k, v, cache, out, a);
+  a.length = length;
+  a.dcount = device_count;
+  a.lstride = c->length_stride;
   return MLOPS_FBLA_OK;
 }
-mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *dcount, int max_count,
-                             const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
-                             cudaStream_t stream) {
+mlops_fbla_status run_chunk_at(const char *fn, const mlops_fbla_config *c, const int *length, const int *device_count, int max_count,
+                               const uint16_t *q, const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
+                               cudaStream_t stream) {
   fbla_k_prefill a;
-  const mlops_fbla_status st = prefill_at_prepare(fn, c, length, dcount, max_count, q, k, v, cache, out, a);
-  // a chunk of at most max_count tokens starting anywhere closes at most max_count / 128 + 1 groups
-  return st != MLOPS_FBLA_OK ? st : run_prefill(fn, a, max_count / G + 1, stream);
+  const mlops_fbla_status st = make_chunk_at(fn, c, length, device_count, max_count, q, k, v, cache, out, a);
+  // wherever it starts, a chunk of max_count tokens completes at most max_count / 128 + 1 groups
+  return st == MLOPS_FBLA_OK ? enqueue_chunk(fn, a, max_count / kGroup + 1, stream) : st;
 }
 
 }  // namespace
@@ -236,45 +295,44 @@ mlops_fbla_status prefill_at(const char *fn, const mlops_fbla_config *c, const i
 extern "C" {
 
 size_t mlops_fbla_decode_scratch_bytes(const mlops_fbla_config *c) {
-  if (!valid_decode_shape(c) || !valid_format(c)) return 0;
-  return scratch_bytes_of(c);
+  return decode_shape_acceptable(c) && known_format(c) ? scratch_size(c, 0) : 0;
 }
 
+// per_head: partial rows per virtual head an executor wants room for on top of this library's own launch shape. The
+// plans always use the library's persistent grid; a larger per_head only enlarges the answer, never shrinks it.
 size_t mlops_fbla_decode_scratch_bytes_for(const mlops_fbla_config *c, int per_head) {
-  if (!c || c->capacity <= 0 || per_head < 0) return 0;
-  mlops_fbla_config lc = *c;
-  lc.tokens = c->capacity;
-  if (!valid_decode_shape(&lc) || !valid_format(c)) return 0;
-  return scratch_bytes_of(&lc);
+  if (!c || per_head < 0 || c->capacity <= 0) return 0;
+  mlops_fbla_config layout = *c;
+  layout.tokens = c->capacity;
+  return decode_shape_acceptable(&layout) && known_format(c) ? scratch_size(&layout, per_head) : 0;
 }
 
 mlops_fbla_status mlops_fbla_decode(const mlops_fbla_config *c, const uint16_t *q, const mlops_fbla_cache *k, uint16_t *out,
                                     void *scratch, size_t scratch_bytes, cudaStream_t stream) {
-  return decode("mlops_fbla_decode", c, nullptr, q, k, out, scratch, scratch_bytes, stream);
+  return run_decode("mlops_fbla_decode", c, nullptr, q, k, out, scratch, scratch_bytes, stream);
 }
 
 mlops_fbla_status mlops_fbla_decode_at(const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k,
                                        uint16_t *out, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
-  if (!length) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_decode_at: null length");
-  if (c && c->capacity <= 0) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_decode_at: capacity must be positive");
-  return decode("mlops_fbla_decode_at", c, length, q, k, out, scratch, scratch_bytes, stream);
+  constexpr const char *fn = "mlops_fbla_decode_at";
+  if (!length) return refuse(fn, "the device length pointer is null");
+  if (c && c->capacity <= 0) return refuse(fn, "a device-length decode is laid out by capacity, which has to be positive");
+  return run_decode(fn, c, length, q, k, out, scratch, scratch_bytes, stream);
 }
 
-size_t mlops_fbla_images_bytes(const mlops_fbla_config *) { return 0; }
+size_t mlops_fbla_images_bytes(const mlops_fbla_config *) { return 0; }  // no persistent prefill images in this library
 
 int mlops_fbla_cache_sizes(const mlops_fbla_config *c, mlops_fbla_sizes *out) {
-  if (!c || !out || c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->q_heads % c->kv_heads || !valid_strides(c)) return 0;
-  if (!valid_format(c)) return 0;
-  const long long tokens = c->capacity ? c->capacity : c->tokens;
-  if (tokens <= 0 || (c->capacity && c->capacity < c->tokens)) return 0;
-  const size_t heads = (size_t)c->batch * c->kv_heads, groups = (size_t)((tokens + G - 1) / G);
-  const size_t hs = c->head_stride ? (size_t)c->head_stride : groups, gs = c->group_stride ? (size_t)c->group_stride : 1;
-  const size_t units = (heads - 1) * hs + (groups - 1) * gs + 1;
-  const bool three = c->format == MLOPS_FBLA_3P3;
-  out->coarse = units * SBG * (three ? 1536 : 2048);
-  out->fine = units * SBG * (three ? 1536 : 1024);
+  if (!c || !out || !heads_consistent(c) || !unit_strides_consistent(c) || !known_format(c)) return 0;
+  const long long room = c->capacity ? c->capacity : c->tokens;
+  if (room <= 0 || (c->capacity != 0 && c->capacity < c->tokens)) return 0;
+  const size_t heads = (size_t)c->batch * c->kv_heads, groups = (size_t)groups_of(room);
+  const size_t head_step = c->head_stride ? (size_t)c->head_stride : groups, group_step = c->group_stride ? (size_t)c->group_stride : 1;
+  const size_t units = (heads - 1) * head_step + (groups - 1) * group_step + 1;  // up to the last unit any (head, group) maps to
+  out->coarse = units * kBlocksPerGroup * (size_t)(512 * coarse_bits(c));
+  out->fine = units * kBlocksPerGroup * (size_t)(512 * fine_bits(c));
   out->meta = units * 1024;
-  out->exact = heads * G * D * sizeof(uint16_t);
+  out->exact = heads * kGroup * kHeadDim * sizeof(uint16_t);
   out->images = 0;
   return 1;
 }
@@ -282,176 +340,199 @@ int mlops_fbla_cache_sizes(const mlops_fbla_config *c, mlops_fbla_sizes *out) {
 mlops_fbla_status mlops_fbla_prefill(const mlops_fbla_config *c, int count, const uint16_t *q, const uint16_t *k, const uint16_t *v,
                                      const mlops_fbla_cache *cache, uint16_t *out, cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_prefill";
-  if (!c || !cache || !k || !v) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
-  if (q && !out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q needs output", fn);
-  const long long n1 = (long long)c->tokens + count;
-  if (c->batch <= 0 || c->q_heads <= 0 || c->kv_heads <= 0 || c->tokens < 0 || count <= 0 || !valid_strides(c) || c->q_heads % c->kv_heads ||
-      !(c->capacity == 0 || c->capacity >= n1) || n1 > MAX_TOKENS)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch, heads and count must be positive, tokens >= 0, q_heads a multiple of kv_heads, "
-                "tokens + count <= capacity (0: tokens + count) and <= 2^26, strides both 0 or both positive", fn);
-  const mlops_fbla_status st = prefill_common(fn, c, q, k, v, cache, out);
+  if (!c || !cache || !k || !v) return refuse(fn, "a required pointer is null");
+  if (q && !out) return refuse(fn, "queries were given but no output to write their attention to");
+  const long long end = (long long)c->tokens + count;
+  const bool shape_ok = heads_consistent(c) && unit_strides_consistent(c) && c->tokens >= 0 && count > 0 && end <= kTokenLimit &&
+                        (c->capacity == 0 || c->capacity >= end);
+  if (!shape_ok)
+    return refuse(fn, "needs batch, q_heads, kv_heads > 0 with kv_heads dividing q_heads; tokens >= 0; count > 0; tokens + count within the "
+                      "capacity (when one is given) and 2^26; head_stride and group_stride given together or not at all");
+  const mlops_fbla_status st = check_chunk_operands(fn, c, q, k, v, cache, out);
   if (st != MLOPS_FBLA_OK) return st;
   fbla_k_prefill a{};
-  fill_prefill(c, count, c->capacity ? c->capacity : n1, q, k, v, cache, out, a);
-  const int g_first = c->tokens == 0 ? 0 : (c->tokens - 1) / G, g_end = (int)((n1 - 1) / G);
-  return run_prefill(fn, a, g_end - g_first, stream);
+  fill_chunk(c, count, c->capacity ? c->capacity : end, q, k, v, cache, out, a);
+  // groups completed by this chunk: those whose last token lies before `end` and that were still open before it
+  const int first_open = c->tokens == 0 ? 0 : (c->tokens - 1) / kGroup, last_open = (int)((end - 1) / kGroup);
+  return enqueue_chunk(fn, a, last_open - first_open, stream);
 }
 
 mlops_fbla_status mlops_fbla_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q,
                                         const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out,
                                         cudaStream_t stream) {
-  if (!count) return fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_prefill_at: null argument");
-  return prefill_at("mlops_fbla_prefill_at", c, length, count, max_count, q, k, v, cache, out, stream);
+  constexpr const char *fn = "mlops_fbla_prefill_at";
+  if (!count) return refuse(fn, "a required pointer is null");
+  return run_chunk_at(fn, c, length, count, max_count, q, k, v, cache, out, stream);
 }
 
 mlops_fbla_status mlops_fbla_append_at(const mlops_fbla_config *c, const int *length, const uint16_t *k, const uint16_t *v,
                                        const mlops_fbla_cache *cache, cudaStream_t stream) {
-  return prefill_at("mlops_fbla_append_at", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, stream);
+  return run_chunk_at("mlops_fbla_append_at", c, length, nullptr, 1, nullptr, k, v, cache, nullptr, stream);
 }
 
-// ---- fused QKV step (reference: attention/fbla/src/fbla.cu:307-400) ---------------------------------------------------------
-static mlops_fbla_status token_common(const char *fn, const mlops_fbla_token *t, fbla_k_token &a) {
-  if (!t->q_norm != !t->k_norm) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: q_norm and k_norm both or neither", fn);
-  if (!(t->eps >= 0.f) || !(t->attention_factor >= 0.f)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: eps and attention_factor nonnegative", fn);
-  a.q = t->q; a.k = t->k; a.v = t->v;
-  a.batch_stride = t->batch_stride; a.q_group_stride = t->q_group_stride; a.kv_group_stride = t->kv_group_stride;
-  a.q_norm = t->q_norm; a.k_norm = t->k_norm; a.freq = t->freq; a.eps = t->eps;
+// ---- fused QKV step (reference rules: attention/fbla/src/fbla.cu:307-400) ----------------------------------------------------
+static mlops_fbla_status fill_token_common(const char *fn, const mlops_fbla_token *t, fbla_k_token &a) {
+  if ((t->q_norm == nullptr) != (t->k_norm == nullptr)) return refuse(fn, "give the norm weights of q and k both or neither");
+  if (!(t->eps >= 0.f) || !(t->attention_factor >= 0.f)) return refuse(fn, "eps and attention_factor may not be negative or NaN");
+  a.q = t->q;
+  a.k = t->k;
+  a.v = t->v;
+  a.batch_stride = t->batch_stride;
+  a.q_group_stride = t->q_group_stride;
+  a.kv_group_stride = t->kv_group_stride;
+  a.q_norm = t->q_norm;
+  a.k_norm = t->k_norm;
+  a.freq = t->freq;
+  a.eps = t->eps;
   a.att = t->attention_factor == 0.f ? 1.f : t->attention_factor;
   return MLOPS_FBLA_OK;
 }
 
-static mlops_fbla_status qkv_at_prepare(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
-                                        fbla_k_prefill &cl, fbla_k_token &a) {
+static mlops_fbla_status make_token_step(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
+                                         fbla_k_prefill &closing, fbla_k_token &a) {
   constexpr const char *fn = "mlops_fbla_qkv_at";
-  if (!c || !length || !t || !cache || !t->q || !t->k || !t->v || !t->freq || !t->q_out) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
-  if (c->batch <= 0 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || c->capacity <= 0 || !valid_strides(c))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch and heads must be positive, q_heads a multiple of kv_heads, tokens >= 0, capacity positive, "
-                "strides both 0 or both positive", fn);
-  if (!valid_format(c)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: invalid format", fn);
+  if (!c || !length || !t || !cache || !t->q || !t->k || !t->v || !t->freq || !t->q_out) return refuse(fn, "a required pointer is null");
+  if (!heads_consistent(c) || !unit_strides_consistent(c) || c->tokens < 0 || c->capacity <= 0)
+    return refuse(fn, "needs batch, q_heads, kv_heads > 0 with kv_heads dividing q_heads; a token offset >= 0; capacity > 0; "
+                      "head_stride and group_stride given together or not at all");
+  if (!known_format(c)) return refuse(fn, "format %d is neither MLOPS_FBLA_3P3 nor MLOPS_FBLA_4P2", (int)c->format);
   a = fbla_k_token{};
-  mlops_fbla_status st = token_common(fn, t, a);
+  const mlops_fbla_status st = fill_token_common(fn, t, a);
   if (st != MLOPS_FBLA_OK) return st;
-  if (!cache_complete(cache)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: every cache pointer is required", fn);
-  const void *p16[] = {cache->coarse, cache->fine, cache->meta, cache->exact_sink_k, cache->exact_sink_v, cache->exact_open_k, cache->exact_open_v, t->freq};
-  for (const void *p : p16)
-    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: cache pointers and freq must be 16-byte aligned", fn);
-  const void *p4[] = {length, t->q, t->k, t->v, t->q_norm, t->k_norm, t->q_out};
-  for (const void *p : p4)
-    if (!aligned(p, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length and the token's pointers must be 4-byte aligned", fn);
-  if (t->batch_stride % 2 || t->q_group_stride % 2 || t->kv_group_stride % 2)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: strides must be even (4-byte rows)", fn);
-  if (t->batch_stride < 0 || t->q_group_stride < 0 || t->kv_group_stride < 0 || t->batch_stride > INT32_MAX || t->q_group_stride > INT32_MAX ||
-      t->kv_group_stride > INT32_MAX)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: strides are nonnegative and below 2^31", fn);
-  if (!aligned(cache->tc_images, 128)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: tc_images must be 128-byte aligned", fn);
-  if (c->length_stride != 0 && c->length_stride != 1) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length_stride is 0 or 1", fn);
-  // the group that the position closes (when it is a multiple of 128) is quantized from the open window first
-  cl = fbla_k_prefill{};
-  fill_prefill(c, 1, c->capacity, nullptr, nullptr, nullptr, cache, nullptr, cl);
-  cl.length = length; cl.lstride = c->length_stride;
-  a.c = cl.c; a.length = length; a.lstride = c->length_stride; a.n0 = c->tokens; a.max_count = 1;
-  a.batch = c->batch; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads; a.q_out = t->q_out;
+  if (!all_cache_arrays_given(cache)) return refuse(fn, "the cache lacks one of its seven arrays");
+  const void *const wide[] = {cache->coarse, cache->fine, cache->meta, cache->exact_sink_k, cache->exact_sink_v, cache->exact_open_k,
+                              cache->exact_open_v, t->freq};
+  if (!all_on_boundary(wide, 16)) return refuse(fn, "the cache arrays and freq have to start on 16-byte boundaries");
+  const void *const narrow[] = {length, t->q, t->k, t->v, t->q_norm, t->k_norm, t->q_out};
+  if (!all_on_boundary(narrow, 4)) return refuse(fn, "the device length and the token's tensors have to start on 4-byte boundaries");
+  const int64_t strides[] = {t->batch_stride, t->q_group_stride, t->kv_group_stride};
+  for (const int64_t stride : strides) {
+    if (stride % 2) return refuse(fn, "an odd stride: head rows are read as 4-byte words, strides have to be even");
+    if (stride < 0 || stride > INT32_MAX) return refuse(fn, "strides lie between 0 and 2^31 - 1 elements");
+  }
+  if (!on_boundary(cache->tc_images, 128)) return refuse(fn, "tc_images has to start on a 128-byte boundary");
+  if (c->length_stride != 0 && c->length_stride != 1) return refuse(fn, "length_stride %d: only 0 or 1", c->length_stride);
+  // a position that is a multiple of 128 completes the previous group: it is quantized from the open window first
+  closing = fbla_k_prefill{};
+  fill_chunk(c, 1, c->capacity, nullptr, nullptr, nullptr, cache, nullptr, closing);
+  closing.length = length;
+  closing.lstride = c->length_stride;
+  a.c = closing.c;
+  a.length = length;
+  a.lstride = c->length_stride;
+  a.n0 = c->tokens;
+  a.max_count = 1;
+  a.batch = c->batch;
+  a.q_heads = c->q_heads;
+  a.kv_heads = c->kv_heads;
+  a.q_out = t->q_out;
   return MLOPS_FBLA_OK;
 }
 mlops_fbla_status mlops_fbla_qkv_at(const mlops_fbla_config *c, const int *length, const mlops_fbla_token *t, const mlops_fbla_cache *cache,
                                     cudaStream_t stream) {
-  fbla_k_prefill cl;
+  fbla_k_prefill closing;
   fbla_k_token a;
-  const mlops_fbla_status st = qkv_at_prepare(c, length, t, cache, cl, a);
+  const mlops_fbla_status st = make_token_step(c, length, t, cache, closing, a);
   if (st != MLOPS_FBLA_OK) return st;
-  cudaError_t e = fbla_k_close_launch(&cl, 1, stream);
+  cudaError_t e = fbla_k_close_launch(&closing, 1, stream);
   if (e == cudaSuccess) e = fbla_k_qkv_token_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "mlops_fbla_qkv_at: %s", cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure("mlops_fbla_qkv_at", e);
 }
 
-static mlops_fbla_status qkv_chunk_prepare(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
-                                           uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, fbla_k_token &a) {
+static mlops_fbla_status make_token_chunk(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
+                                          uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, fbla_k_token &a) {
   constexpr const char *fn = "mlops_fbla_qkv_prefill_at";
   if (!c || !length || !count || !t || !t->q || !t->k || !t->v || !t->freq || !q_out || !k_out || !v_out)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: null argument", fn);
-  if (c->batch != 1 || c->kv_heads <= 0 || c->q_heads <= 0 || c->q_heads % c->kv_heads || c->tokens < 0 || max_count <= 0 || c->capacity <= 0 ||
-      (long long)c->tokens + max_count > c->capacity)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: batch 1, positive heads (q_heads a multiple of kv_heads), tokens >= 0, max_count > 0, "
-                "tokens + max_count <= capacity", fn);
+    return refuse(fn, "a required pointer is null");
+  const bool shape_ok = c->batch == 1 && c->kv_heads > 0 && c->q_heads > 0 && c->q_heads % c->kv_heads == 0 && c->tokens >= 0 && max_count > 0 &&
+                        c->capacity > 0 && (long long)c->tokens + max_count <= c->capacity;
+  if (!shape_ok)
+    return refuse(fn, "works on batch 1 with q_heads, kv_heads > 0 (kv_heads dividing q_heads), a token offset >= 0, max_count > 0 and "
+                      "offset + max_count within the capacity");
   a = fbla_k_token{};
-  mlops_fbla_status st = token_common(fn, t, a);
+  const mlops_fbla_status st = fill_token_common(fn, t, a);
   if (st != MLOPS_FBLA_OK) return st;
-  if (t->batch_stride < D || t->batch_stride % 2 || t->q_group_stride % 2 || t->kv_group_stride % 2 || t->q_group_stride < 0 || t->kv_group_stride < 0)
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: the row stride (batch_stride) and the group strides must be even, the row at least 128", fn);
-  const void *p16[] = {q_out, k_out, v_out, t->freq};
-  for (const void *p : p16)
-    if (!aligned(p, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: outputs and freq must be 16-byte aligned", fn);
-  const void *p4[] = {length, count, t->q, t->k, t->v, t->q_norm, t->k_norm};
-  for (const void *p : p4)
-    if (!aligned(p, 4)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: length, count and the projection's pointers must be 4-byte aligned", fn);
-  a.length = length; a.dcount = count; a.n0 = c->tokens; a.max_count = max_count;
-  a.batch = 1; a.q_heads = c->q_heads; a.kv_heads = c->kv_heads;
-  a.q_out = q_out; a.k_out = k_out; a.v_out = v_out;
+  const bool strides_ok = t->batch_stride >= kHeadDim && t->batch_stride % 2 == 0 && t->q_group_stride >= 0 && t->q_group_stride % 2 == 0 &&
+                          t->kv_group_stride >= 0 && t->kv_group_stride % 2 == 0;
+  if (!strides_ok) return refuse(fn, "batch_stride is the stride between projection rows: even and at least one head (128); the group strides even, >= 0");
+  const void *const wide[] = {q_out, k_out, v_out, t->freq};
+  if (!all_on_boundary(wide, 16)) return refuse(fn, "q_out, k_out, v_out and freq have to start on 16-byte boundaries");
+  const void *const narrow[] = {length, count, t->q, t->k, t->v, t->q_norm, t->k_norm};
+  if (!all_on_boundary(narrow, 4)) return refuse(fn, "length, count and the projection's tensors have to start on 4-byte boundaries");
+  a.length = length;
+  a.dcount = count;
+  a.n0 = c->tokens;
+  a.max_count = max_count;
+  a.batch = 1;
+  a.q_heads = c->q_heads;
+  a.kv_heads = c->kv_heads;
+  a.q_out = q_out;
+  a.k_out = k_out;
+  a.v_out = v_out;
   return MLOPS_FBLA_OK;
 }
 mlops_fbla_status mlops_fbla_qkv_prefill_at(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const mlops_fbla_token *t,
                                             uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, cudaStream_t stream) {
   fbla_k_token a;
-  const mlops_fbla_status st = qkv_chunk_prepare(c, length, count, max_count, t, q_out, k_out, v_out, a);
+  const mlops_fbla_status st = make_token_chunk(c, length, count, max_count, t, q_out, k_out, v_out, a);
   if (st != MLOPS_FBLA_OK) return st;
   const cudaError_t e = fbla_k_qkv_chunk_launch(&a, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "mlops_fbla_qkv_prefill_at: %s", cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure("mlops_fbla_qkv_prefill_at", e);
 }
 
 // ---- sequence shards (include/mlops_fbla_shard.h) ------------------------------------------------------------------------
-static mlops_fbla_status shard_args(const char *fn, const mlops_fbla_shard *sh, fbla_k_decode &a) {
+static mlops_fbla_status apply_shard(const char *fn, const mlops_fbla_shard *sh, fbla_k_decode &a) {
   if (!sh || sh->group_first < 0 || sh->group_count < 0 || (sh->windows & ~3))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: shard needs group_first >= 0, group_count >= 0, windows in 0..3", fn);
-  a.shard_on = 1; a.sh_first = sh->group_first; a.sh_count = sh->group_count; a.sh_windows = sh->windows;
+    return refuse(fn, "the shard descriptor needs group_first >= 0, group_count >= 0 and windows within 0..3");
+  a.shard_on = 1;
+  a.sh_first = sh->group_first;
+  a.sh_count = sh->group_count;
+  a.sh_windows = sh->windows;
   return MLOPS_FBLA_OK;
 }
 
 mlops_fbla_status mlops_fbla_shard_mass(const mlops_fbla_config *c, const mlops_fbla_shard *sh, const uint16_t *q, const mlops_fbla_cache *k,
                                         float *row_mass, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_shard_mass";
-  if (!row_mass || !aligned(row_mass, 16)) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: row_mass must be a 16-byte aligned device pointer", fn);
+  if (!row_mass || !on_boundary(row_mass, 16)) return refuse(fn, "row_mass has to be a device pointer on a 16-byte boundary");
   fbla_k_decode a;
-  mlops_fbla_status st = prepare_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
-  if (st == MLOPS_FBLA_OK) st = shard_args(fn, sh, a);
+  mlops_fbla_status st = make_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
+  if (st == MLOPS_FBLA_OK) st = apply_shard(fn, sh, a);
   if (st != MLOPS_FBLA_OK) return st;
   a.phase = 1;
   a.row_r = row_mass;
-  return launch_decode(fn, a, stream);
+  return enqueue_decode(fn, a, stream);
 }
 
 mlops_fbla_status mlops_fbla_shard_partial(const mlops_fbla_config *c, const mlops_fbla_shard *sh, const uint16_t *q, const mlops_fbla_cache *k,
                                            const float *row_mass_total, float *partial, void *scratch, size_t scratch_bytes,
                                            cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_shard_partial";
-  if (!row_mass_total || !partial || !aligned(row_mass_total, 16) || !aligned(partial, 16))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: row_mass_total and partial must be 16-byte aligned device pointers", fn);
+  if (!row_mass_total || !partial || !on_boundary(row_mass_total, 16) || !on_boundary(partial, 16))
+    return refuse(fn, "row_mass_total and partial have to be device pointers on 16-byte boundaries");
   fbla_k_decode a;
-  mlops_fbla_status st = prepare_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
-  if (st == MLOPS_FBLA_OK) st = shard_args(fn, sh, a);
+  mlops_fbla_status st = make_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, a);
+  if (st == MLOPS_FBLA_OK) st = apply_shard(fn, sh, a);
   if (st != MLOPS_FBLA_OK) return st;
   a.phase = 2;
   a.row_r = const_cast<float *>(row_mass_total);
   a.out_partial = partial;
-  return launch_decode(fn, a, stream);
+  return enqueue_decode(fn, a, stream);
 }
 
 mlops_fbla_status mlops_fbla_shard_total_mass(int shards, int rows, const float *gathered, float *row_mass_total, cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_shard_total_mass";
-  if (shards <= 0 || rows <= 0 || !gathered || !row_mass_total) return fail(MLOPS_FBLA_INVALID_VALUE, "%s: shards and rows must be positive, pointers non-null", fn);
+  if (shards <= 0 || rows <= 0 || !gathered || !row_mass_total) return refuse(fn, "needs shards > 0, rows > 0 and both device pointers");
   const cudaError_t e = fbla_k_total_mass_launch(gathered, row_mass_total, shards, rows, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure(fn, e);
 }
 
 mlops_fbla_status mlops_fbla_shard_combine(int rows, const float *partial_sum, uint16_t *output, cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_shard_combine";
-  if (rows <= 0 || !partial_sum || !output || !aligned(partial_sum, 16) || !aligned(output, 16))
-    return fail(MLOPS_FBLA_INVALID_VALUE, "%s: rows must be positive, pointers 16-byte aligned", fn);
+  if (rows <= 0 || !partial_sum || !output || !on_boundary(partial_sum, 16) || !on_boundary(output, 16))
+    return refuse(fn, "needs rows > 0 and both device pointers on 16-byte boundaries");
   const cudaError_t e = fbla_k_combine_launch(partial_sum, output, rows, stream);
-  if (e != cudaSuccess) return fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
-  return ok();
+  return e == cudaSuccess ? accepted() : device_failure(fn, e);
 }
 
 // ---- work items (include/mlops_fbla_items.h; reference: attention/fbla/src/fbla_kernels.cuh:1446-1510 plan builders,
@@ -473,11 +554,11 @@ template <class A> bool fill_pass(mlops_fbla_items &p, int kind, const fbla_k_pa
 }
 void cache_geom(mlops_fbla_items &p, int hs, int gs, long long capacity, int cb, int fb) {
   p.geom[MLOPS_FBLA_GEOM_HEAD_STRIDE] = hs; p.geom[MLOPS_FBLA_GEOM_GROUP_STRIDE] = gs;
-  p.geom[MLOPS_FBLA_GEOM_CAPACITY_GROUPS] = (capacity + G - 1) / G;
+  p.geom[MLOPS_FBLA_GEOM_CAPACITY_GROUPS] = groups_of(capacity);
   p.geom[MLOPS_FBLA_GEOM_COARSE_BYTES] = 2 * cb * 256; p.geom[MLOPS_FBLA_GEOM_FINE_BYTES] = 2 * fb * 256;
 }
 int plan_fail(const cudaError_t e, const char *fn) {
-  fail(MLOPS_FBLA_CUDA_ERROR, "%s: %s", fn, cudaGetErrorString(e));
+  device_failure(fn, e);
   return -1;
 }
 
@@ -493,13 +574,13 @@ struct Ranges {
 // the units of KV head h (all groups the layout holds): records and metadata
 void head_units(Ranges &r, const mlops_fbla_items &p, int h, int write, bool coarse, bool fine, bool meta) {
   const long long hs = p.geom[MLOPS_FBLA_GEOM_HEAD_STRIDE], gs = p.geom[MLOPS_FBLA_GEOM_GROUP_STRIDE], cg = p.geom[MLOPS_FBLA_GEOM_CAPACITY_GROUPS];
-  const long long uc = SBG * p.geom[MLOPS_FBLA_GEOM_COARSE_BYTES], uf = SBG * p.geom[MLOPS_FBLA_GEOM_FINE_BYTES];
+  const long long uc = kBlocksPerGroup * p.geom[MLOPS_FBLA_GEOM_COARSE_BYTES], uf = kBlocksPerGroup * p.geom[MLOPS_FBLA_GEOM_FINE_BYTES];
   if (coarse) r.add(MLOPS_FBLA_ARG_COARSE, write, h * hs * uc, uc, gs * uc, (int)cg);
   if (fine) r.add(MLOPS_FBLA_ARG_FINE, write, h * hs * uf, uf, gs * uf, (int)cg);
   if (meta) r.add(MLOPS_FBLA_ARG_META, write, h * hs * 1024, 1024, gs * 1024, (int)cg);
 }
 void head_windows(Ranges &r, int h, int write, bool sink, bool open) {
-  const long long w = (long long)G * D * 2;
+  const long long w = (long long)kGroup * kHeadDim * 2;
   if (sink) { r.add(MLOPS_FBLA_ARG_SINK_K, write, h * w, w); r.add(MLOPS_FBLA_ARG_SINK_V, write, h * w, w); }
   if (open) { r.add(MLOPS_FBLA_ARG_OPEN_K, write, h * w, w); r.add(MLOPS_FBLA_ARG_OPEN_V, write, h * w, w); }
 }
@@ -507,14 +588,14 @@ void head_windows(Ranges &r, int h, int write, bool sink, bool open) {
 }  // extern "C++"
 
 int mlops_fbla_decode_at_items(const mlops_fbla_config *c, const int *length, const uint16_t *q, const mlops_fbla_cache *k, uint16_t *out,
-                               void *scratch, size_t scratch_bytes, int /*per_head*/, mlops_fbla_items *passes, int max) {
+                               void *scratch, size_t scratch_bytes, int /*per_head: see mlops_fbla_decode_scratch_bytes_for*/, mlops_fbla_items *passes, int max) {
   constexpr const char *fn = "mlops_fbla_decode_at_items";
-  if (!length) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: null length", fn); return -1; }
-  if (c && c->capacity <= 0) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: capacity must be positive", fn); return -1; }
+  if (!length) { refuse(fn, "the device length pointer is null"); return -1; }
+  if (c && c->capacity <= 0) { refuse(fn, "a device-length decode is laid out by capacity, which has to be positive"); return -1; }
   fbla_k_decode a;
-  if (prepare_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a) != MLOPS_FBLA_OK) return -1;
-  if (max == 0) { ok(); return 4; }
-  if (!passes || max < 4) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 4 passes is needed", fn); return -1; }
+  if (make_decode(fn, c, length, q, k, out, true, scratch, scratch_bytes, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { accepted(); return 4; }
+  if (!passes || max < 4) { refuse(fn, "the plan has 4 passes: `max` is too small or `passes` is null"); return -1; }
   fbla_k_pass info[4];
   const cudaError_t e = fbla_k_decode_passes(&a, info);
   if (e != cudaSuccess) return plan_fail(e, fn);
@@ -529,38 +610,42 @@ int mlops_fbla_decode_at_items(const mlops_fbla_config *c, const int *length, co
     p.geom[MLOPS_FBLA_GEOM_ITEMS] = (const char *)a.items - base; p.geom[MLOPS_FBLA_GEOM_COUNTS] = (const char *)a.counts - base;
     p.geom[3] = (const char *)a.item_off - base; p.geom[4] = (const char *)a.status - base;
   }
-  ok();
+  accepted();
   return 4;
 }
 
 static int prefill_items(const char *fn, const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q,
                          const uint16_t *k, const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out, mlops_fbla_items *passes, int max) {
   fbla_k_prefill a;
-  if (prefill_at_prepare(fn, c, length, count, max_count, q, k, v, cache, out, a) != MLOPS_FBLA_OK) return -1;
-  const int n = q ? 3 : 2;
-  if (max == 0) { ok(); return n; }
-  if (!passes || max < n) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for %d passes is needed", fn, n); return -1; }
+  if (make_chunk_at(fn, c, length, count, max_count, q, k, v, cache, out, a) != MLOPS_FBLA_OK) return -1;
+  fbla_k_prefill parts[2];
+  int tc[2];
+  const int np = q ? fbla_k_attend_plan(&a, parts, tc) : 0, n = 2 + np;  // close, the attention's one or two passes, finish
+  if (max == 0) { accepted(); return n; }
+  if (!passes || max < n) { refuse(fn, "the plan has %d passes: `max` is too small or `passes` is null", n); return -1; }
   fbla_k_pass info;
-  int at = 0, tensor = 0;
-  cudaError_t e = fbla_k_close_pass(&a, max_count / G + 1, &info);
+  int at = 0;
+  cudaError_t e = fbla_k_close_pass(&a, max_count / kGroup + 1, &info);
   if (e != cudaSuccess) return plan_fail(e, fn);
   fill_pass(passes[at++], MLOPS_FBLA_ITEM_CLOSE, info, "fbla_k_prefill", a);
   if (q) {
-    e = fbla_k_attend_pass(&a, &info, &tensor);
-    if (e != cudaSuccess) return plan_fail(e, fn);
-    fill_pass(passes[at++], tensor ? MLOPS_FBLA_ITEM_TC : MLOPS_FBLA_ITEM_STREAM, info, "fbla_k_prefill", a);
+    for (int i = 0; i < np; ++i) {
+      e = tc[i] ? fbla_k_attend_tc_pass(&parts[i], &info) : fbla_k_attend_rows_pass(&parts[i], &info);
+      if (e != cudaSuccess) return plan_fail(e, fn);
+      fill_pass(passes[at++], tc[i] ? MLOPS_FBLA_ITEM_TC : MLOPS_FBLA_ITEM_STREAM, info, "fbla_k_prefill", parts[i]);
+    }
   }
   e = fbla_k_finish_pass(&a, &info);
   if (e != cudaSuccess) return plan_fail(e, fn);
   fill_pass(passes[at++], MLOPS_FBLA_ITEM_FINISH, info, "fbla_k_prefill", a);
   for (int i = 0; i < at; ++i) { cache_geom(passes[i], a.hs, a.gs, c->capacity, a.cb, a.fb); passes[i].geom[3] = max_count; }
-  ok();
+  accepted();
   return at;
 }
 
 int mlops_fbla_prefill_at_items(const mlops_fbla_config *c, const int *length, const int *count, int max_count, const uint16_t *q, const uint16_t *k,
                                 const uint16_t *v, const mlops_fbla_cache *cache, uint16_t *out, mlops_fbla_items *passes, int max) {
-  if (!count) { fail(MLOPS_FBLA_INVALID_VALUE, "mlops_fbla_prefill_at_items: null argument"); return -1; }
+  if (!count) { refuse("mlops_fbla_prefill_at_items", "a required pointer is null"); return -1; }
   return prefill_items("mlops_fbla_prefill_at_items", c, length, count, max_count, q, k, v, cache, out, passes, max);
 }
 
@@ -574,9 +659,9 @@ int mlops_fbla_qkv_at_items(const mlops_fbla_config *c, const int *length, const
   constexpr const char *fn = "mlops_fbla_qkv_at_items";
   fbla_k_prefill cl;
   fbla_k_token a;
-  if (qkv_at_prepare(c, length, t, cache, cl, a) != MLOPS_FBLA_OK) return -1;
-  if (max == 0) { ok(); return 2; }
-  if (!passes || max < 2) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 2 passes is needed", fn); return -1; }
+  if (make_token_step(c, length, t, cache, cl, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { accepted(); return 2; }
+  if (!passes || max < 2) { refuse(fn, "the plan has 2 passes: `max` is too small or `passes` is null"); return -1; }
   fbla_k_pass info;
   cudaError_t e = fbla_k_close_pass(&cl, 1, &info);
   if (e != cudaSuccess) return plan_fail(e, fn);
@@ -585,7 +670,7 @@ int mlops_fbla_qkv_at_items(const mlops_fbla_config *c, const int *length, const
   if (e != cudaSuccess) return plan_fail(e, fn);
   fill_pass(passes[1], MLOPS_FBLA_ITEM_QKV, info, "fbla_k_token", a);
   for (int i = 0; i < 2; ++i) { cache_geom(passes[i], cl.hs, cl.gs, c->capacity, cl.cb, cl.fb); passes[i].geom[3] = 1; }
-  ok();
+  accepted();
   return 2;
 }
 
@@ -593,15 +678,15 @@ int mlops_fbla_qkv_prefill_at_items(const mlops_fbla_config *c, const int *lengt
                                     uint16_t *q_out, uint16_t *k_out, uint16_t *v_out, mlops_fbla_items *passes, int max) {
   constexpr const char *fn = "mlops_fbla_qkv_prefill_at_items";
   fbla_k_token a;
-  if (qkv_chunk_prepare(c, length, count, max_count, t, q_out, k_out, v_out, a) != MLOPS_FBLA_OK) return -1;
-  if (max == 0) { ok(); return 1; }
-  if (!passes || max < 1) { fail(MLOPS_FBLA_INVALID_VALUE, "%s: room for 1 pass is needed", fn); return -1; }
+  if (make_token_chunk(c, length, count, max_count, t, q_out, k_out, v_out, a) != MLOPS_FBLA_OK) return -1;
+  if (max == 0) { accepted(); return 1; }
+  if (!passes || max < 1) { refuse(fn, "the plan has 1 pass: `max` is too small or `passes` is null"); return -1; }
   fbla_k_pass info;
   const cudaError_t e = fbla_k_qkv_chunk_pass(&a, &info);
   if (e != cudaSuccess) return plan_fail(e, fn);
   fill_pass(passes[0], MLOPS_FBLA_ITEM_QKV_CHUNK, info, "fbla_k_token", a);
   passes[0].geom[3] = max_count;
-  ok();
+  accepted();
   return 1;
 }
 
@@ -620,7 +705,7 @@ int mlops_fbla_item_access(const mlops_fbla_items *passes, int npasses, int pass
   if (item < 0 || item >= p.items) return -1;
   Ranges r{ranges, max, 0};
   const int x = item % (int)p.geom[0], y = (item / (int)p.geom[0]) % (int)p.geom[1];
-  const long long row = D * 2;  // bytes of one head vector
+  const long long row = kHeadDim * 2;  // bytes of one head vector
   if (p.kind >= MLOPS_FBLA_ITEM_COARSE && p.kind <= MLOPS_FBLA_ITEM_MERGE) {
     fbla_k_decode a;
     memcpy(&a, p.args.bytes, sizeof a);
@@ -723,6 +808,6 @@ const char *mlops_fbla_status_string(mlops_fbla_status status) {
   return "unknown status";
 }
 
-const char *mlops_fbla_last_error(void) { return error_buf; }
+const char *mlops_fbla_last_error(void) { return g_message; }
 
 }  // extern "C"

@@ -66,6 +66,10 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   }
   if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   cudaError_t e = cudaSuccess;
+  if (a.status_cleared) {  // ordered before every report of this call (a bounded wait that gives up)
+    e = cudaMemsetAsync(a.status, 0, 16, stream);
+    if (e != cudaSuccess) return e;
+  }
   if (a.phase != 2) {
     if (a.coarse_warps == CoarseShape<CB>::TOTAL) coarse_kernel<CB, FB, QG, true><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
     else coarse_kernel<CB, FB, QG, false><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
@@ -79,6 +83,25 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   if (e == cudaSuccess) e = launch_dependent(refine_kernel<CB, FB, QG>, dim3(a.refine_ctas), dim3(32 * RefineShape<CB, FB>::WARPS), rsm, stream, a);
   if (e == cudaSuccess) e = launch_dependent(merge_kernel<QG>, dim3(vheads * QG), dim3(512), 0, stream, a);
   return e;
+}
+
+// one pass alone, as an ordinary launch (no overlap with its neighbours): for measurements pass by pass
+template <int CB, int FB, int QG> cudaError_t launch_one(const fbla_k_decode &a, int pass, cudaStream_t stream) {
+  const int vheads = a.batch * a.kv_heads * a.vg;
+  const size_t csm = sizeof(CoarseSmem<CB>);
+  const size_t rsm = sizeof(RefineWarp<CB, FB>) * RefineShape<CB, FB>::WARPS + sizeof(int) * ((size_t)vheads * a.nslices + 1);
+  if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
+  switch (pass) {
+    case 0:
+      if (a.coarse_warps == CoarseShape<CB>::TOTAL) coarse_kernel<CB, FB, QG, true><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+      else coarse_kernel<CB, FB, QG, false><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+      break;
+    case 1: select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a); break;
+    case 2: refine_kernel<CB, FB, QG><<<a.refine_ctas, 32 * RefineShape<CB, FB>::WARPS, rsm, stream>>>(a); break;
+    case 3: merge_kernel<QG><<<vheads * QG, 512, 0, stream>>>(a); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 template <int CB, int FB, int QG> cudaError_t passes_of(const fbla_k_decode &a, fbla_k_pass *p) {
@@ -129,6 +152,12 @@ extern "C" cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out
   return cudaGetLastError();
 }
 
+extern "C" long long fbla_k_refine_entry_limit(int cb) {
+  using namespace fbla;
+  const size_t ring = cb == 3 ? sizeof(RefineWarp<3, 3>) * RefineShape<3, 3>::WARPS : sizeof(RefineWarp<4, 2>) * RefineShape<4, 2>::WARPS;
+  return (long long)((REFINE_SMEM_MAX - ring) / sizeof(int)) - 1;
+}
+
 extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -136,7 +165,7 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return e;
   a->coarse_ctas = sms;
-  a->coarse_warps = a->cb == 4 ? fbla::CoarseShape<4>::WARPS : fbla::CoarseShape<3>::WARPS;
+  a->coarse_warps = fbla::CoarseShape<4>::TOTAL;  // (the larger of the two layouts: what the scratch is sized for)
   a->refine_ctas = sms;
   a->refine_warps = fbla::RefineShape<4, 2>::WARPS;
   return cudaSuccess;
@@ -165,6 +194,23 @@ extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t
     case 1: return launch_all<4, 2, 1>(*a, stream);
     case 2: return launch_all<4, 2, 2>(*a, stream);
     default: return launch_all<4, 2, 4>(*a, stream);
+  }
+}
+
+// (after one whole fbla_k_decode_launch on this device: that call sets the kernels' shared-memory attributes)
+extern "C" cudaError_t fbla_k_decode_pass_launch(const fbla_k_decode *a, int pass, cudaStream_t stream) {
+  using namespace fbla;
+  if (a->cb == 3) {
+    switch (a->qg) {
+      case 1: return launch_one<3, 3, 1>(*a, pass, stream);
+      case 2: return launch_one<3, 3, 2>(*a, pass, stream);
+      default: return launch_one<3, 3, 4>(*a, pass, stream);
+    }
+  }
+  switch (a->qg) {
+    case 1: return launch_one<4, 2, 1>(*a, pass, stream);
+    case 2: return launch_one<4, 2, 2>(*a, pass, stream);
+    default: return launch_one<4, 2, 4>(*a, pass, stream);
   }
 }
 

@@ -138,9 +138,9 @@ __device__ __forceinline__ int q_row(const fbla_k_decode &a, int b, int hir, int
 
 // ---- per-group query quantization (the definition of include/mlops_fbla.h) --------------------------------------------
 // Lane l holds channels 4 l .. 4 l + 3: km = the lane's 16 metadata bytes of K (4 bases, 4 steps), q4 = its 4 q values.
-// Writes the lane's qhat word to qst_row[l]; returns through the references the warp-uniform sq, qb (= sl q . base),
-// qsum (= sum qhat).
-__device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, uint32_t *qst_row, int lane, float &sq, float &qb, float &qsum) {
+// Returns the lane's qhat word (quantize_query also writes it to qst_row[l]) and, through the references, the
+// warp-uniform sq, qb (= sl q . base), qsum (= sum qhat).
+__device__ __forceinline__ uint32_t quantize_query_word(uint4 km, float4 q4, float sl, float &sq, float &qb, float &qsum) {
   const float kb[4] = {bf_lo(km.x), bf_hi(km.x), bf_lo(km.y), bf_hi(km.y)}, ks[4] = {bf_lo(km.z), bf_hi(km.z), bf_lo(km.w), bf_hi(km.w)};
   const float qf[4] = {q4.x, q4.y, q4.z, q4.w};
   float z[4], amax = 0.f, dot = 0.f;
@@ -157,10 +157,13 @@ __device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, ui
 #pragma unroll
   for (int x = 0; x < 4; ++x)  // rint(z r) in the low mantissa bits: one rounding of the exact product
     word |= (__float_as_uint(fmaf(z[x], r, MAGICF)) & 255u) << (8 * x);
-  qst_row[lane] = word;
   sq = __fmul_rn(amax, __fmul_rn(sl, 1.f / 127.f));
   qb = __fmul_rn(warp_sum(dot), sl);
   qsum = (float)__reduce_add_sync(FULL, __dp4a((int)word, 0x01010101, 0));  // the exact integer sum of the codes
+  return word;
+}
+__device__ __forceinline__ void quantize_query(uint4 km, float4 q4, float sl, uint32_t *qst_row, int lane, float &sq, float &qb, float &qsum) {
+  qst_row[lane] = quantize_query_word(km, q4, sl, sq, qb, qsum);
 }
 
 // ---- shared memory of the coarse kernel ---------------------------------------------------------------------------------
@@ -170,6 +173,11 @@ template <int CB> struct __align__(128) StreamWarp {
   uint8_t qst[8 * QST_ROW];  // qhat rows (rows >= QG stay zero)
   uint8_t pst[128];          // P bytes of a record pair: [block parity][query 0..3][16 tokens]
   uint64_t bar_pair[CoarseShape<CB>::NP], bar_meta[2];
+  // The partial rows of the first and the last virtual head of the warp's run, which neighbouring warps of the CTA may
+  // share: they are folded into one row per (CTA, virtual head) before they leave the CTA. stage_vh: the rows' virtual
+  // heads (-1: no such row).
+  float stage[2][4][FBLA_K_PSTRIDE];
+  int stage_vh[2];
 };
 struct __align__(16) ExactWarp {
   float q[4][D];
@@ -222,7 +230,9 @@ struct WindowTile {
   uint2 v[16];
   int j, count;  // sub-block within its window, the window's token count
 };
-template <int QG>
+// AHEAD: the next sub-block's loads are issued before the current one is computed (two tiles of registers); without it
+// a warp that shares its CTA with many others stays within their register budget.
+template <int QG, bool AHEAD = true>
 __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
   const int hpr = a.kv_heads * a.vg;
   const long long total = total_units<true>(a, hpr), per = ceil_div(total, nxw);
@@ -258,8 +268,9 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       w.v[tt] = w.j * S + tt < w.count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(w.j * S + tt) * D) + lane) : make_uint2(0u, 0u);
   };
   WindowTile cur, nxt;
-  load(c, cur);
+  if (AHEAD) load(c, cur);
   for (long long u = lo; u < hi; ++u) {
+    if (!AHEAD) load(c, cur);
     const int vh = c.b * hpr + c.hir;
     if (vh != cur_vh) {
       if (cur_vh >= 0) flush();
@@ -275,7 +286,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       __syncwarp();
     }
     advance<true>(a, hpr, c);
-    if (u + 1 < hi) load(c, nxt);
+    if (AHEAD && u + 1 < hi) load(c, nxt);
     const int tok = cur.j * S + t;
     float x[QG];
 #pragma unroll
@@ -335,7 +346,7 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
       for (int cc = 0; cc < 4; ++cc) o[qi][cc] = fmaf(al[qi], o[qi][cc], w[qi] * y[qi][cc]);
     }
     __syncwarp();
-    cur = nxt;
+    if (AHEAD) cur = nxt;
   }
   flush();
 }
@@ -589,6 +600,31 @@ template <int QG> __device__ __forceinline__ void write_partial(float *p, const 
 }
 
 
+// dst (scratch) = the staged row set `own` merged with the first staged row sets of the next `more` warps (`next` points at
+// the first of them, the following ones lie one StreamWarp further each): per query the usual log-sum-exp merge of
+// (m, l, o[128]), taken in warp order. Lane l owns channels 4 l .. 4 l + 3.
+template <int QG, class W>
+__device__ __forceinline__ void fold_rows(float *dst, const float *own, const float *next, int more, int lane, size_t warp_stride_floats) {
+#pragma unroll
+  for (int qi = 0; qi < QG; ++qi) {
+    const float *p = own + qi * PSTRIDE;
+    float4 o = *reinterpret_cast<const float4 *>(p + 4 * lane);
+    float m = p[D], l = p[D + 1];
+    for (int x = 0; x < more; ++x) {
+      const float *n = next + (size_t)x * warp_stride_floats + qi * PSTRIDE;
+      const float4 o2 = *reinterpret_cast<const float4 *>(n + 4 * lane);
+      const float m2 = n[D], l2 = n[D + 1];
+      const float mn = fmaxf(m, m2), sa = ex2(m - mn), sb = ex2(m2 - mn);
+      o.x = fmaf(o.x, sa, o2.x * sb); o.y = fmaf(o.y, sa, o2.y * sb); o.z = fmaf(o.z, sa, o2.z * sb); o.w = fmaf(o.w, sa, o2.w * sb);
+      l = fmaf(l, sa, l2 * sb);
+      m = mn;
+    }
+    float *d = dst + qi * PSTRIDE;
+    *reinterpret_cast<float4 *>(d + 4 * lane) = o;
+    if (lane == 0) { d[D] = m; d[D + 1] = l; }
+  }
+}
+
 template <int CB, int FB, int QG, bool DYN>
 __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *smem_raw) {
   using Sh = CoarseShape<CB>;
@@ -596,7 +632,7 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   smem_raw += (128u - (smem_u32(smem_raw) & 127u)) & 127u;  // (an executor's storage is 16-byte aligned; an offset keeps the pointer's address space known)
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = FBLA_POS::tid() & 31, warp = FBLA_POS::tid() >> 5;
-  if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status) { a.status[0] = 0; a.status[1] = 0; }
+  if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status && !a.status_cleared) { a.status[0] = 0; a.status[1] = 0; }
   if (!DYN) {
     if (warp >= Sh::WARPS) {
 #ifdef FBLA_NOWINDOW  // tuning builds only
@@ -633,44 +669,96 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
 
   const long long total = total_units<false>(a, hpr), tw = (long long)FBLA_POS::nx() * sw, per = ceil_div(total, tw);
   const long long gw = (long long)FBLA_POS::x() * sw + warp, lo = gw * per, hi = min(total, lo + per);
-  if (lo >= hi) return;
-  Cursor cc = locate<false>(a, hpr, lo);
-  Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(Sh::CPG * (hi - lo)), nullptr, nullptr};
-  ring.point();
+  // (before leaving, a warp invalidates its barriers: an executor may run another item on this CTA, whose initialisation
+  // then meets no live barrier object)
+  auto retire = [&]() {
+    __syncwarp();
+    if (lane == 0) {
 #pragma unroll
-  for (int s = 0; s < Sh::NP; ++s) ring.issue_next();
-  Run run;
-  float4 q4[QG];
-  int cur_vh = -1;
-  for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
-    const int vh = cc.b * hpr + cc.hir;
-    if (vh != cur_vh) {
-      if (cur_vh >= 0) write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
-      cur_vh = vh;
-      reset<QG>(run);
+      for (int s = 0; s < Sh::NP; ++s) mbar_inval(&w.bar_pair[s]);
+      mbar_inval(&w.bar_meta[0]);
+      mbar_inval(&w.bar_meta[1]);
+    }
+  };
+  // One partial row per (CTA, virtual head): slot cta + vh. Rows of virtual heads that lie wholly inside the warp's run go
+  // straight to the scratch; the run's first and last virtual head may continue in the neighbouring warps, so their rows
+  // are staged in shared memory and folded below, in warp order (a fixed order: the result is reproducible bit for bit).
+  const int cta = FBLA_POS::x();
+  int first_vh = -1, cur_vh = -1;
+  bool ok = true;
+  if (lo < hi) {
+    Cursor cc = locate<false>(a, hpr, lo);
+    Ring<CB> ring{w, a, hpr, lane, cc, 0, (int)(Sh::CPG * (hi - lo)), nullptr, nullptr};
+    ring.point();
 #pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, cc.b, cc.hir, qi) * D) + lane);
-        q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
+    for (int s = 0; s < Sh::NP; ++s) ring.issue_next();
+    Run run;
+    float4 q4[QG];
+    for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
+      const int vh = cc.b * hpr + cc.hir;
+      if (vh != cur_vh) {
+        if (cur_vh >= 0) write_partial<QG>(cur_vh == first_vh ? &w.stage[0][0][0] : a.part + (size_t)(cta + cur_vh) * QG * PSTRIDE, run, lane, false);
+        if (cur_vh < 0) first_vh = vh;
+        cur_vh = vh;
+        reset<QG>(run);
+#pragma unroll
+        for (int qi = 0; qi < QG; ++qi) {
+          const uint2 qw = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, cc.b, cc.hir, qi) * D) + lane);
+          q4[qi] = make_float4(bf_lo(qw.x), bf_hi(qw.x), bf_lo(qw.y), bf_hi(qw.y));
+        }
+      }
+      if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)group_of(a, cc) * SBG) * QG)) {
+        if (lane == 0) report(a, 1);
+        ok = false;
+        break;
       }
     }
-    if (!coarse_group<CB, FB, QG>(ring, (int)(u - lo), q4, a.sl, lane, run, a.lse + ((size_t)vh * a.nblocks + (size_t)group_of(a, cc) * SBG) * QG)) {
-      if (lane == 0) report(a, 1);
-      return;
-    }
+    if (ok) write_partial<QG>(&w.stage[cur_vh == first_vh ? 0 : 1][0][0], run, lane, false);
   }
-  write_partial<QG>(a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, false);
+  if (ok) retire();  // (after a wait that gave up a copy may still be in flight: the barriers stay as they are)
+  if (lane == 0) {
+    w.stage_vh[0] = ok ? first_vh : -1;
+    w.stage_vh[1] = ok && cur_vh != first_vh ? cur_vh : -1;
+  }
+  // every streaming warp of the CTA has staged its rows
+  asm volatile("bar.sync 1, %0;" ::"r"(32 * sw) : "memory");
+  // Row r of this warp is folded here unless an earlier warp does it: the first row belongs to the first warp that
+  // touched its virtual head, the last row (a later virtual head) always to this warp. The rows that continue it are
+  // the first rows of the following warps, as long as those warps stay inside the same virtual head.
+#pragma unroll 1
+  for (int r = 0; r < 2; ++r) {
+    const int v = w.stage_vh[r];
+    if (v < 0) continue;
+    if (r == 0 && warp > 0) {
+      const StreamWarp<CB> &prev = sm.w[warp - 1];
+      const int prev_last = prev.stage_vh[1] >= 0 ? prev.stage_vh[1] : prev.stage_vh[0];
+      if (prev_last == v) continue;
+    }
+    if (r == 0 && w.stage_vh[1] >= 0) {  // the virtual head ends inside this warp's run: nothing to fold
+      fold_rows<QG, StreamWarp<CB>>(a.part + (size_t)(cta + v) * QG * PSTRIDE, &w.stage[0][0][0], nullptr, 0, lane, 0);
+      continue;
+    }
+    int more = 0;
+    for (int x = warp + 1; x < sw && sm.w[x].stage_vh[0] == v; ++x) {
+      ++more;
+      if (sm.w[x].stage_vh[1] >= 0) break;
+    }
+    fold_rows<QG, StreamWarp<CB>>(a.part + (size_t)(cta + v) * QG * PSTRIDE, &w.stage[r][0][0], warp + 1 < Sh::WARPS ? &sm.w[warp + 1].stage[0][0][0] : nullptr, more, lane, sizeof(StreamWarp<CB>) / sizeof(float));
+  }
 }
 
 // ---- which partial slots belong to a virtual head ------------------------------------------------------------------------
-struct Slots { int c0, c1, x0, x1; };  // coarse warps c0..c1 (slot w + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
+struct Slots { int c0, c1, x0, x1; };  // coarse CTAs c0..c1 (slot cta + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
 __device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
   const int hpr = a.kv_heads * a.vg;
   Slots s{0, -1, 0, -1};
   int n;
   const Split sp = split_of(a, hpr);
   long long off = head_offset<false>(a, hpr, vh, n);
-  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
+  if (n > 0) {  // a CTA's sw streaming warps take sw consecutive runs of `per` units: one (folded) row per CTA
+    const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw) * sp.sw;
+    s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per);
+  }
   off = head_offset<true>(a, hpr, vh, n);
   if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * sp.xw); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
   return s;
@@ -694,12 +782,13 @@ __device__ __forceinline__ void select_item(const fbla_k_decode &a, uint8_t *sme
   const Row row = row_of(a, vh / hpr);
   const Slots s = slots_of(a, vh);
   wait_previous_pass();
-  // the slice's sub-block masses first (they do not depend on R): every load of the warp in flight together
-  const int lo = slice * SLICE + warp * (SLICE / 8), first = SBG * row.g0, hi = SBG * (row.g0 + row.closed);
+  // the slice's sub-block masses first (they do not depend on R): a thread takes four consecutive sub-blocks, so its loads
+  // are contiguous and all in flight together
+  const int mine0 = slice * SLICE + warp * (SLICE / 8) + 4 * lane, first = SBG * row.g0, hi = SBG * (row.g0 + row.closed);
   float x[4][QG];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int sb = lo + 32 * i + lane;
+    const int sb = mine0 + i;
     const bool closed = a.phase != 1 && sb >= first && sb < hi;
     const float *p = a.lse + ((size_t)vh * a.nblocks + (closed ? sb : 0)) * QG;
 #pragma unroll
@@ -710,14 +799,24 @@ __device__ __forceinline__ void select_item(const fbla_k_decode &a, uint8_t *sme
   } else if (warp < QG) {  // R of query `warp`: one pass over the head's partial (m, l), merged online, then across lanes
     const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
     float mx = -FBLA_INF, ls = 0.f;
-    for (int i = lane; i < n; i += 32) {
-      const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
-      const float m = __ldcg(p + D), l = __ldcg(p + D + 1);
-      if (m != -FBLA_INF) {
-        const float mn = fmaxf(mx, m);
-        ls = fmaf(ls, ex2(mx - mn), l * ex2(m - mn));
-        mx = mn;
+    for (int i0 = 0; i0 < n; i0 += 128) {  // four rows per lane at a time, their loads all in flight before the first is used
+      float mm[4], ll[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + 32 * j + lane;
+        mm[j] = -FBLA_INF; ll[j] = 0.f;
+        if (i < n) {
+          const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, warp) : window_slot(a, s.x0 + i - nc, vh, warp);
+          mm[j] = __ldcg(p + D); ll[j] = __ldcg(p + D + 1);
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (mm[j] != -FBLA_INF) {
+          const float mn = fmaxf(mx, mm[j]);
+          ls = fmaf(ls, ex2(mx - mn), ll[j] * ex2(mm[j] - mn));
+          mx = mn;
+        }
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) {
@@ -733,27 +832,31 @@ __device__ __forceinline__ void select_item(const fbla_k_decode &a, uint8_t *sme
   }
   if (a.phase == 1) return;  // only the local mass was asked for
   __syncthreads();
-  int qm[4], n = 0;
-  uint32_t bal[4];
+  // The thread's selected sub-blocks become items (sub-block << 4) | query mask; their place in the slice's list:
+  // an inclusive scan of the per-thread counts over the warp, and the warps' totals through shared memory.
+  int masks[4], kept = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    qm[i] = 0;
+    masks[i] = 0;
 #pragma unroll
-    for (int qi = 0; qi < QG; ++qi) qm[i] |= (x[i][qi] - R[qi] > a.log2_tau) << qi;
-    bal[i] = __ballot_sync(FULL, qm[i] != 0);
-    n += __popc(bal[i]);
+    for (int qi = 0; qi < QG; ++qi) masks[i] |= (x[i][qi] - R[qi] > a.log2_tau ? 1 : 0) << qi;
+    kept += masks[i] != 0;
   }
-  if (!lane) wc[warp] = n;
+  int upto = kept;  // selected by lanes 0 .. lane of this warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int below = __shfl_up_sync(FULL, upto, o);
+    if (lane >= o) upto += below;
+  }
+  if (lane == 31) wc[warp] = upto;
   __syncthreads();
-  int off = 0, total = 0;
+  int before = 0, total = 0;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) { off += w < warp ? wc[w] : 0; total += wc[w]; }
-  int *items = a.items + ((size_t)vh * a.nslices + slice) * SLICE;
+  for (int w = 0; w < 8; ++w) { if (w < warp) before += wc[w]; total += wc[w]; }
+  int *dst = a.items + ((size_t)vh * a.nslices + slice) * SLICE + before + (upto - kept);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (qm[i]) items[off + __popc(bal[i] & ((1u << lane) - 1u))] = (lo + 32 * i + lane) << 4 | qm[i];
-    off += __popc(bal[i]);
-  }
+  for (int i = 0; i < 4; ++i)
+    if (masks[i]) *dst++ = ((mine0 + i) << 4) | masks[i];
   if (!FBLA_POS::tid()) a.counts[(size_t)vh * a.nslices + slice] = total;
 }
 
@@ -1007,6 +1110,11 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
     }
   }
   write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
+  __syncwarp();
+  if (lane == 0) {  // (as the coarse pass: no live barrier is left behind for the CTA's next item)
+#pragma unroll
+    for (int s = 0; s < Sh::NST; ++s) mbar_inval(&w.bar[s]);
+  }
 }
 
 // ---- merge: out = (sum 2^(m_c - R) o_c + sum do) / (sum 2^(m_c - R) l_c + sum dl), BF16 ---------------------------------
@@ -1070,11 +1178,15 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
   if (sl == 0) {
     const float Os = (so[0][ch] + so[1][ch]) + (so[2][ch] + so[3][ch]), Ls = (sl_[0] + sl_[1]) + (sl_[2] + sl_[3]);
     const size_t row = (size_t)q_row(a, b, hir, qi);
+    // a pass of this call reported a wait that gave up: some partial rows were never written, so the row is NaN, not a
+    // plausible number (every pass has completed by now, so every report is visible)
+    const bool failed = a.status && __ldcg(a.status) != 0;
+    const float nan = __int_as_float(0x7fc00000);
     if (a.out_partial) {  // a shard's share of the row, in units of 2^-R: summed over the shards before the division
-      a.out_partial[row * PSTRIDE + ch] = Os;
-      if (ch == 0) a.out_partial[row * PSTRIDE + D] = Ls;
+      a.out_partial[row * PSTRIDE + ch] = failed ? nan : Os;
+      if (ch == 0) a.out_partial[row * PSTRIDE + D] = failed ? nan : Ls;
     } else {
-      a.out[row * D + ch] = f32_to_bf16(__fdividef(Os, Ls));
+      a.out[row * D + ch] = failed ? (uint16_t)0x7fc0 : f32_to_bf16(__fdividef(Os, Ls));
     }
   }
 }

@@ -113,6 +113,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_inval(uint64_t *bar) {  // the word may then be re-initialised (the next item on this CTA) or reused
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_init_fence() {  // make the initialised barriers visible to the copy engine
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -159,6 +162,22 @@ __host__ __device__ constexpr int word_offset(int bits, int t, int l, int w) {
        : bits == 2 ? 512 * t + 16 * l + 4 * w
        : w < 4 ? 512 * t + 16 * l + 4 * w
        : t ? 1280 + 8 * l + 4 * (w - 4) : 1024 + 16 * (l % 16) + 8 * (l / 16) + 4 * (w - 4);
+}
+
+// the four codes of slot s of a lane's words W[0 .. 2 BITS - 1] of one tensor, one code per byte, unscaled
+template <int BITS> __device__ __forceinline__ uint32_t slot_value(const uint32_t *W, int s) {
+  if (BITS == 4) return s < 8 ? W[s] & 0x0f0f0f0fu : (W[s - 8] >> 4) & 0x0f0f0f0fu;
+  if (BITS == 2) return (W[s & 3] >> (2 * (s >> 2))) & 0x03030303u;
+  if (s < 6) return W[s] & 0x07070707u;
+  if (s < 12) return (W[s - 6] >> 3) & 0x07070707u;
+  const int r = s - 12;
+  return ((W[r] >> 6) & 0x03030303u) | ((W[4 + (r >> 1)] >> (4 + (r & 1))) & 0x04040404u);
+}
+// the V slot holding channel cc (of the lane's four) and token quad `quad`: the inverse of (v_chan, v_quad)
+__host__ __device__ constexpr int v_slot_of(int bits, int cc, int quad) {
+  return bits == 4 ? (cc < 2 ? 2 * quad + cc : 8 + 2 * quad + (cc - 2))
+       : bits == 2 ? 4 * cc + quad
+       : cc == 0 ? quad : cc == 1 ? 6 + quad : cc == 2 ? (quad < 2 ? 4 + quad : 8 + quad) : 12 + quad;
 }
 
 }  // namespace fbla

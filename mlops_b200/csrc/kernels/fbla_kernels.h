@@ -45,7 +45,7 @@ typedef struct {
   int qg, vg;            // queries per virtual head, virtual heads per KV head
   int cb, fb;            // plane bits
   int coarse_ctas, coarse_warps;  // persistent coarse CTAs; coarse_warps: 7 = seven streaming warps + one window warp per CTA,
-                                  // 8 = the CTA's eight warps split by the lengths (TW = 8 coarse_ctas bounds both kinds)
+                                  // 8 = the CTA's eight warps split by the lengths (8 coarse_ctas bounds both layouts)
   int refine_ctas, refine_warps;  // RW = refine_ctas * refine_warps
   float sl, log2_tau;
   // Sequence shards (one GPU's part of a long context); shard_on 0: the whole cache. A shard processes the closed groups
@@ -54,18 +54,25 @@ typedef struct {
   // the given (global) row_r, refine, and the rows' unnormalised sums (o[128], l, relative to row_r) into out_partial.
   int shard_on, sh_first, sh_count, sh_windows, phase;
   float *out_partial;  // [rows][FBLA_K_PSTRIDE] floats (phase 2)
+  int status_cleared;  // 1: the launcher zeroes the status word on the stream before the first pass; 0: CTA 0 of the coarse pass does
 } fbla_k_decode;
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */
 
 FBLA_HOST_API(cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream);)
+// One pass of a decode alone (0 coarse, 1 select, 2 refine, 3 merge) as an ordinary launch, for timing the passes one by
+// one; `a` as fbla_k_decode_launch takes it (e.g. the argument blob of a decode plan). Valid after one whole decode has
+// run on the device.
+FBLA_HOST_API(cudaError_t fbla_k_decode_pass_launch(const fbla_k_decode *a, int pass, cudaStream_t stream);)
 // chooses the split of the coarse CTAs' warps for rows of about `tokens` tokens (after fbla_k_decode_shape; the scratch layout holds either)
 FBLA_HOST_API(void fbla_k_decode_split(fbla_k_decode *a, long long tokens);)
 // out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
 // total[i] = log2 sum over shards of 2^mass[s][i]
 FBLA_HOST_API(cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);)
 FBLA_HOST_API(cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *out, int rows, cudaStream_t stream);)
+// the most (virtual head, slice) entries one decode may have: the refine pass keeps their prefix sums in shared memory
+FBLA_HOST_API(long long fbla_k_refine_entry_limit(int cb);)
 // occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
 FBLA_HOST_API(cudaError_t fbla_k_decode_shape(fbla_k_decode *a);)
 
@@ -83,17 +90,26 @@ typedef struct {
   int hs, gs;
   int cb, fb;
   float sl;
+  // 0: the attention pass serves every count. > 0 (a chunk whose count lives on the device): the attention is two
+  // passes and the count decides on the device which of them works -- the tensor-core pass when count * queries per KV
+  // head >= tc_min_rows, the warp-per-row pass below that -- so that a device-count call takes the kernel the host-count
+  // call of the same chunk takes and the two stay bit-identical.
+  int tc_min_rows;
 } fbla_k_prefill;
 
 // close_blocks: grid x of the close pass (groups the chunk can close); 0 skips it
 FBLA_HOST_API(cudaError_t fbla_k_close_launch(const fbla_k_prefill *a, int close_blocks, cudaStream_t stream);)
 FBLA_HOST_API(cudaError_t fbla_k_finish_launch(const fbla_k_prefill *a, cudaStream_t stream);)
-// attention of the chunk's rows: the tensor-core kernel (tcgen05, 128 rows per CTA), or -- for chunks of fewer than
-// FBLA_K_TC_MIN_ROWS rows, or when the environment variable MLOPS_FBLA_PREFILL=rows asks for it -- one warp per row
-FBLA_HOST_API(cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);)
+// Attention of the chunk's rows: the tensor-core kernel (tcgen05, 128 rows per CTA), or -- for chunks of fewer than
+// FBLA_K_TC_MIN_ROWS rows, or when the environment variable MLOPS_FBLA_PREFILL=rows asks for it -- one warp per row.
+// fbla_k_attend_plan splits a chunk's attention into its one or two passes (two when the count is on the device and
+// its ceiling reaches the tensor-core kernel, see tc_min_rows): args[i] / tensor[i] for pass i; returns their number.
+FBLA_HOST_API(int fbla_k_attend_plan(const fbla_k_prefill *a, fbla_k_prefill args[2], int tensor[2]);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream);)  // every pass of the plan
 FBLA_HOST_API(cudaError_t fbla_k_attend_rows_launch(const fbla_k_prefill *a, cudaStream_t stream);)
 FBLA_HOST_API(cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream);)
-// 1 if a bounded wait of the tensor-core kernel gave up since the last call (and clears it), 0 if not, -1 on a CUDA error
+// 1 if a bounded wait of the tensor-core kernel gave up since the last call (and clears it), 0 if not, -1 on a CUDA
+// error. A CTA whose wait gave up also writes NaN to every output row it owns, so the failure shows in the data.
 FBLA_HOST_API(int fbla_k_attend_tc_status(void);)
 #define FBLA_K_TC_MIN_ROWS 64
 
@@ -125,7 +141,7 @@ FBLA_HOST_API(cudaError_t fbla_k_decode_passes(const fbla_k_decode *a, fbla_k_pa
 FBLA_HOST_API(cudaError_t fbla_k_close_pass(const fbla_k_prefill *a, int close_blocks, fbla_k_pass *info);)
 FBLA_HOST_API(cudaError_t fbla_k_finish_pass(const fbla_k_prefill *a, fbla_k_pass *info);)
 FBLA_HOST_API(cudaError_t fbla_k_attend_rows_pass(const fbla_k_prefill *a, fbla_k_pass *info);)
-FBLA_HOST_API(cudaError_t fbla_k_attend_pass(const fbla_k_prefill *a, fbla_k_pass *info, int *tensor_cores);)
+FBLA_HOST_API(cudaError_t fbla_k_attend_tc_pass(const fbla_k_prefill *a, fbla_k_pass *info);)
 FBLA_HOST_API(cudaError_t fbla_k_qkv_token_pass(const fbla_k_token *a, fbla_k_pass *info);)
 FBLA_HOST_API(cudaError_t fbla_k_qkv_chunk_pass(const fbla_k_token *a, fbla_k_pass *info);)
 

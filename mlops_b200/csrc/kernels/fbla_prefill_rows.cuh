@@ -12,20 +12,6 @@
 
 namespace fbla {
 
-// the four codes of slot s of a lane's words W[0 .. 2 BITS - 1], unscaled (one code per byte)
-template <int BITS> __device__ __forceinline__ uint32_t slot_value(const uint32_t *W, int s) {
-  if (BITS == 4) return s < 8 ? W[s] & 0x0f0f0f0fu : (W[s - 8] >> 4) & 0x0f0f0f0fu;
-  if (BITS == 2) return (W[s & 3] >> (2 * (s >> 2))) & 0x03030303u;
-  if (s < 6) return W[s] & 0x07070707u;
-  if (s < 12) return (W[s - 6] >> 3) & 0x07070707u;
-  const int r = s - 12;
-  return ((W[r] >> 6) & 0x03030303u) | ((W[4 + (r >> 1)] >> (4 + (r & 1))) & 0x04040404u);
-}
-__host__ __device__ constexpr int v_slot_of(int bits, int cc, int quad) {
-  return bits == 4 ? (cc < 2 ? 2 * quad + cc : 8 + 2 * quad + (cc - 2))
-       : bits == 2 ? 4 * cc + quad
-       : cc == 0 ? quad : cc == 1 ? 6 + quad : cc == 2 ? (quad < 2 ? 4 + quad : 8 + quad) : 12 + quad;
-}
 template <int BITS> __device__ __forceinline__ void load_words(const uint8_t *rec, int tensor, int lane, uint32_t *W) {
 #pragma unroll
   for (int w = 0; w < 2 * BITS; ++w) W[w] = __ldcg(reinterpret_cast<const uint32_t *>(rec + word_offset(BITS, tensor, lane, w)));
@@ -64,7 +50,7 @@ __device__ __forceinline__ void attend_rows_item(const fbla_k_prefill &a, uint8_
   const int n0 = (a.length ? FBLA_POS::ro(a.length + (a.lstride ? b : 0)) : 0) + a.n0;
   const int count = a.dcount ? FBLA_POS::ro(a.dcount) : a.count, n1 = n0 + count;
   const int r = FBLA_POS::x() * 8 + warp;
-  if (r >= count * qg) return;
+  if (r >= count * qg || (a.tc_min_rows && count * qg >= a.tc_min_rows)) return;  // (a long device count is the tensor-core pass's work)
   const int i = r / qg, hq = kh * qg + (r - i * qg), pos = n0 + i, own = pos / G;
   const size_t eh = (size_t)bh * G * D, ih = (size_t)bh * a.count * D;
   {

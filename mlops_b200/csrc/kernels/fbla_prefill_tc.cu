@@ -32,14 +32,6 @@ extern "C" int fbla_k_attend_tc_status(void) {
   return v;
 }
 
-#ifdef FBLA_PF_TIMING
-extern "C" void fbla_k_attend_tc_prof(unsigned long long *out) {
-  unsigned long long zero[64] = {0};
-  cudaMemcpyFromSymbol(out, fbla::tc::g_prof, sizeof(zero));
-  cudaMemcpyToSymbol(fbla::tc::g_prof, zero, sizeof(zero));
-}
-#endif
-
 extern "C" cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStream_t stream) {
   using namespace fbla::tc;
   const int qg = a->q_heads / a->kv_heads;
@@ -59,20 +51,33 @@ extern "C" cudaError_t fbla_k_attend_tc_launch(const fbla_k_prefill *a, cudaStre
   return cudaGetLastError();
 }
 
-extern "C" cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream) {
+extern "C" int fbla_k_attend_plan(const fbla_k_prefill *a, fbla_k_prefill args[2], int tensor[2]) {
   static const bool rows_only = [] { const char *e = getenv("MLOPS_FBLA_PREFILL"); return e && !strcmp(e, "rows"); }();
-  const int rows = a->count * (a->q_heads / a->kv_heads);
-  return rows_only || rows < FBLA_K_TC_MIN_ROWS ? fbla_k_attend_rows_launch(a, stream) : fbla_k_attend_tc_launch(a, stream);
+  const int rows = a->count * (a->q_heads / a->kv_heads);  // (with a device count: the ceiling)
+  args[0] = *a;
+  args[0].tc_min_rows = 0;
+  if (rows_only || rows < FBLA_K_TC_MIN_ROWS) { tensor[0] = 0; return 1; }
+  tensor[0] = 1;
+  if (!a->dcount) return 1;
+  args[0].tc_min_rows = FBLA_K_TC_MIN_ROWS;
+  args[1] = args[0];
+  tensor[1] = 0;
+  return 2;
 }
 
-extern "C" cudaError_t fbla_k_attend_pass(const fbla_k_prefill *a, fbla_k_pass *info, int *tensor_cores) {
+extern "C" cudaError_t fbla_k_attend_launch(const fbla_k_prefill *a, cudaStream_t stream) {
+  fbla_k_prefill args[2];
+  int tensor[2];
+  const int n = fbla_k_attend_plan(a, args, tensor);
+  cudaError_t e = cudaSuccess;
+  for (int i = 0; i < n && e == cudaSuccess; ++i) e = tensor[i] ? fbla_k_attend_tc_launch(&args[i], stream) : fbla_k_attend_rows_launch(&args[i], stream);
+  return e;
+}
+
+extern "C" cudaError_t fbla_k_attend_tc_pass(const fbla_k_prefill *a, fbla_k_pass *info) {
   using namespace fbla::tc;
   const int qg = a->q_heads / a->kv_heads, rows = a->count * qg, heads = a->batch * a->kv_heads;
-  *tensor_cores = rows >= FBLA_K_TC_MIN_ROWS;
-  if (*tensor_cores) {
-    const size_t smem = sizeof(Smem) + 1024;
-    if (a->cb == 3) return pass_of(attend_tc_kernel<3, 3>, (rows + CTA_ROWS - 1) / CTA_ROWS, heads, THREADS, smem, "fbla::tc::attend_tc_item<3, 3>", info);
-    return pass_of(attend_tc_kernel<4, 2>, (rows + CTA_ROWS - 1) / CTA_ROWS, heads, THREADS, smem, "fbla::tc::attend_tc_item<4, 2>", info);
-  }
-  return fbla_k_attend_rows_pass(a, info);
+  const size_t smem = sizeof(Smem) + 1024;
+  if (a->cb == 3) return pass_of(attend_tc_kernel<3, 3>, (rows + CTA_ROWS - 1) / CTA_ROWS, heads, THREADS, smem, "fbla::tc::attend_tc_item<3, 3>", info);
+  return pass_of(attend_tc_kernel<4, 2>, (rows + CTA_ROWS - 1) / CTA_ROWS, heads, THREADS, smem, "fbla::tc::attend_tc_item<4, 2>", info);
 }

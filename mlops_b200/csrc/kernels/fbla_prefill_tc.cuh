@@ -26,7 +26,7 @@
 // Every wait is bounded: on a timeout the thread raises a flag, everybody drains, tensor memory is freed, the kernel
 // returns and the host sees fbla_k_attend_tc_status() != 0.
 #pragma once
-#include "fbla_device.cuh"
+#include "fbla_tc.cuh"
 #include "fbla_kernels.h"
 #include <cuda_fp16.h>
 
@@ -48,17 +48,6 @@ constexpr uint32_t WAIT_LIMIT = 1u << 18;
 
 __device__ int g_status = 0;  // nonzero: a bounded wait gave up in some launch since the last read
 
-#ifdef FBLA_PF_TIMING  // tuning only: cycles per role and section, summed over CTAs (lane 0 of one warp per role)
-__device__ unsigned long long g_prof[64];  // 4 roles x 16 slots
-#define PF_DECL long long pf_prev = clock64(); unsigned long long pf_acc[16] = {0};
-#define PF_MARK(slot) { const long long pf_t = clock64(); pf_acc[slot] += pf_t - pf_prev; pf_prev = pf_t; }
-#define PF_FLUSH(role) { for (int pf_i = 0; pf_i < 16; ++pf_i) atomicAdd(&g_prof[16 * (role) + pf_i], pf_acc[pf_i]); }
-#else
-#define PF_DECL
-#define PF_MARK(slot)
-#define PF_FLUSH(role) {}
-#endif
-
 struct __align__(1024) Smem {
   uint8_t q[2][TILE];   // Qop of BF16 passes: the rows' q, BF16
   uint8_t qp[2][TILE];  // Qop of closed passes (qhat, FP16), then P' of the same pass
@@ -76,46 +65,8 @@ struct __align__(1024) Smem {
 
 static_assert(sizeof(Smem) + 1024 <= 232448, "operand tiles exceed the shared memory of an SM");
 
-// ---- tcgen05 wrappers ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint64_t smem_desc(const void *tile_base, int slab, int kstep) {  // K-major, 128-byte swizzle
-  const uint32_t addr = smem_u32(tile_base) + slab * SLAB + kstep * 32;
-  return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-constexpr uint32_t IDESC_F16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);           // D FP32, A / B FP16, M 128, N 128
-constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);                                // A / B BF16
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, bool accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\ttcgen05.wait::ld.sync.aligned;"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
-                 "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-                 "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
-                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-                 "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// bounded wait (each poll may suspend up to ~2 us in hardware) that also gives up when some thread has raised the abort flag
-__device__ __forceinline__ bool try_wait_hint(uint64_t *bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(2000u) : "memory");
-  return ok != 0;
-}
+// ---- operand descriptors of this kernel's tiles ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t smem_desc(const void *tile_base, int slab, int kstep) { return smem_desc_at(tile_base, slab * SLAB + kstep * 32); }
 __device__ __forceinline__ bool wait(Smem &sm, uint64_t *bar, uint32_t parity) {
   if (try_wait_hint(bar, parity)) return true;
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
@@ -137,19 +88,6 @@ __device__ __forceinline__ uint8_t *chunk_at(uint8_t *tile, int r, int k0) {
 }
 
 // ---- record unpacking (the slot maps of include/mlops_fbla.h) --------------------------------------------------------------
-template <int BITS> __device__ __forceinline__ uint32_t slot_value(const uint32_t *W, int s) {  // 4 codes, one per byte, unscaled
-  if (BITS == 4) return s < 8 ? W[s] & 0x0f0f0f0fu : (W[s - 8] >> 4) & 0x0f0f0f0fu;
-  if (BITS == 2) return (W[s & 3] >> (2 * (s >> 2))) & 0x03030303u;
-  if (s < 6) return W[s] & 0x07070707u;
-  if (s < 12) return (W[s - 6] >> 3) & 0x07070707u;
-  const int r = s - 12;
-  return ((W[r] >> 6) & 0x03030303u) | ((W[4 + (r >> 1)] >> (4 + (r & 1))) & 0x04040404u);
-}
-__host__ __device__ constexpr int v_slot_of(int bits, int cc, int quad) {
-  return bits == 4 ? (cc < 2 ? 2 * quad + cc : 8 + 2 * quad + (cc - 2))
-       : bits == 2 ? 4 * cc + quad
-       : cc == 0 ? quad : cc == 1 ? 6 + quad : cc == 2 ? (quad < 2 ? 4 + quad : 8 + quad) : 12 + quad;
-}
 template <int BITS> __device__ __forceinline__ void lane_words(const uint8_t *rec, int tensor, int lane, uint32_t *W) {
 #pragma unroll
   for (int w = 0; w < 2 * BITS; ++w) W[w] = lds32(rec + word_offset(BITS, tensor, lane, w));
@@ -172,16 +110,10 @@ __device__ __forceinline__ uint32_t hfma2_bits(uint32_t code2, __half2 step, __h
   return *reinterpret_cast<const uint32_t *>(&r);
 }
 __device__ __forceinline__ float2 bf2(uint32_t w) { return make_float2(bf_lo(w), bf_hi(w)); }
-// pairs of FP32 operations: the packed FP32x2 instructions of sm_100 (FBLA_PF_SCALAR, tuning only: scalar instructions)
-#ifndef FBLA_PF_SCALAR
+// pairs of FP32 operations: the packed FP32x2 instructions of sm_100
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-#else
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
-#endif
 
 template <int CB, int FB>
 __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t *smem_raw) {
@@ -194,7 +126,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   const int count = a.dcount ? FBLA_POS::ro(a.dcount) : a.count, n1 = n0 + count;
   // the last tiles attend to the most groups: they are taken first, so that the grid's tail is made of short CTAs
   const int rows = count * qg, r0 = (FBLA_POS::nx() - 1 - FBLA_POS::x()) * CTA_ROWS;
-  if (r0 >= rows) return;  // (CTA-uniform)
+  if (r0 >= rows || rows < a.tc_min_rows) return;  // (CTA-uniform; a short device count is the warp-per-row pass's work)
   const int last_row = min(r0 + CTA_ROWS, rows) - 1;
   const int own_min = (n0 + r0 / qg) / G, own_max = (n0 + last_row / qg) / G;
   // passes: closed groups 1 .. own_max - 1, then the BF16 groups: 0 and the rows' own groups
@@ -212,8 +144,9 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     mbar_init_fence();
   }
   if (warp == ISSUER_WARP) {  // all 512 columns of tensor memory: S of tile x at 128 x, O at 256 + 128 x
+    // (the allocation permit is kept: an executor may run further tensor-core items on this CTA, and a CTA that has given
+    // its permit up may not allocate again)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(512) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -240,7 +173,6 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       };
       if (n_closed > 0) { fetch(1); fetch_meta(0); }
       if (n_closed > 1) fetch_meta(1);
-      PF_DECL
       for (int n = 0; n < n_pass; ++n) {
         bool closed;
         pass_group(n, closed);
@@ -248,50 +180,40 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
         // Both tiles' S first, then both tiles' O: the tiles run in step (holding tile 1 back by half a pass, so that one
         // tile quantises while the other exponentiates, measured slower: each tile then waits for the other's operands)
         bool ok = wait(sm, &sm.bar_k, ph);
-        PF_MARK(0)
         for (int x = 0; x < 2 && ok; ++x) {
           if (!(ok = wait(sm, &sm.bar_q[x], ph))) break;
-          PF_MARK(1 + x)
           tc_fence_after();
           const uint8_t *qop = closed ? sm.qp[x] : sm.q[x];
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) mma_f16(tmem + 128 * x, smem_desc(qop, kk >> 2, kk & 3), smem_desc(sm.k, kk >> 2, kk & 3), idesc, kk > 0);
           mma_commit(&sm.bar_s[x]);
         }
-        PF_MARK(3)
         if (!ok || !wait(sm, &sm.bar_v, ph)) break;
-        PF_MARK(4)
         if (n + 1 < n_closed) fetch(2 + n);  // the raw buffer has been consumed: the next closed group's records
         if (n + 2 < n_closed) fetch_meta(n + 2);  // (this pass's metadata has been consumed too)
         for (int x = 0; x < 2 && ok; ++x) {
           if (!(ok = wait(sm, &sm.bar_p[x], ph))) break;
-          PF_MARK(5 + x)
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             mma_f16(tmem + 256 + 128 * x, smem_desc(sm.qp[x], kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
           mma_commit(&sm.bar_o[x]);
         }
-        PF_MARK(7)
         if (!ok) break;
       }
-      PF_FLUSH(0)
     }
   } else if (warp >= PRODUCER_WARP0) {
     // ================= operand producers =================
     const int pt = tid - 32 * PRODUCER_WARP0;  // 0 .. PT - 1
     const int l = pt & 31;
     int raw_uses = 0;
-    PF_DECL
     for (int n = 0; n < n_pass; ++n) {
       bool closed;
       const int g = pass_group(n, closed);
       const uint32_t prev = (n - 1) & 1;
       // ---- Kop (free once both tiles' S of the previous pass are complete; the row threads are then done with the previous
       // pass's steps and bases too) ----
-      PF_MARK(1)
       if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
-      PF_MARK(2)
       if (closed) {
         if (!wait(sm, &sm.bar_meta[n & 1], (uint32_t)(n >> 1) & 1u)) break;
         {  // K bases and steps as FP32 for the row threads: long before they ask for them
@@ -303,7 +225,6 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
         }
         mbar_arrive(&sm.bar_mf);
         if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
-        PF_MARK(0)
       }
       if (closed) {
         // (record j, lane l): token 16 j + l % 16, channels 64 (l / 16) + 4 s + byte: one 128-byte row of slab l / 16
@@ -329,10 +250,8 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       }
       fence_async_smem();
       mbar_arrive(&sm.bar_k);
-      PF_MARK(3)
       // ---- V' (free once both tiles' O products of the previous pass are complete) ----
       if (n > 0 && (!wait(sm, &sm.bar_o[0], prev) || !wait(sm, &sm.bar_o[1], prev))) break;
-      PF_MARK(4)
       if (closed) {
         // (record j, lane l): channels 4 l + cc, tokens 16 j + 4 quad + byte, value base + step * code in FP16 arithmetic
         const uint4 vm = lds128(sm.meta[n & 1] + 512 + 16 * l);
@@ -370,9 +289,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       }
       fence_async_smem();
       mbar_arrive(&sm.bar_v);
-      PF_MARK(5)
     }
-    if (pt == 0) PF_FLUSH(1)
   } else {
     // ================= row threads: qhat, softmax, P', output =================
     // Softmax: two threads per row (warps w and w + 8 share a tensor-memory lane quadrant): thread hf owns tokens
@@ -415,19 +332,15 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     const uint32_t tmem_s = tmem + 128 * X + 64 * hf + lane_base, tmem_o = tmem + 256 + 128 * X + 64 * hf + lane_base;
     int mf_uses = 0;
     bool ok = true;
-    PF_DECL
     for (int n = 0; n < n_pass; ++n) {
       bool closed;
       const int g = pass_group(n, closed);
       const bool include = valid && (closed ? g < own : (g == 0 || g == own));
       const bool any = __any_sync(FULL, include);
-      PF_MARK(0)
       // the previous pass's O product has read P' (the buffer qhat goes to) and O is stable
       if (n > 0) ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n - 1) & 1));
-      PF_MARK(1)
       if (closed) {
         ok &= __all_sync(FULL, wait(sm, &sm.bar_mf, mf_uses++ & 1));
-        PF_MARK(2)
         if (g < tile_own) {
           // qhat for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r) written as FP16; four rows per batch, with
           // every load ahead of the arithmetic and every store behind it, so that the rows' dependency chains overlap
@@ -497,12 +410,9 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           }
         }
       }
-      PF_MARK(3)
       fence_async_smem();
       mbar_arrive(&sm.bar_q[X]);
-      PF_MARK(6)
       ok &= __all_sync(FULL, wait(sm, &sm.bar_s[X], n & 1));
-      PF_MARK(4)
       tc_fence_after();
       // softmax of the row over the pass's 128 tokens, by 16-token blocks; P' = fp16(2^(m_block - m_row) p)
       const int lim = (include ? (closed ? G : pos - g * G) : -1) - 64 * hf;  // this thread's tokens 0 .. lim are attended
@@ -537,7 +447,6 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       } else {
         const float2 e = *reinterpret_cast<const float2 *>(&sm.ex2[X][r][0]);
         const float mp = fmaxf(e.x, e.y);
-        PF_MARK(10)
         // the row's running maximum moves only when a block exceeds it by more than 2^8 (rare): its sums and its O row in
         // tensor memory are rescaled. Tensor-memory accesses are warp-wide, so the whole warp takes part (rows that do
         // not move scale by 1); both threads of a row decide alike and each rescales its own 64 columns.
@@ -556,7 +465,6 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           }
           if (need) { l_run *= al; m_run = mp; }
         }
-        PF_MARK(11)
         // sweep 2: the integer P blocks times their weights
         const float2 mul = splat(mul1), add = splat(add1), c255 = splat(255.f), mg = splat(MAGICF), ng = splat(-MAGICF);
         float2 lacc = make_float2(0.f, 0.f);
@@ -597,13 +505,10 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
         }
         l_run += lacc.x + lacc.y;
       }
-      PF_MARK(5)
       fence_async_smem();
       tc_fence_before();
       mbar_arrive(&sm.bar_p[X]);
-      PF_MARK(7)
     }
-    if (lane == 0 && hf == 0 && (warp & 3) == 0) PF_FLUSH(2 + X)
     ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n_pass - 1) & 1));
     tc_fence_after();
     pair_sync();  // (the partner has read the last pass's exchange)
@@ -624,10 +529,11 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           stage[8 * ((l >> 1) ^ (r & 15)) + 4 * (l & 1) + cc] = f32_to_bf16(__uint_as_float(o[l]) * inv);
       }
       pair_sync();
-      if (valid && ok) {
+      if (valid) {  // (after a wait that gave up: NaN, so that the failure shows in the caller's data)
         uint16_t *orow = a.out + (size_t)(b * a.q_heads + hq) * a.out_hs + (size_t)i * a.out_ts;
+        const uint4 nan4 = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
 #pragma unroll
-        for (int c = 8 * hf; c < 8 * hf + 8; ++c) reinterpret_cast<uint4 *>(orow)[c] = reinterpret_cast<const uint4 *>(stage)[c ^ (r & 15)];
+        for (int c = 8 * hf; c < 8 * hf + 8; ++c) reinterpret_cast<uint4 *>(orow)[c] = ok ? reinterpret_cast<const uint4 *>(stage)[c ^ (r & 15)] : nan4;
       }
     }
   }
@@ -636,6 +542,10 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   if (warp == ISSUER_WARP) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+  if (tid == 0) {  // no live barrier object is left behind: an executor may run another item on this CTA next
+    mbar_inval(&sm.bar_raw); mbar_inval(&sm.bar_meta[0]); mbar_inval(&sm.bar_meta[1]); mbar_inval(&sm.bar_mf); mbar_inval(&sm.bar_k); mbar_inval(&sm.bar_v);
+    for (int x = 0; x < 2; ++x) { mbar_inval(&sm.bar_q[x]); mbar_inval(&sm.bar_s[x]); mbar_inval(&sm.bar_p[x]); mbar_inval(&sm.bar_o[x]); }
   }
 }
 

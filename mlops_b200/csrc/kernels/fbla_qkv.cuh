@@ -30,33 +30,35 @@ __device__ __forceinline__ float2 cos_sin_at(int pos, float4 f, float att) {
   return make_float2(__fmul_rn(c, att), __fmul_rn(s, att));
 }
 
-// one head: x (128 BF16), optional norm weights w; cs: the 64 pairs' (cos, sin); returns the lane's two output words
-// (elements 2 l, 2 l + 1 and 64 + 2 l, 65 + 2 l)
+// One head vector through the optional RMSNorm and the rotation. A lane owns the two rotation pairs (2 l, 64 + 2 l) and
+// (2 l + 1, 65 + 2 l): `first` = elements 2 l, 2 l + 1, `second` = elements 64 + 2 l, 65 + 2 l, each pair of BF16 in one
+// word. cs[i] = (cos, sin) of pair i. Returns the lane's two output words in the same arrangement.
+struct LaneQuad { float a0, a1, b0, b1; };  // a: elements 2 l, 2 l + 1; b: their partners 64 further on
+__device__ __forceinline__ LaneQuad unpack_quad(uint32_t first, uint32_t second) { return LaneQuad{bf_lo(first), bf_hi(first), bf_lo(second), bf_hi(second)}; }
+__device__ __forceinline__ float round_through_bf16(float x) { return bf16_to_f32(f32_to_bf16(x)); }
+
 template <bool NORM>
 __device__ __forceinline__ uint2 norm_rotate(const uint16_t *x, const uint16_t *w, float eps, const float2 *cs, int lane) {
-  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t *>(x) + lane), hi = __ldg(reinterpret_cast<const uint32_t *>(x + 64) + lane);
-  float v[4] = {bf_lo(lo), bf_hi(lo), bf_lo(hi), bf_hi(hi)};
+  const uint32_t *xw = reinterpret_cast<const uint32_t *>(x);
+  LaneQuad v = unpack_quad(__ldg(xw + lane), __ldg(xw + 32 + lane));
   if (NORM) {
-    float s = __fmul_rn(v[0], v[0]);
-    s = __fmaf_rn(v[1], v[1], s);
-    s = __fmaf_rn(v[2], v[2], s);
-    s = __fmaf_rn(v[3], v[3], s);
-#pragma unroll
-    for (int o = 16; o; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(FULL, s, o));
-    const float r = __frsqrt_rn(__fadd_rn(__fmul_rn(s, 1.f / D), eps));
-    const uint32_t wl = __ldg(reinterpret_cast<const uint32_t *>(w) + lane), wh = __ldg(reinterpret_cast<const uint32_t *>(w + 64) + lane);
-    const float wv[4] = {bf_lo(wl), bf_hi(wl), bf_lo(wh), bf_hi(wh)};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = bf16_to_f32(f32_to_bf16(__fmul_rn(bf16_to_f32(f32_to_bf16(__fmul_rn(v[i], r))), wv[i])));
+    // sum of squares: the lane's four terms chained through FMAs in element order, then the xor butterfly from 16 down
+    float sq = __fmaf_rn(v.b1, v.b1, __fmaf_rn(v.b0, v.b0, __fmaf_rn(v.a1, v.a1, __fmul_rn(v.a0, v.a0))));
+    for (int stride = 16; stride > 0; stride >>= 1) sq = __fadd_rn(sq, __shfl_xor_sync(FULL, sq, stride));
+    const float inv_rms = __frsqrt_rn(__fadd_rn(__fmul_rn(sq, 1.f / D), eps));
+    const uint32_t *ww = reinterpret_cast<const uint32_t *>(w);
+    const LaneQuad g = unpack_quad(__ldg(ww + lane), __ldg(ww + 32 + lane));
+    // two roundings to BF16, as a BF16 norm layer gives: the normalised value, then its product with the weight
+    v.a0 = round_through_bf16(__fmul_rn(round_through_bf16(__fmul_rn(v.a0, inv_rms)), g.a0));
+    v.a1 = round_through_bf16(__fmul_rn(round_through_bf16(__fmul_rn(v.a1, inv_rms)), g.a1));
+    v.b0 = round_through_bf16(__fmul_rn(round_through_bf16(__fmul_rn(v.b0, inv_rms)), g.b0));
+    v.b1 = round_through_bf16(__fmul_rn(round_through_bf16(__fmul_rn(v.b1, inv_rms)), g.b1));
   }
-  uint16_t y[4];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float2 f = cs[2 * lane + i];
-    y[i] = f32_to_bf16(__fmaf_rn(v[i], f.x, __fmul_rn(-v[2 + i], f.y)));
-    y[2 + i] = f32_to_bf16(__fmaf_rn(v[2 + i], f.x, __fmul_rn(v[i], f.y)));
-  }
-  return make_uint2(y[0] | (uint32_t)y[1] << 16, y[2] | (uint32_t)y[3] << 16);
+  // (a, b) -> (a cos - b sin, b cos + a sin): the sine product rounded first, then one FMA, then BF16
+  const float2 p0 = cs[2 * lane], p1 = cs[2 * lane + 1];
+  const uint32_t ra0 = f32_to_bf16(__fmaf_rn(v.a0, p0.x, __fmul_rn(-v.b0, p0.y))), rb0 = f32_to_bf16(__fmaf_rn(v.b0, p0.x, __fmul_rn(v.a0, p0.y)));
+  const uint32_t ra1 = f32_to_bf16(__fmaf_rn(v.a1, p1.x, __fmul_rn(-v.b1, p1.y))), rb1 = f32_to_bf16(__fmaf_rn(v.b1, p1.x, __fmul_rn(v.a1, p1.y)));
+  return make_uint2(ra0 | ra1 << 16, rb0 | rb1 << 16);
 }
 
 // ---- one token per sequence: q to q_out, k and v into the windows (the group the position closes has been quantized by

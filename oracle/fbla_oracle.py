@@ -49,6 +49,11 @@ def threads():
     return lib().fbla_oracle_threads()
 
 
+def set_threads(n):
+    """Let the oracle's parallel loops use n threads (overrides an inherited OMP_NUM_THREADS)."""
+    lib().fbla_oracle_set_threads(ctypes.c_int(int(n)))
+
+
 def quantize_group(x_bits):
     """x_bits [n, 128] uint16 (BF16) -> base, step [128] uint16, code [n, 128] uint8."""
     x = np.ascontiguousarray(x_bits, dtype=np.uint16)

@@ -51,10 +51,16 @@ __device__ __forceinline__ void position(int item, int nx, int ny, int nz) {
 '''
 
 
-def kernel_source(name, threads, statements):
-    """one executor kernel: CTA i runs item i of the pass"""
-    return (f'extern "C" __global__ void __launch_bounds__({threads}, 1) {name}(const unsigned char *args) {{\n'
-            f'  extern __shared__ __align__(16) unsigned char sm[];\n  const int item = blockIdx.x;\n  {statements}\n}}\n')
+def kernel_source(name, threads, statements, items=None):
+    """One executor kernel. items None: CTA i runs item i of the pass. items = the pass's item count: a persistent loop,
+    each CTA of a smaller grid walks items blockIdx.x, blockIdx.x + gridDim.x, ... back to back (as the reference's
+    emulation runs fewer CTAs than items, attention/fbla/tests/test_items.cu:115-181), so whatever an item leaves behind
+    in shared memory, barriers or tensor memory meets the next item on the same CTA."""
+    head = (f'extern "C" __global__ void __launch_bounds__({threads}, 1) {name}(const unsigned char *args) {{\n'
+            f'  extern __shared__ __align__(16) unsigned char sm[];\n')
+    if items is None:
+        return head + f'  const int item = blockIdx.x;\n  {statements}\n}}\n'
+    return head + f'  for (int item = blockIdx.x; item < {items}; item += gridDim.x) {{\n    {statements}\n    __syncthreads();\n  }}\n}}\n'
 
 
 def compile_program(source, want_cubin=True):
@@ -90,13 +96,15 @@ def item_call(lib, p):
     return buf.value.decode()
 
 
-def run_plan(lib, passes, n, stream):
+def run_plan(lib, passes, n, stream, ctas=None):
     """Compiles one kernel per pass and launches them in order on `stream` (a CUDA stream handle): an executor whose only
-    dependency rule is 'every item of a pass after every item of the pass before' (stream order)."""
+    dependency rule is 'every item of a pass after every item of the pass before' (stream order). ctas: run every pass
+    as a persistent loop on that many CTAs instead of one CTA per item."""
     import numpy as np
     import torch
     from cuda.bindings import driver
-    src = POLICY + "".join(kernel_source(f"pass_{i}", passes[i].threads, item_call(lib, passes[i])) for i in range(n))
+    src = POLICY + "".join(kernel_source(f"pass_{i}", passes[i].threads, item_call(lib, passes[i]), None if ctas is None else passes[i].items)
+                           for i in range(n))
     cubin = compile_program(src)
     err, module = driver.cuModuleLoadData(cubin)
     assert err == driver.CUresult.CUDA_SUCCESS, err
@@ -112,7 +120,7 @@ def run_plan(lib, passes, n, stream):
         keep.append(blob)
         arg = np.array([blob.data_ptr()], dtype=np.uint64)
         params = np.array([arg.ctypes.data], dtype=np.uint64)
-        err, = driver.cuLaunchKernel(fn, p.items, 1, 1, p.threads, 1, 1, p.smem_bytes, stream, params.ctypes.data, 0)
+        err, = driver.cuLaunchKernel(fn, p.items if ctas is None else min(ctas, p.items), 1, 1, p.threads, 1, 1, p.smem_bytes, stream, params.ctypes.data, 0)
         assert err == driver.CUresult.CUDA_SUCCESS, err
     torch.cuda.synchronize()
     driver.cuModuleUnload(module)

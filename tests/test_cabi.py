@@ -79,10 +79,10 @@ def test_validation_without_a_device(C):
     st = lib.mlops_fbla_decode(ctypes.byref(cfg(C, tau=-1.0)), 0x1000, ctypes.byref(cache), 0x1000, 0x1000, 1 << 30, None)
     assert st == C.INVALID_VALUE and "tau" in C.last_error()
     st = lib.mlops_fbla_decode(ctypes.byref(cfg(C)), 0x1008, ctypes.byref(cache), 0x1000, 0x1000, 1 << 30, None)
-    assert st == C.INVALID_VALUE and "aligned" in C.last_error()
+    assert st == C.INVALID_VALUE and "boundar" in C.last_error()
     missing = C.Cache(0x1000, None, *([0x1000] * 5), None)
     st = lib.mlops_fbla_decode(ctypes.byref(cfg(C)), 0x1000, ctypes.byref(missing), 0x1000, 0x1000, 1 << 30, None)
-    assert st == C.INVALID_VALUE and "cache pointer" in C.last_error()
+    assert st == C.INVALID_VALUE and "seven arrays" in C.last_error()
     st = lib.mlops_fbla_decode(ctypes.byref(cfg(C, length_stride=1)), 0x1000, ctypes.byref(cache), 0x1000, 0x1000, 1 << 30, None)
     assert st == C.INVALID_VALUE
     # prefill

@@ -56,9 +56,12 @@ def _write_ranges(lib, passes, n, arg):
     return out
 
 
-@pytest.mark.parametrize("mode,QH,KH", [("4+2", 8, 2), ("3+3", 4, 4)])
-def test_decode_plan_equals_decode_at(ours, mode, QH, KH):
-    B, N, cap = 2, 3000, 4096
+@pytest.mark.parametrize("mode,QH,KH,N,cap,ctas", [("4+2", 8, 2, 3000, 4096, None), ("3+3", 4, 4, 3000, 4096, None),
+                                                     # capacities beyond ~4 700 tokens take the coarse kernel with the fixed warp split;
+                                                     # ctas = 3: every pass as a persistent loop of three CTAs walking its items back to back
+                                                     ("4+2", 8, 2, 9000, 16384, None), ("3+3", 8, 2, 9000, 16384, 3), ("4+2", 4, 4, 3000, 4096, 3)])
+def test_decode_plan_equals_decode_at(ours, mode, QH, KH, N, cap, ctas):
+    B = 2
     q, k, v = datagen.baseline_case(41, B, QH, KH, N)
     qd = gu.bf16_tensor(q)
     c = ours.encode(gu.bf16_tensor(k), gu.bf16_tensor(v), mode, capacity=cap)
@@ -79,16 +82,18 @@ def test_decode_plan_equals_decode_at(ours, mode, QH, KH):
     assert lib.mlops_fbla_decode_at_items(ctypes.byref(cfg), vp(length.data_ptr()), vp(qd.data_ptr()), ctypes.byref(kc), vp(out.data_ptr()),
                                           vp(scratch.data_ptr()), ctypes.c_size_t(nbytes), 0, None, 0) == 4  # max = 0 only counts
     before = scratch.cpu().numpy().copy()
-    iu.run_plan(lib, passes, n, _stream())
+    iu.run_plan(lib, passes, n, _stream(), ctas)
     assert torch.equal(out, want), "the plan's items differ from mlops_fbla_decode_at"
     changed = scratch.cpu().numpy() != before
     _covered(changed, _write_ranges(lib, passes, n, "SCRATCH"), "decode scratch")
     _covered(np.ones(out.numel() * 2, bool), _write_ranges(lib, passes, n, "OUT"), "decode output")
 
 
-@pytest.mark.parametrize("mode,count", [("4+2", 300), ("3+3", 5)])
-def test_prefill_plan_equals_prefill_at(ours, mode, count):
-    """count 300: the tensor-core pass (TC); count 5: the warp-per-row pass (STREAM)"""
+@pytest.mark.parametrize("mode,count,ctas", [("4+2", 300, None), ("3+3", 5, None), ("3+3", 700, 3)])
+def test_prefill_plan_equals_prefill_at(ours, mode, count, ctas):
+    """count 300 / 700: the tensor-core pass (TC) -- with ctas = 3 as a persistent loop, so that one CTA runs several
+    tensor-core items back to back, each allocating and freeing tensor memory and its barriers; count 5: the
+    warp-per-row pass (STREAM)"""
     B, QH, KH, n0, cap = 1, 8, 2, 200, 1024
     max_count = count + 3
     q, k, v = datagen.uneven_case(43, B, QH, KH, n0 + count, q_rows=n0 + count)
@@ -104,14 +109,17 @@ def test_prefill_plan_equals_prefill_at(ours, mode, count):
     cfg = _cfg(b, QH)
     kc = ours._cache(b)
     lib, vp = ours.lib, ctypes.c_void_p
-    passes = (iu.Items * 3)()
+    passes = (iu.Items * 4)()
     n = lib.mlops_fbla_prefill_at_items(ctypes.byref(cfg), vp(length.data_ptr()), vp(cnt.data_ptr()), max_count, vp(qp.data_ptr()), vp(kp.data_ptr()),
-                                        vp(vp_.data_ptr()), ctypes.byref(kc), vp(out.data_ptr()), passes, 3)
-    assert n == 3, ours.error()
-    assert [passes[i].kind for i in range(3)] == [iu.KINDS["CLOSE"], iu.KINDS["TC" if count * (QH // KH) >= 64 else "STREAM"], iu.KINDS["FINISH"]]
+                                        vp(vp_.data_ptr()), ctypes.byref(kc), vp(out.data_ptr()), passes, 4)
+    # a count on the device whose ceiling reaches the tensor-core kernel: both attention passes are planned and the count
+    # decides on the device which of them works (the other returns at once)
+    kinds = ["CLOSE", "TC", "STREAM", "FINISH"] if max_count * (QH // KH) >= 64 else ["CLOSE", "STREAM", "FINISH"]
+    assert n == len(kinds), ours.error()
+    assert [passes[i].kind for i in range(n)] == [iu.KINDS[x] for x in kinds]
     as_bytes = lambda t: t.contiguous().view(torch.uint8).cpu().numpy().reshape(-1).copy()
     before = {key: as_bytes(b[key]) for key in ("coarse", "fine", "meta", "sink_k", "sink_v", "open_k", "open_v")}
-    iu.run_plan(lib, passes, n, _stream())
+    iu.run_plan(lib, passes, n, _stream(), ctas)
     assert torch.equal(out, want)
     a["tokens"] = b["tokens"] = n0 + count
     gu.assert_cache_equal(a, gu.cache_to_numpy(b), mode)

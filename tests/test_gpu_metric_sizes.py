@@ -1,0 +1,203 @@
+"""Parity at the sizes the headline metric and the BASELINE configurations name, through the C ABI, against the CPU
+oracle and against the reference's own CUDA library (oracle/_ref) on the same device buffers:
+
+  * decode batch 1, 32q / 8kv, 131 072 tokens, both formats (the metric's "128K ctx");
+  * the reference's own 262 144-token decode case (attention/fbla/tests/test_fbla.cu:1219: 4q / 2kv, tau 1e-4, seed 9);
+  * 1 048 576 tokens (configs[2]) through 8 emulated sequence shards against the single-cache decode;
+  * causal prefill batch 4 x 8 192, 32q / 8kv, 4+2 (configs[3]) at sampled positions of every sequence;
+  * mixed serving decode (configs[4]): batch 64, 32q / 8kv, 3+3, per-row device lengths drawn from [1 024, 65 536],
+    the cache laid out in whole 256-token pages (two group units per page) through head_stride / group_stride.
+
+Every case prints its measured distances, max|ours - oracle| / max|oracle| and max|ours - ref_gpu| / max|ref_gpu|."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import datagen
+from tests import gpu_util as gu
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ours():
+    assert os.path.exists(gu.OURS)
+    return gu.CLib(gu.OURS)
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return gu.CLib(gu.REF) if os.path.exists(gu.REF) else None
+
+
+def _f64(t):
+    return datagen.bf16_to_f32(gu.bits_of(t)).astype(np.float64)
+
+
+def _against_ref(out, ref_out, what):
+    a, b = _f64(out), _f64(ref_out)
+    rel = np.abs(a - b).max() / np.abs(b).max()
+    assert (np.abs(a - b) <= 2e-3 * np.abs(b).max() + gu.bf16_ulp(b)).all(), f"{what}: {rel:.3e} of max|ref_gpu|"
+    return rel
+
+
+@pytest.mark.parametrize("mode", ["3+3", "4+2"])
+def test_decode_128k_context(ours, ref, oracle, mode):
+    B, QH, KH, N = 1, 32, 8, 131072
+    q, k, v = datagen.baseline_case(1003, B, QH, KH, N, outliers=False)
+    qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
+    c = ours.encode(kd, vd, mode)
+    out = ours.decode(c, qd)
+    again = ours.decode(c, qd)
+    torch.cuda.synchronize()
+    assert torch.equal(out, again), "two decodes on poisoned scratches differ"
+    o = oracle.encode(k, v, mode)
+    gu.assert_cache_equal(c, o, f"128K {mode} cache")
+    rel = gu.check_close(gu.bits_of(out), oracle.decode(q, o), f"128K {mode} decode")
+    rel_ref = _against_ref(out, ref.decode(c, qd), f"128K {mode}") if ref is not None else float("nan")
+    print(f"\n[parity] decode B1 32q/8kv ctx131072 {mode}: vs oracle {rel:.2e}, vs ref_gpu {rel_ref:.2e}")
+
+
+@pytest.mark.parametrize("mode", ["3+3", "4+2"])
+def test_decode_262144_reference_case(ours, ref, oracle, mode):
+    B, QH, KH, N, tau = 1, 4, 2, 262144, 1e-4
+    q, k, v = datagen.uneven_case(9, B, QH, KH, N)
+    qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
+    c = ours.encode(kd, vd, mode)
+    out = ours.decode(c, qd, tau=tau)
+    torch.cuda.synchronize()
+    o = oracle.encode(k, v, mode)
+    gu.assert_cache_equal(c, o, f"256K {mode} cache")
+    rel = gu.check_close(gu.bits_of(out), oracle.decode(q, o, tau=tau), f"256K {mode} decode")
+    rel_ref = _against_ref(out, ref.decode(c, qd, tau=tau), f"256K {mode}") if ref is not None else float("nan")
+    print(f"\n[parity] decode B1 4q/2kv ctx262144 tau 1e-4 {mode}: vs oracle {rel:.2e}, vs ref_gpu {rel_ref:.2e}")
+
+
+def test_decode_1m_through_eight_shards(ours, ref):
+    """configs[2] at its largest: one 1 048 576-token sequence (3+3) held as 8 sequence shards -- here all on one GPU and
+    run one after the other, the two exchanges replaced by a concatenation and a sum -- against the decode of the same
+    tokens held in one cache, and against the reference's CUDA library on that cache."""
+    from mlops_b200.attention import sharded
+    QH, KH, N, world, mode = 32, 8, 1 << 20, 8, "3+3"
+    rng = np.random.default_rng(1005)
+    q = datagen.to_bf16_bits(rng.standard_normal((1, QH, 128), dtype=np.float32))
+    qd = gu.bf16_tensor(q)
+    whole = ours.empty(1, KH, N, mode)
+    plans = sharded.plan_shards(N, world)
+    shards, prev_first = [], None
+    # the sequence is generated and appended in the shards' own pieces (2 x 134 MB of BF16 each), never held whole on the host
+    pieces = []
+    for p in plans:
+        kk = datagen.to_bf16_bits(rng.standard_normal((1, KH, p.token_end - p.token_first, 128), dtype=np.float32))
+        vv = datagen.to_bf16_bits(rng.standard_normal((1, KH, p.token_end - p.token_first, 128), dtype=np.float32))
+        pieces.append((gu.bf16_tensor(kk), gu.bf16_tensor(vv)))
+    for i, p in enumerate(plans):
+        kd, vd = pieces[i]
+        ours.prefill(whole, kd, vd)
+        if p.extra:  # the first token of the next shard closes this shard's last group
+            kd = torch.cat([kd, pieces[i + 1][0][:, :, :1]], 2)
+            vd = torch.cat([vd, pieces[i + 1][1][:, :, :1]], 2)
+        shards.append(sharded.encode_shard(kd.contiguous(), vd.contiguous(), mode, p))
+    del pieces
+    rows = QH
+    masses = torch.cat([sharded.local_mass(qd, s).clone() for s in shards])
+    total = torch.empty(rows, dtype=torch.float32, device="cuda")
+    sharded.total_mass(masses, len(shards), rows, total)
+    partial = sum(sharded.local_partial(qd, s, total).clone() for s in shards)
+    out = sharded.combine(partial, qd)
+    single = ours.decode(whole, qd)
+    torch.cuda.synchronize()
+    rel = _against_ref(out, single, "1M: 8 shards against one cache")
+    rel_ref = _against_ref(single, ref.decode(whole, qd), "1M one cache") if ref is not None else float("nan")
+    print(f"\n[parity] decode B1 32q/8kv ctx1048576 3+3: 8 shards vs one cache {rel:.2e}, one cache vs ref_gpu {rel_ref:.2e}")
+
+
+def test_prefill_configs3_batch4(ours, ref, oracle):
+    B, QH, KH, S, mode = 4, 32, 8, 8192, "4+2"
+    q, k, v = datagen.baseline_case(1004, B, QH, KH, S, q_rows=S, outliers=True)
+    qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
+    c = ours.empty(B, KH, S, mode)
+    out = ours.prefill(c, kd, vd, qd)
+    torch.cuda.synchronize()
+    assert ctypes.CDLL(gu.OURS).fbla_k_attend_tc_status() == 0
+    o = oracle.encode(k, v, mode)
+    gu.assert_cache_equal(c, o, "configs[3] cache after the prefill")
+    step = 1171  # 7 positions per sequence through the oracle's float64 model of the reference's prefill
+    want = oracle.prefill(q, k, v, oracle.empty(B, KH, S, mode), pos_step=step)
+    worst = 0.0
+    for i in range(0, S, step):
+        worst = max(worst, gu.check_close(gu.bits_of(out)[:, :, i], want[:, :, i], f"configs[3] prefill position {i}"))
+    rel_ref = float("nan")
+    if ref is not None:
+        rc = ref.empty(B, KH, S, mode)
+        ro = ref.prefill(rc, kd, vd, qd)
+        torch.cuda.synchronize()
+        a, b = _f64(out), _f64(ro)
+        rel_ref = 0.0
+        for i in range(0, S, 97):  # per position: the output scale shrinks along the sequence
+            d, m = np.abs(a[:, :, i] - b[:, :, i]), np.abs(b[:, :, i]).max()
+            assert (d <= 2e-3 * m + gu.bf16_ulp(b[:, :, i])).all(), i
+            rel_ref = max(rel_ref, d.max() / m)
+    print(f"\n[parity] prefill B4 S8192 32q/8kv 4+2: vs oracle (sampled) {worst:.2e}, vs ref_gpu {rel_ref:.2e}")
+
+
+def serving_lengths(batch=64, seed=1005):
+    return np.random.default_rng(seed).integers(1024, 65536, size=batch, endpoint=True).astype(np.int32)
+
+
+def build_serving_cache(lib, lengths, KH, mode, page_tokens=256, seed=1005, keep=()):
+    """configs[4]'s cache: every row laid out for the same number of whole pages (the API addresses units affinely:
+    head_stride = groups per head, group_stride = 1, so a 256-token page is two consecutive group units), filled row by
+    row with seeded N(0,1) tokens up to the row's own length. keep: rows whose (k, v) bit patterns are returned."""
+    B = len(lengths)
+    cap = -(-int(lengths.max()) // page_tokens) * page_tokens
+    c = lib.empty(B, KH, cap, mode)
+    rng = np.random.default_rng(seed + 1)
+    kept = {}
+    for b, n in enumerate(lengths):
+        kk = datagen.to_bf16_bits(rng.standard_normal((1, KH, int(n), 128), dtype=np.float32))
+        vv = datagen.to_bf16_bits(rng.standard_normal((1, KH, int(n), 128), dtype=np.float32))
+        row = {key: (val[b:b + 1] if torch.is_tensor(val) else val) for key, val in c.items()}
+        row["batch"], row["tokens"] = 1, 0
+        lib.prefill(row, gu.bf16_tensor(kk), gu.bf16_tensor(vv))
+        if b in keep:
+            kept[b] = (kk, vv)
+    return c, cap, kept
+
+
+def test_serving_decode_configs4(ours, ref, oracle):
+    B, QH, KH, mode = 64, 32, 8, "3+3"
+    lengths = serving_lengths(B)
+    c, cap, kept = build_serving_cache(ours, lengths, KH, mode, keep=range(B))
+    q = datagen.to_bf16_bits(np.random.default_rng(77).standard_normal((B, QH, 128), dtype=np.float32))
+    qd = gu.bf16_tensor(q)
+    ld = torch.from_numpy(lengths).cuda()
+    out = ours.decode_at(c, qd, ld, length_stride=1)
+    again = ours.decode_at(c, qd, ld, length_stride=1)
+    torch.cuda.synchronize()
+    assert torch.equal(out, again)
+    # against the oracle: every row, each with its own cache and length (the acceptance rule of every decode test)
+    worst = 0.0
+    for b in range(B):
+        kk, vv = kept.pop(b)
+        o = oracle.encode(kk, vv, mode)
+        worst = max(worst, gu.check_close(gu.bits_of(out)[b:b + 1], oracle.decode(q[b:b + 1], o), f"configs[4] row {b} ({lengths[b]} tokens)"))
+    # Against the reference's CUDA library, same batched call. Both outputs are rounded to BF16 and a long row's values
+    # are small (|out| ~ 0.02 after averaging 50 000 tokens: one BF16 ulp is up to 4.6e-3 of the row's largest value), so
+    # two correctly rounded results of sums taken in different orders can sit two ulps of a small element apart; the
+    # reference's own test of batched rows allows 1/32 per element (attention/fbla/tests/test_fbla.cu:1136-1149).
+    rel_ref = float("nan")
+    if ref is not None:
+        ro = ref.decode_at(c, qd, ld, length_stride=1)
+        torch.cuda.synchronize()
+        a, r = _f64(out), _f64(ro)
+        rel_ref = 0.0
+        for b in range(B):  # per row: every row has its own output scale
+            d, m = np.abs(a[b] - r[b]), np.abs(r[b]).max()
+            assert (d <= 2e-3 * m + 2 * gu.bf16_ulp(r[b])).all(), (b, int(lengths[b]), d.max() / m)
+            rel_ref = max(rel_ref, d.max() / m)
+    print(f"\n[parity] serving decode B64 32q/8kv 3+3 lengths {lengths.min()}..{lengths.max()} (capacity {cap}): "
+          f"vs oracle (all rows) {worst:.2e}, vs ref_gpu (all rows) {rel_ref:.2e}")

@@ -61,7 +61,7 @@ def test_plan_builders_reject_bad_arguments_before_touching_a_device():
     assert b"capacity" in lib.mlops_fbla_last_error()
     # append_at: misaligned k
     assert lib.mlops_fbla_append_at_items(ctypes.byref(cfg), vp(0x1000), vp(0x1002), vp(0x1000), ctypes.byref(cache), passes, 4) == -1
-    assert b"aligned" in lib.mlops_fbla_last_error()
+    assert b"boundar" in lib.mlops_fbla_last_error()
     # qkv: a norm weight without its partner
     tok = gu.Token(0x1000, 0x1000, 0x1000, 1024, 768, 768, 0x1000, None, 1e-6, 0x1000, 0.0, 0x1000)
     assert lib.mlops_fbla_qkv_at_items(ctypes.byref(cfg), vp(0x1000), ctypes.byref(tok), ctypes.byref(cache), passes, 4) == -1
