@@ -159,7 +159,7 @@ def timed_blocks(D, step, steps, warmup, sample_clocks=False):
     if sampler:
         sampler.start()
     per_step, total = [], 0.0
-    while total < MIN_TIMED_S * 1000.0 and len(per_step) < 400:
+    while (not per_step or total < MIN_TIMED_S * 1000.0) and len(per_step) < 400:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         D.barrier()
         e0.record(stream)
@@ -528,7 +528,7 @@ def run_prefill(D, cfg, args):
 # ---- sequence split (configs[2]) ----------------------------------------------------------------------------------------------
 def run_seqsplit(D, cfg, args):
     """One sequence (batch 1, 32q/8kv, 3+3, plain N(0,1)) split over the ranks by whole groups; every decode step = two
-    local passes + two NCCL exchanges (row masses, partial sums)."""
+    local passes + two small exchanges (row masses, partial sums)."""
     import torch
     import torch.distributed as dist
     from mlops_b200.attention import sharded
@@ -549,20 +549,32 @@ def run_seqsplit(D, cfg, args):
     for _ in range(3):
         sharded.decode(qd, shard, group)
     torch.cuda.synchronize()
-    # the step's local segments as CUDA graphs, the two exchanges as ordinary NCCL calls between them
-    graph, launch = None, "eager"
+    # The whole step as ONE CUDA graph: the two exchanges are peer stores and bounded polls inside the step's own kernels
+    # (mlops_fbla_shard_step). If the peer-mapped mailboxes cannot be set up: the local segments as graphs around two
+    # eager NCCL exchanges.
+    runner, launch = None, "eager launches, NCCL exchanges"
     try:
-        graph = sharded.GraphedDecode(qd, shard, group)
-        graph()
+        runner = sharded.LinkedDecode(qd, shard, group)
+        runner()
         torch.cuda.synchronize()
-        launch = "cuda graphs around eager exchanges" if D.world > 1 else "cuda graphs"
+        if runner.status() != 0:
+            raise RuntimeError(f"link status {runner.status()}")
+        launch = "one CUDA graph; exchanges by peer stores and bounded polls (no NCCL on the path)"
     except Exception as exc:  # noqa: BLE001
-        graph = None
-        print(f"graph capture unavailable ({type(exc).__name__}: {exc}); timing eager launches", file=sys.stderr)
+        print(f"linked step unavailable ({type(exc).__name__}: {exc}); falling back to NCCL exchanges", file=sys.stderr)
+        runner = None
+        try:
+            runner = sharded.GraphedDecode(qd, shard, group)
+            runner()
+            torch.cuda.synchronize()
+            launch = "cuda graphs around eager NCCL exchanges"
+        except Exception as exc2:  # noqa: BLE001
+            runner = None
+            print(f"graph capture unavailable ({type(exc2).__name__}: {exc2}); timing eager launches", file=sys.stderr)
 
     def step(i):
-        if graph is not None:
-            graph()
+        if runner is not None:
+            runner()
         else:
             sharded.decode(qd, shard, group)
 
@@ -573,7 +585,7 @@ def run_seqsplit(D, cfg, args):
     ach = coarse / (ms * 1e-3) / 1e9
     return dict(metric=METRIC, value=1000.0 / ms, unit=UNIT, ms_per_step=ms, blocks=blocks,
                 config=dict(workload=cfg["name"], tokens=tokens, l2="cache larger than L2", launch=launch,
-                            sharding="the sequence's groups over %d GPUs; two NCCL exchanges per step (4 B and 528 B per row)" % D.world),
+                            sharding="the sequence's groups over %d GPUs; two exchanges per step (4 B and 528 B per row and rank)" % D.world),
                 roofline=dict(bound="hbm", achieved=ach, peak=peak * D.world, unit="GB/s", frac=ach / (peak * D.world), traffic=None, peak_kind=peak_kind,
                               algorithmic_bytes=coarse, note="coarse planes + metadata + BF16 windows only (refined share not counted)"),
                 dtype="u8")
@@ -637,7 +649,11 @@ def main():
     ap.add_argument("--workload", default="decode_128k", choices=sorted(WORKLOADS),
                     help="the line's workload; the default also measures the other configurations as sub-records")
     ap.add_argument("--no-subs", action="store_true", help="measure the named workload only (short runs under a profiler)")
+    ap.add_argument("--min-time", type=float, default=MIN_TIMED_S,
+                    help="seconds to time at least, in blocks of --steps steps (0: one block; for captures under a profiler)")
     args = ap.parse_args()
+    global MIN_TIMED_S
+    MIN_TIMED_S = args.min_time
     if args.impl == "reference":
         return run_reference(args)
     import torch

@@ -107,7 +107,11 @@ typedef struct {
 size_t mlops_fbla_decode_scratch_bytes(const mlops_fbla_config *cfg);
 
 /* One query per q head: q, output [batch, q_heads, 128] BF16. Work is enqueued on `stream`; no host
- * synchronisation. tokens <= 2^26. reference: mlops_fbla.h:98-100 */
+ * synchronisation. tokens <= 2^26. One call handles at most about 27 500 (virtual head, slice of 16 384 tokens) pairs --
+ * batch * kv_heads * max(1, q_heads / kv_heads / 4) * ceil(tokens / 16384) -- beyond which it returns
+ * MLOPS_FBLA_INVALID_VALUE ("split the batch"): a limit of this library, not of the reference.
+ * A device-side wait that gives up (not seen on a healthy device) turns the affected output rows into NaN.
+ * reference: mlops_fbla.h:98-100 */
 mlops_fbla_status mlops_fbla_decode(const mlops_fbla_config *cfg, const uint16_t *q,
                                     const mlops_fbla_cache *cache, uint16_t *output,
                                     void *scratch, size_t scratch_bytes, cudaStream_t stream);
@@ -120,8 +124,10 @@ size_t mlops_fbla_images_bytes(const mlops_fbla_config *cfg);
  * *out, or 0 (out untouched) for an invalid cfg. reference: mlops_fbla.h:117 */
 int mlops_fbla_cache_sizes(const mlops_fbla_config *cfg, mlops_fbla_sizes *out);
 
-/* Scratch of mlops_fbla_decode_at for cfg->capacity (> 0). per_head is accepted for source compatibility; this
- * library's scratch layout does not depend on it (any per_head >= 0 gives the same size). reference: mlops_fbla.h:122 */
+/* Scratch of mlops_fbla_decode_at for cfg->capacity (> 0). per_head (the reference: CTAs per head the partials are laid
+ * out for) only enlarges the answer here -- per_head further partial rows per head, so a larger per_head never gives a
+ * smaller scratch -- because this library's passes are persistent grids whose shape it does not change.
+ * reference: mlops_fbla.h:122 */
 size_t mlops_fbla_decode_scratch_bytes_for(const mlops_fbla_config *cfg, int per_head);
 
 /* Append `count` tokens k, v [batch, kv_heads, count, 128] BF16 to a cache holding cfg->tokens tokens: groups that
@@ -195,6 +201,10 @@ mlops_fbla_status mlops_fbla_decode_static(const mlops_fbla_config *cfg, const u
                                            uint16_t *output, cudaStream_t stream);
 size_t mlops_fbla_decode_static_scratch_limit(void);
 const char *mlops_fbla_decode_static_error(void);
+/* Optional, once per device at start-up (that device current), before the caller takes its memory arena and before any
+ * capture: makes the driver load this library's module on the device -- which is when the 32 MiB array and the kernels'
+ * code get their device memory -- and looks the array's address up. Launches nothing. No counterpart in the reference. */
+mlops_fbla_status mlops_fbla_decode_static_prepare(void);
 
 /* reference: mlops_fbla.h:185-186 */
 const char *mlops_fbla_status_string(mlops_fbla_status status);

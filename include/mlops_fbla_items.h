@@ -35,7 +35,8 @@ extern "C" {
 
 /* Pass kinds (values as the reference's). This library emits: CLOSE (one group the chunk may close, x, of KV head y),
  * STREAM (8 query rows of KV head y on CUDA cores: chunks of fewer than 64 rows), TC (256 query rows of KV head y on
- * tcgen05 tensor cores; no split pieces, no TC_MERGE pass, no TRANSCODE: this library keeps no images), FINISH (one KV
+ * tcgen05 tensor cores; no split pieces, no TC_MERGE pass, no TRANSCODE: this library keeps no images; a prefill plan whose
+ * count lives on the device and may reach 64 rows has a TC and a STREAM pass, of which the count activates one), FINISH (one KV
  * head's windows), COARSE / REFINE (CTA x of the persistent pass), SELECT (slice x of virtual head y), MERGE (one output
  * row), QKV (one (batch, KV head)), QKV_CHUNK (8 positions x of KV head y). */
 enum { MLOPS_FBLA_ITEM_CLOSE = 1, MLOPS_FBLA_ITEM_TRANSCODE, MLOPS_FBLA_ITEM_STREAM, MLOPS_FBLA_ITEM_TC,
@@ -84,8 +85,8 @@ int mlops_fbla_prefill_at_items(const mlops_fbla_config *cfg, const int *length,
                                 uint16_t *output, mlops_fbla_items *passes, int max);
 int mlops_fbla_append_at_items(const mlops_fbla_config *cfg, const int *length, const uint16_t *k, const uint16_t *v,
                                const mlops_fbla_cache *cache, mlops_fbla_items *passes, int max);
-/* per_head is accepted for compatibility and ignored: the passes always use the stream call's launch shape and scratch
- * layout (size the scratch with mlops_fbla_decode_scratch_bytes of a cfg whose tokens = capacity). */
+/* per_head does not change the plan: the passes always use the stream call's persistent launch shape and scratch layout
+ * (a scratch sized with mlops_fbla_decode_scratch_bytes_for(cfg, per_head) for any per_head >= 0 is large enough). */
 int mlops_fbla_decode_at_items(const mlops_fbla_config *cfg, const int *length, const uint16_t *q,
                                const mlops_fbla_cache *cache, uint16_t *output, void *scratch, size_t scratch_bytes,
                                int per_head, mlops_fbla_items *passes, int max);

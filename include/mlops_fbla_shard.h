@@ -44,6 +44,31 @@ mlops_fbla_status mlops_fbla_shard_mass(const mlops_fbla_config *cfg, const mlop
 mlops_fbla_status mlops_fbla_shard_partial(const mlops_fbla_config *cfg, const mlops_fbla_shard *shard, const uint16_t *q,
                                            const mlops_fbla_cache *cache, const float *row_mass_total, float *partial,
                                            void *scratch, size_t scratch_bytes, cudaStream_t stream);
+/* ---- the whole step with the exchanges done by the GPUs themselves ---------------------------------------------------------
+ * Instead of two host-launched collectives the ranks store their few KB straight into each other's memory (NVLink peer
+ * stores, one release flag per exchange, bounded acquire polls on the receiving side; mlops_b200/csrc/kernels/fbla_link.cu).
+ * Every rank owns a "mailbox" of mlops_fbla_shard_mailbox_bytes(world, batch * q_heads) bytes that all ranks can address
+ * (symmetric / peer-mapped memory: cudaIpc handles, cuMemMap, torch's symmetric memory ...), zero-filled ONCE before the
+ * first step and after that touched only by these calls. `mailboxes` lists the `world` base addresses as THIS rank sees
+ * them (mailboxes[rank] its own). mlops_fbla_shard_step enqueues one decode step -- nine kernel launches, no host
+ * synchronisation, no allocation; it can be captured in a CUDA graph -- and leaves the full output on every rank (the
+ * ranks add the shards' sums in rank order, so all hold the same bits). All ranks must make the same sequence of calls.
+ * A peer that never arrives: after wait_polls polls (64 ns apart; 0 = about a quarter of a second) the wait gives up, the
+ * output rows become NaN and mlops_fbla_shard_link_status reports which exchange and which rank (0 = healthy). */
+enum { MLOPS_FBLA_SHARD_MAX_RANKS = 8 };
+typedef struct {
+  int rank, world;          /* world <= MLOPS_FBLA_SHARD_MAX_RANKS */
+  void *const *mailboxes;   /* host array of `world` device pointers, 256-byte aligned */
+  unsigned wait_polls;
+} mlops_fbla_shard_link;
+
+size_t mlops_fbla_shard_mailbox_bytes(int world, int rows);
+mlops_fbla_status mlops_fbla_shard_step(const mlops_fbla_config *cfg, const mlops_fbla_shard *shard, const mlops_fbla_shard_link *link,
+                                        const uint16_t *q, const mlops_fbla_cache *cache, uint16_t *output, void *scratch,
+                                        size_t scratch_bytes, cudaStream_t stream);
+/* reads this rank's status word (synchronises with `stream` first): 0, or 1 / 2 (the mass / the sum exchange gave up) + 16 * rank */
+int mlops_fbla_shard_link_status(const mlops_fbla_shard_link *link, int rows, cudaStream_t stream);
+
 /* exchange A's arithmetic: gathered [shards][rows] local masses -> row_mass_total [rows] */
 mlops_fbla_status mlops_fbla_shard_total_mass(int shards, int rows, const float *gathered, float *row_mass_total, cudaStream_t stream);
 mlops_fbla_status mlops_fbla_shard_combine(int rows, const float *partial_sum, uint16_t *output, cudaStream_t stream);

@@ -35,6 +35,20 @@ _lib.mlops_fbla_shard_combine.restype = ctypes.c_int
 _lib.mlops_fbla_shard_combine.argtypes = [ctypes.c_int, _vp, _vp, _vp]
 
 
+class Link(ctypes.Structure):
+    """mlops_fbla_shard_link"""
+    _fields_ = [("rank", ctypes.c_int), ("world", ctypes.c_int), ("mailboxes", ctypes.POINTER(ctypes.c_void_p)), ("wait_polls", ctypes.c_uint)]
+
+
+_lib.mlops_fbla_shard_mailbox_bytes.restype = ctypes.c_size_t
+_lib.mlops_fbla_shard_mailbox_bytes.argtypes = [ctypes.c_int, ctypes.c_int]
+_lib.mlops_fbla_shard_step.restype = ctypes.c_int
+_lib.mlops_fbla_shard_step.argtypes = [ctypes.POINTER(_C.Config), ctypes.POINTER(Shard), ctypes.POINTER(Link), _vp, ctypes.POINTER(_C.Cache), _vp, _vp,
+                                       ctypes.c_size_t, _vp]
+_lib.mlops_fbla_shard_link_status.restype = ctypes.c_int
+_lib.mlops_fbla_shard_link_status.argtypes = [ctypes.POINTER(Link), ctypes.c_int, _vp]
+
+
 @dataclass
 class ShardPlan:
     rank: int
@@ -215,3 +229,79 @@ class GraphedDecode:
             exchange_partial(self.s.partial, self.group)
         self.g_combine.replay()
         return self.out
+
+
+class LinkedDecode:
+    """The sharded decode step with both exchanges done by the GPUs themselves (mlops_fbla_shard_step): every rank stores
+    its rows' masses and sums straight into the other ranks' mailboxes over NVLink and polls its own mailbox, with a
+    bound, for theirs. No NCCL call is on the step's path, so the whole step -- nine small launches -- is captured in
+    ONE CUDA graph and replayed. The mailboxes are torch symmetric memory (peer-mapped; multicast is not used).
+
+        step = LinkedDecode(q, shard, group)      # collective: every rank of `group` constructs it
+        out = step()                              # every rank calls it the same number of times
+
+    mailboxes: give the list of the ranks' mailbox base addresses (ints) instead of a group to supply the memory yourself
+    (a single process driving one GPU, tests)."""
+
+    def __init__(self, q: torch.Tensor, s: SequenceShard, group=None, *, scale: float = 0.0, tau: float = 0.0, mailboxes=None, rank=None,
+                 wait_polls: int = 0, graph: bool = True):
+        self.q, self.s = q, s
+        rows = q.shape[0] * q.shape[1]
+        world = s.plan.world if mailboxes is None else len(mailboxes)
+        rank = s.plan.rank if rank is None else rank
+        nbytes = _lib.mlops_fbla_shard_mailbox_bytes(world, rows)
+        if nbytes == 0:
+            raise ValueError(f"no mailbox layout for {world} ranks and {rows} rows")
+        self._keep = []
+        if mailboxes is None:
+            if world > 1:
+                import os
+                os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all this path uses
+                import torch.distributed as dist
+                import torch.distributed._symmetric_memory as symm
+                box = symm.empty(nbytes, dtype=torch.uint8, device=q.device)
+                box.zero_()
+                torch.cuda.synchronize(q.device)
+                handle = symm.rendezvous(box, group if group is not None else dist.group.WORLD)
+                mailboxes = [int(p) for p in handle.buffer_ptrs]
+                self._keep += [box, handle]
+                dist.barrier(group)  # every mailbox is zeroed before anybody's first store can land in it
+            else:
+                box = torch.zeros(nbytes, dtype=torch.uint8, device=q.device)
+                mailboxes = [box.data_ptr()]
+                self._keep.append(box)
+        self._boxes = (ctypes.c_void_p * world)(*mailboxes)
+        self.link = Link(rank, world, ctypes.cast(self._boxes, ctypes.POINTER(ctypes.c_void_p)), wait_polls)
+        self.rows = rows
+        self.out = torch.empty_like(q)
+        self._cfg, self._cache, self._sh, _ = _prepare(q, s)
+        self._cfg.scale, self._cfg.tau = scale, tau
+        self.graph = None
+        self._eager()  # once eagerly: per-device kernel configuration happens here, not under capture
+        torch.cuda.synchronize(q.device)
+        if graph:
+            side = torch.cuda.Stream(q.device)
+            side.wait_stream(torch.cuda.current_stream(q.device))
+            with torch.cuda.stream(side):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    self._eager()
+            torch.cuda.current_stream(q.device).wait_stream(side)
+            self.graph = g
+
+    def _eager(self):
+        st = _lib.mlops_fbla_shard_step(ctypes.byref(self._cfg), ctypes.byref(self._sh), ctypes.byref(self.link), self.q.data_ptr(),
+                                        ctypes.byref(self._cache), self.out.data_ptr(), self.s.scratch.data_ptr(), self.s.scratch.numel(),
+                                        torch.cuda.current_stream(self.q.device).cuda_stream)
+        _raise(st, "mlops_fbla_shard_step")
+
+    def __call__(self) -> torch.Tensor:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._eager()
+        return self.out
+
+    def status(self) -> int:
+        """0, or which exchange gave up waiting (1 masses, 2 sums) + 16 * the rank that stayed silent; synchronises."""
+        return _lib.mlops_fbla_shard_link_status(ctypes.byref(self.link), self.rows, torch.cuda.current_stream(self.q.device).cuda_stream)

@@ -520,6 +520,67 @@ mlops_fbla_status mlops_fbla_shard_partial(const mlops_fbla_config *c, const mlo
   return enqueue_decode(fn, a, stream);
 }
 
+size_t mlops_fbla_shard_mailbox_bytes(int world, int rows) {
+  if (world <= 0 || world > MLOPS_FBLA_SHARD_MAX_RANKS || rows <= 0) return 0;
+  return fbla_k_mailbox_of(world, rows).bytes;
+}
+
+static mlops_fbla_status make_link(const char *fn, const mlops_fbla_shard_link *link, int rows, fbla_k_link &L) {
+  if (!link || !link->mailboxes || link->world <= 0 || link->world > MLOPS_FBLA_SHARD_MAX_RANKS || link->rank < 0 || link->rank >= link->world)
+    return refuse(fn, "the link needs 1 <= world <= %d, 0 <= rank < world and the list of mailboxes", MLOPS_FBLA_SHARD_MAX_RANKS);
+  L = fbla_k_link{};
+  for (int p = 0; p < link->world; ++p) {
+    if (!link->mailboxes[p] || !on_boundary(link->mailboxes[p], 256)) return refuse(fn, "mailbox %d is null or not on a 256-byte boundary", p);
+    L.peer[p] = link->mailboxes[p];
+  }
+  L.rank = link->rank;
+  L.world = link->world;
+  L.rows = rows;
+  L.spin_limit = link->wait_polls ? link->wait_polls : (1u << 22);
+  return MLOPS_FBLA_OK;
+}
+
+mlops_fbla_status mlops_fbla_shard_step(const mlops_fbla_config *c, const mlops_fbla_shard *sh, const mlops_fbla_shard_link *link, const uint16_t *q,
+                                        const mlops_fbla_cache *k, uint16_t *output, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
+  constexpr const char *fn = "mlops_fbla_shard_step";
+  if (!output || !on_boundary(output, 16)) return refuse(fn, "output has to be a device pointer on a 16-byte boundary");
+  if (!c) return refuse(fn, "a required pointer is null");
+  fbla_k_link L;
+  mlops_fbla_status st = make_link(fn, link, c->batch * c->q_heads, L);
+  fbla_k_decode mass_pass, sum_pass;
+  if (st == MLOPS_FBLA_OK) st = make_decode(fn, c, nullptr, q, k, nullptr, false, scratch, scratch_bytes, mass_pass);
+  if (st == MLOPS_FBLA_OK) st = apply_shard(fn, sh, mass_pass);
+  if (st != MLOPS_FBLA_OK) return st;
+  const fbla_k_mailbox M = fbla_k_mailbox_of(L.world, L.rows);
+  char *own = static_cast<char *>(L.peer[L.rank]);
+  sum_pass = mass_pass;
+  mass_pass.phase = 1;  // coarse pass; the rows' local masses
+  mass_pass.row_r = reinterpret_cast<float *>(own + M.local_mass);
+  mass_pass.status_cleared = 1;
+  sum_pass.phase = 2;   // select with the common masses, refine, the shard's sums
+  sum_pass.row_r = reinterpret_cast<float *>(own + M.total);
+  sum_pass.out_partial = reinterpret_cast<float *>(own + M.local_part);
+  sum_pass.status_cleared = 1;
+  cudaError_t e = fbla_k_decode_launch(&mass_pass, stream);
+  if (e == cudaSuccess) e = fbla_k_link_push_mass(&L, stream);
+  if (e == cudaSuccess) e = fbla_k_link_gather_mass(&L, stream);
+  if (e == cudaSuccess) e = fbla_k_decode_launch(&sum_pass, stream);
+  if (e == cudaSuccess) e = fbla_k_link_push_partial(&L, stream);
+  if (e == cudaSuccess) e = fbla_k_link_combine(&L, output, stream);
+  return e == cudaSuccess ? accepted() : device_failure(fn, e);
+}
+
+int mlops_fbla_shard_link_status(const mlops_fbla_shard_link *link, int rows, cudaStream_t stream) {
+  fbla_k_link L;
+  if (make_link("mlops_fbla_shard_link_status", link, rows, L) != MLOPS_FBLA_OK) return -1;
+  int word = 0;
+  const char *own = static_cast<const char *>(L.peer[L.rank]);
+  if (cudaMemcpyAsync(&word, own + fbla_k_mailbox_of(L.world, L.rows).status, sizeof word, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+  accepted();
+  return word;
+}
+
 mlops_fbla_status mlops_fbla_shard_total_mass(int shards, int rows, const float *gathered, float *row_mass_total, cudaStream_t stream) {
   constexpr const char *fn = "mlops_fbla_shard_total_mass";
   if (shards <= 0 || rows <= 0 || !gathered || !row_mass_total) return refuse(fn, "needs shards > 0, rows > 0 and both device pointers");

@@ -11,6 +11,12 @@
 // The array's name is only a host-side handle; kernels need its device address, which differs per device. The first
 // call on a device (with that device current) asks the runtime for it with cudaGetSymbolAddress, checks the answer
 // and caches it. That first call should therefore be made before any stream capture begins on that device.
+// "Allocates nothing" is about this library's calls: the CUDA driver itself commits the 32 MiB and the kernels' code
+// when it first loads this module on a device (lazy loading, the default, does that at the first use). A caller whose
+// arena will take all device memory calls mlops_fbla_decode_static_prepare() on every device at start-up, BEFORE it
+// takes the arena (and before any capture): it forces that load and looks the address up, and launches nothing. The
+// cached address does not survive cudaDeviceReset. Rejections of this entry point are reported by
+// mlops_fbla_decode_static_error() (mlops_fbla_last_error() keeps the text of the ordinary entry points).
 //
 // All calls on one device share the one array. The decode passes write every scratch word before they read it and
 // clear their own status word, so nothing has to be zeroed between calls and the previous call's contents are
@@ -54,6 +60,11 @@ void *static_scratch() {
 }  // namespace
 
 extern "C" size_t mlops_fbla_decode_static_scratch_limit(void) { return FBLA_STATIC_SCRATCH_BYTES; }
+
+extern "C" mlops_fbla_status mlops_fbla_decode_static_prepare(void) {
+  g_error[0] = 0;
+  return static_scratch() ? MLOPS_FBLA_OK : MLOPS_FBLA_CUDA_ERROR;
+}
 
 extern "C" const char *mlops_fbla_decode_static_error(void) { return g_error; }
 

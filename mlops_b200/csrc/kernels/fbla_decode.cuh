@@ -534,22 +534,12 @@ __device__ __forceinline__ bool coarse_group(Ring<CB> &ring, int k, const float4
     __syncwarp();  // pst is free; after a chunk's last pair its slot is too
     if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();  // refill the slot with the chunk NP ahead
   };
-#ifdef FBLA_NOCOMPUTE  // tuning builds only: stream the chunks without touching them
-#pragma unroll 1
-  for (int J = 0; J < SBG / 2; ++J) {
-    const int p = CoarseShape<CB>::CPG * k + J / CoarseShape<CB>::PPC;
-    if (J % CoarseShape<CB>::PPC == 0 && !ring.wait_pair(p)) return false;
-    __syncwarp();
-    if (J % CoarseShape<CB>::PPC == CoarseShape<CB>::PPC - 1) ring.issue_next();
-  }
-#else
 #pragma unroll 1
   for (int J = 0; J < SBG / 2; ++J) {
     Scores sc;
     if (!stage_a(J, sc)) return false;
     stage_b(J, sc);
   }
-#endif
   // fold the group into the running softmax: o += vs' A + vb' B, coarse cell midpoints folded into vb'
   run.l[0] += Bs.x; run.l[1] += Bs.y;
 #pragma unroll
@@ -635,9 +625,6 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status && !a.status_cleared) { a.status[0] = 0; a.status[1] = 0; }
   if (!DYN) {
     if (warp >= Sh::WARPS) {
-#ifdef FBLA_NOWINDOW  // tuning builds only
-      return;
-#endif
       exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, FBLA_POS::x() + (warp - Sh::WARPS), FBLA_POS::nx());
       return;
     }
@@ -652,9 +639,6 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
       return;
     }
   }
-#ifdef FBLA_NOSTREAM  // tuning builds only
-  return;
-#endif
   StreamWarp<CB> &w = sm.w[warp];
   for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
   reinterpret_cast<uint32_t *>(w.pst)[lane] = 0u;
@@ -680,9 +664,10 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
       mbar_inval(&w.bar_meta[1]);
     }
   };
-  // One partial row per (CTA, virtual head): slot cta + vh. Rows of virtual heads that lie wholly inside the warp's run go
-  // straight to the scratch; the run's first and last virtual head may continue in the neighbouring warps, so their rows
-  // are staged in shared memory and folded below, in warp order (a fixed order: the result is reproducible bit for bit).
+  // a.fold (few virtual heads, each spread over many warps): one partial row per (CTA, virtual head), slot cta + vh. Rows
+  // of virtual heads that lie wholly inside the warp's run go straight to the scratch; the run's first and last virtual
+  // head may continue in the neighbouring warps, so their rows are staged in shared memory and folded below, in warp order
+  // (a fixed order: the result is reproducible bit for bit). Otherwise: one row per (warp, virtual head), slot gw + vh.
   const int cta = FBLA_POS::x();
   int first_vh = -1, cur_vh = -1;
   bool ok = true;
@@ -697,7 +682,9 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
     for (long long u = lo; u < hi; ++u, advance<false>(a, hpr, cc)) {
       const int vh = cc.b * hpr + cc.hir;
       if (vh != cur_vh) {
-        if (cur_vh >= 0) write_partial<QG>(cur_vh == first_vh ? &w.stage[0][0][0] : a.part + (size_t)(cta + cur_vh) * QG * PSTRIDE, run, lane, false);
+        if (cur_vh >= 0)
+          write_partial<QG>(!a.fold ? a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE
+                            : cur_vh == first_vh ? &w.stage[0][0][0] : a.part + (size_t)(cta + cur_vh) * QG * PSTRIDE, run, lane, false);
         if (cur_vh < 0) first_vh = vh;
         cur_vh = vh;
         reset<QG>(run);
@@ -713,7 +700,11 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
         break;
       }
     }
-    if (ok) write_partial<QG>(&w.stage[cur_vh == first_vh ? 0 : 1][0][0], run, lane, false);
+    if (ok) write_partial<QG>(!a.fold ? a.part + (size_t)(gw + cur_vh) * QG * PSTRIDE : &w.stage[cur_vh == first_vh ? 0 : 1][0][0], run, lane, false);
+  }
+  if (!a.fold) {  // one row per (warp, virtual head), already in the scratch
+    if (ok) retire();
+    return;
   }
   if (ok) retire();  // (after a wait that gave up a copy may still be in flight: the barriers stay as they are)
   if (lane == 0) {
@@ -748,15 +739,15 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
 }
 
 // ---- which partial slots belong to a virtual head ------------------------------------------------------------------------
-struct Slots { int c0, c1, x0, x1; };  // coarse CTAs c0..c1 (slot cta + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
+struct Slots { int c0, c1, x0, x1; };  // coarse CTAs (a.fold) or warps c0..c1 (slot c + vh), window warps x0..x1 (slot tw + vheads + x + vh); empty if c1 < c0
 __device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
   const int hpr = a.kv_heads * a.vg;
   Slots s{0, -1, 0, -1};
   int n;
   const Split sp = split_of(a, hpr);
   long long off = head_offset<false>(a, hpr, vh, n);
-  if (n > 0) {  // a CTA's sw streaming warps take sw consecutive runs of `per` units: one (folded) row per CTA
-    const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw) * sp.sw;
+  if (n > 0) {  // (a.fold: a CTA's sw streaming warps take sw consecutive runs of units and leave one folded row per CTA)
+    const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw) * (a.fold ? sp.sw : 1);
     s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per);
   }
   off = head_offset<true>(a, hpr, vh, n);
@@ -933,11 +924,25 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
     while (h - l > 1) { const int mid = (l + h) >> 1; if (pre[mid] <= lo) l = mid; else h = mid; }
     fe = l;
   }
-  int ce = fe;
-  auto item_at = [&](int k, int &e) {  // item k (>= the previous k): its entry (advanced) and value
-    while (pre[e + 1] <= k) ++e;
-    return __ldcg(a.items + (size_t)e * SLICE + (k - pre[e]));
+  // The warp's items are read 32 at a time, one per lane (lane i: item base + i, with its entry), and handed out by
+  // shuffles: the per-item loads of the list would otherwise sit, one dependent round trip to L2 each, in front of every
+  // copy that is issued and every item that is decoded.
+  int win_base = lo, win_it = 0, win_e = fe;
+  auto load_window = [&](int base, int e_start) {
+    win_base = base;
+    const int k = base + lane;
+    int e = e_start;
+    if (k < hi) {
+      while (pre[e + 1] <= k) ++e;
+      win_it = __ldcg(a.items + (size_t)e * SLICE + (k - pre[e]));
+    }
+    win_e = e;
   };
+  auto item_at = [&](int k, int &e) {  // item k of the window (warp-uniform k): its entry and value
+    e = __shfl_sync(FULL, win_e, k - win_base);
+    return __shfl_sync(FULL, win_it, k - win_base);
+  };
+  load_window(lo, fe);
   long long issued_unit = -1;  // (lane 0) the (virtual head, group) of the last item issued, and which metadata buffer it uses
   int issued_par = 1;
   auto issue = [&](int it, int e, int s) {  // lane 0
@@ -953,12 +958,12 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
       bulk_g2s(w.meta[issued_par], reinterpret_cast<const uint8_t *>(a.c.meta) + unit * 1024, 1024, &w.bar[s]);
     }
   };
-  int fit[Sh::NST];  // the items in flight (warp-uniform)
 #pragma unroll
   for (int s = 0; s < Sh::NST; ++s)
     if (lo + s < hi) {
-      fit[s] = item_at(lo + s, fe);
-      if (lane == 0) issue(fit[s], fe, s);
+      int e;
+      const int first = item_at(lo + s, e);
+      if (lane == 0) issue(first, e, s);
     }
   Run run;  // m unused: corrections are already in units of 2^-R
   float2 Ag[4][4], Bg = make_float2(0.f, 0.f);  // the current group's sums in code units, (.x, .y) = queries e = 0, 1
@@ -966,7 +971,6 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
   for (int u = 0; u < 4; ++u)
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) Ag[u][cc] = make_float2(0.f, 0.f);
-  int pe = fe;  // entry cursor for peeking at the next item
   float4 q4[QG];
   float Rq[2] = {0.f, 0.f}, c0[2] = {0.f, 0.f}, sqc[2] = {0.f, 0.f}, sqf[2] = {0.f, 0.f}, qbf[2] = {0.f, 0.f};
   uint32_t B[8];
@@ -974,6 +978,12 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
   long long cur_unit = -1, cur_unit2 = -1;  // cur_unit is also reset when the virtual head changes; cur_unit2 follows the groups only
   for (int k = lo; k < hi; ++k) {
     const int s = (k - lo) % Sh::NST;
+    if (k + Sh::NST >= win_base + 32) {  // the window moves on before an item beyond it is asked for
+      int e0;
+      item_at(k, e0);
+      load_window(k, e0);
+    }
+    int ce;
     const int it = item_at(k, ce), vh = ce / a.nslices, sb = it >> 4;
     if (vh != cur_vh) {
       if (cur_vh >= 0) write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
@@ -1084,6 +1094,7 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
       // the group's last item of this warp: apply the V affine once (coarse cells at their midpoint)
       bool last = k + 1 >= hi;
       if (!last) {
+        int pe;
         const int nx = item_at(k + 1, pe);
         last = pe / a.nslices != vh || (nx >> 4) / SBG != sb / SBG;
       }
@@ -1105,8 +1116,9 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
     }
     __syncwarp();
     if (k + Sh::NST < hi) {
-      fit[s] = item_at(k + Sh::NST, fe);
-      if (lane == 0) { fence_async_smem(); issue(fit[s], fe, s); }
+      int ne;
+      const int ahead = item_at(k + Sh::NST, ne);
+      if (lane == 0) { fence_async_smem(); issue(ahead, ne, s); }
     }
   }
   write_partial<QG>(a.dpart + (size_t)(gw + cur_vh) * QG * PSTRIDE, run, lane, true);
@@ -1161,15 +1173,15 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
       }
   }
   const int w0 = rr[0], w1 = rr[1];
-  for (int i0 = w0 + sl; i0 <= w1; i0 += 16) {
-    float l[4], o[4];
+  for (int i0 = w0 + sl; i0 <= w1; i0 += 4 * MJ) {  // (one correction row per refine warp that met the head: up to a few hundred)
+    float l[MJ], o[MJ];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < MJ; ++j) {
       const float *p = a.dpart + ((size_t)(min(i0 + 4 * j, w1) + vh) * QG + qi) * PSTRIDE;
       l[j] = __ldcg(p + D); o[j] = __ldcg(p + ch);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < MJ; ++j)
       if (i0 + 4 * j <= w1) { L += l[j]; O += o[j]; }
   }
   so[sl][ch] = O;

@@ -55,6 +55,7 @@ typedef struct {
   int shard_on, sh_first, sh_count, sh_windows, phase;
   float *out_partial;  // [rows][FBLA_K_PSTRIDE] floats (phase 2)
   int status_cleared;  // 1: the launcher zeroes the status word on the stream before the first pass; 0: CTA 0 of the coarse pass does
+  int fold;            // 1: the coarse pass leaves one partial row per (CTA, virtual head) instead of one per (warp, virtual head)
 } fbla_k_decode;
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
@@ -75,6 +76,38 @@ FBLA_HOST_API(cudaError_t fbla_k_combine_launch(const float *partial, uint16_t *
 FBLA_HOST_API(long long fbla_k_refine_entry_limit(int cb);)
 // occupancy-derived launch shape for the current device; fills coarse_ctas .. refine_warps from cb / qg
 FBLA_HOST_API(cudaError_t fbla_k_decode_shape(fbla_k_decode *a);)
+
+// ---- the exchanges of a sequence-sharded decode as stores into the peers' memory (kernels/fbla_link.cu) -------------------
+#define FBLA_K_MAX_RANKS 8
+typedef struct {
+  void *peer[FBLA_K_MAX_RANKS];  // the base of every rank's mailbox, as this rank addresses it (peer[rank]: its own)
+  int rank, world, rows;         // rows = batch * q_heads
+  unsigned spin_limit;           // polls (64 ns apart) before a wait for a peer gives up
+} fbla_k_link;
+// Byte offsets inside a mailbox (the same on every rank). epoch: the step counter; status: 0, or which wait gave up
+// (1 masses, 2 sums, + 16 * the silent rank); *_flag[s], *_in[s]: the stamp and the data rank s stored here.
+typedef struct {
+  size_t epoch, status, mass_flag, part_flag, mass_in, local_mass, total, part_in, local_part, bytes;
+} fbla_k_mailbox;
+static inline __host__ __device__ fbla_k_mailbox fbla_k_mailbox_of(int world, int rows) {
+  fbla_k_mailbox m;
+  size_t at = 0;
+  m.epoch = at; at += 16;
+  m.status = at; at += 240;
+  m.mass_flag = at; at += 256;
+  m.part_flag = at; at += 256;
+  m.mass_in = at; at += ((size_t)world * rows * 4 + 255) / 256 * 256;
+  m.local_mass = at; at += ((size_t)rows * 4 + 255) / 256 * 256;
+  m.total = at; at += ((size_t)rows * 4 + 255) / 256 * 256;
+  m.part_in = at; at += ((size_t)world * rows * FBLA_K_PSTRIDE * 4 + 255) / 256 * 256;
+  m.local_part = at; at += ((size_t)rows * FBLA_K_PSTRIDE * 4 + 255) / 256 * 256;
+  m.bytes = at;
+  return m;
+}
+FBLA_HOST_API(cudaError_t fbla_k_link_push_mass(const fbla_k_link *L, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_link_gather_mass(const fbla_k_link *L, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_link_push_partial(const fbla_k_link *L, cudaStream_t stream);)
+FBLA_HOST_API(cudaError_t fbla_k_link_combine(const fbla_k_link *L, uint16_t *out, cudaStream_t stream);)
 
 // ---- prefill: close the chunk's groups, attention, update the BF16 windows --------------------------------------------
 typedef struct {

@@ -68,3 +68,29 @@ def test_exchanges_two_gloo_ranks(sharded, tmp_path):
     outs = [p.communicate(timeout=120)[0].decode() for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} ok" in o, o
+
+
+def test_linked_step_argument_checks_without_a_device(sharded):
+    """mlops_fbla_shard_step / mlops_fbla_shard_mailbox_bytes reject bad links before anything is launched."""
+    import ctypes
+    from mlops_b200.attention import _C
+    lib = sharded._lib
+    assert lib.mlops_fbla_shard_mailbox_bytes(0, 32) == 0 and lib.mlops_fbla_shard_mailbox_bytes(9, 32) == 0 and lib.mlops_fbla_shard_mailbox_bytes(2, 0) == 0
+    one, eight = lib.mlops_fbla_shard_mailbox_bytes(1, 32), lib.mlops_fbla_shard_mailbox_bytes(8, 32)
+    assert 0 < one < eight and one % 256 == 0 and eight % 256 == 0
+    # 8 ranks x 32 rows: masses 8 x 128 B, sums 8 x 16 896 B, plus this rank's own copies and the flags
+    assert eight >= 8 * 32 * 4 + 8 * 32 * 132 * 4 + 32 * 132 * 4
+    cfg = _C.Config(1, 32, 8, 4096, 0.0, 0.0, 0, 0, 0, 0, 0, 0, 0)
+    cache = _C.Cache(*([0x1000] * 7), None)
+    sh = sharded.Shard(1, 10, 3)
+    vp = ctypes.c_void_p
+    boxes = (ctypes.c_void_p * 2)(0x10000, 0x20000)
+    def call(link):
+        return lib.mlops_fbla_shard_step(ctypes.byref(cfg), ctypes.byref(sh), ctypes.byref(link), vp(0x1000), ctypes.byref(cache), vp(0x1000), vp(0x1000),
+                                         ctypes.c_size_t(1 << 30), None)
+    bad_world = sharded.Link(0, 9, ctypes.cast(boxes, ctypes.POINTER(ctypes.c_void_p)), 0)
+    assert call(bad_world) == _C.INVALID_VALUE and "world" in _C.last_error()
+    bad_rank = sharded.Link(2, 2, ctypes.cast(boxes, ctypes.POINTER(ctypes.c_void_p)), 0)
+    assert call(bad_rank) == _C.INVALID_VALUE
+    odd = (ctypes.c_void_p * 2)(0x10000, 0x20010)  # the second mailbox is not on a 256-byte boundary
+    assert call(sharded.Link(0, 2, ctypes.cast(odd, ctypes.POINTER(ctypes.c_void_p)), 0)) == _C.INVALID_VALUE and "mailbox 1" in _C.last_error()

@@ -33,6 +33,8 @@ def _static_decode(lib, c, q, tau=0.0):
 @pytest.mark.parametrize("mode", ["3+3", "4+2"])
 def test_static_scratch_decode_matches_decode(mode):
     lib = gu.CLib(gu.OURS)
+    lib.lib.mlops_fbla_decode_static_prepare.restype = ctypes.c_int
+    assert lib.lib.mlops_fbla_decode_static_prepare() == 0  # (the start-up call: module load and address look-up, no launch)
     q, k, v = datagen.baseline_case(1001, 1, 16, 8, 4096)
     qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
     c = lib.encode(kd, vd, mode)
