@@ -42,6 +42,8 @@ WORKLOADS = {
                         name="decode B1 32q/8kv ctx131072 3+3 (the metric's 128K context)"),
     "decode_128k_4p2": dict(kind="decode", batch=1, q_heads=32, kv_heads=8, tokens=131072, mode="4+2", seed=1003, outliers=False,
                             name="decode B1 32q/8kv ctx131072 4+2 (the metric's 128K context)"),
+    "decode_4k": dict(kind="decode", batch=1, q_heads=16, kv_heads=8, tokens=4096, mode="3+3", seed=1001, outliers=True,
+                      name="decode B1 16q/8kv ctx4096 3+3 (BASELINE configs[0])"),
     "decode_b8": dict(kind="decode", batch=8, q_heads=32, kv_heads=8, tokens=16384, mode="4+2", seed=1002, outliers=True,
                       name="decode B8 32q/8kv ctx16384 4+2 (BASELINE configs[1])"),
     "serving_b64": dict(kind="serving", batch=64, q_heads=32, kv_heads=8, lo=1024, hi=65536, mode="3+3", seed=1005,
@@ -641,6 +643,7 @@ def run_workload(D, name, args, headline):
 
 
 def main():
+    global MIN_TIMED_S
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50, help="steps per timed block (blocks repeat until 0.5 s has been timed)")
@@ -652,7 +655,6 @@ def main():
     ap.add_argument("--min-time", type=float, default=MIN_TIMED_S,
                     help="seconds to time at least, in blocks of --steps steps (0: one block; for captures under a profiler)")
     args = ap.parse_args()
-    global MIN_TIMED_S
     MIN_TIMED_S = args.min_time
     if args.impl == "reference":
         return run_reference(args)

@@ -3,10 +3,10 @@
 #include <stdio.h>
 
 namespace fbla {
-template <int CB, int FB, int QG, bool DYN>
+template <int CB, int FB, int QG, int DEAL>
 __global__ void __launch_bounds__(32 * CoarseShape<CB>::TOTAL, 1) coarse_kernel(const fbla_k_decode a) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  coarse_item<CB, FB, QG, DYN>(a, smem_raw);
+  coarse_item<CB, FB, QG, DEAL>(a, smem_raw);
 }
 
 template <int QG>
@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(32 * RefineShape<CB, FB>::WARPS, 1) refine_ker
 }
 
 template <int QG>
-__global__ void __launch_bounds__(512) merge_kernel(const fbla_k_decode a) {
+__global__ void __launch_bounds__(512, 2) merge_kernel(const fbla_k_decode a) {
   merge_item<QG>(a, nullptr);
 }
 
@@ -57,8 +57,9 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    cudaError_t e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_LENGTHS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_FIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_COST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csm);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(refine_kernel<CB, FB, QG>, cudaFuncAttributeMaxDynamicSharedMemorySize, REFINE_SMEM_MAX);
     if (e != cudaSuccess) return e;
@@ -72,8 +73,9 @@ template <int CB, int FB, int QG> cudaError_t launch_all(const fbla_k_decode &a,
     if (e != cudaSuccess) return e;
   }
   if (a.phase != 2) {
-    if (a.coarse_warps == CoarseShape<CB>::TOTAL) coarse_kernel<CB, FB, QG, true><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
-    else coarse_kernel<CB, FB, QG, false><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+    if (a.deal == FBLA_K_DEAL_LENGTHS) coarse_kernel<CB, FB, QG, FBLA_K_DEAL_LENGTHS><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+    else if (a.deal == FBLA_K_DEAL_FIXED) coarse_kernel<CB, FB, QG, FBLA_K_DEAL_FIXED><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+    else coarse_kernel<CB, FB, QG, FBLA_K_DEAL_COST><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
     e = cudaGetLastError();
     if (e == cudaSuccess) e = launch_dependent(select_kernel<QG>, dim3(a.phase == 1 ? 1 : a.nslices, vheads), dim3(256), 0, stream, a);
     if (a.phase == 1) return e;
@@ -94,8 +96,9 @@ template <int CB, int FB, int QG> cudaError_t launch_one(const fbla_k_decode &a,
   if (rsm > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   switch (pass) {
     case 0:
-      if (a.coarse_warps == CoarseShape<CB>::TOTAL) coarse_kernel<CB, FB, QG, true><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
-      else coarse_kernel<CB, FB, QG, false><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+      if (a.deal == FBLA_K_DEAL_LENGTHS) coarse_kernel<CB, FB, QG, FBLA_K_DEAL_LENGTHS><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+      else if (a.deal == FBLA_K_DEAL_FIXED) coarse_kernel<CB, FB, QG, FBLA_K_DEAL_FIXED><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
+      else coarse_kernel<CB, FB, QG, FBLA_K_DEAL_COST><<<a.coarse_ctas, 32 * CoarseShape<CB>::TOTAL, csm, stream>>>(a);
       break;
     case 1: select_kernel<QG><<<dim3(a.nslices, vheads), 256, 0, stream>>>(a); break;
     case 2: refine_kernel<CB, FB, QG><<<a.refine_ctas, 32 * RefineShape<CB, FB>::WARPS, rsm, stream>>>(a); break;
@@ -111,10 +114,10 @@ template <int CB, int FB, int QG> cudaError_t passes_of(const fbla_k_decode &a, 
   const size_t rsm = sizeof(RefineWarp<CB, FB>) * RefineShape<CB, FB>::WARPS + sizeof(int) * ((size_t)vheads * a.nslices + 1) + 128;
   if (rsm - 128 > REFINE_SMEM_MAX) return cudaErrorInvalidValue;
   char e[96];
-  const bool dyn = a.coarse_warps == CoarseShape<CB>::TOTAL;
-  snprintf(e, sizeof e, "fbla::coarse_item<%d, %d, %d, %s>", CB, FB, QG, dyn ? "true" : "false");
-  cudaError_t st = dyn ? pass_of(coarse_kernel<CB, FB, QG, true>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0)
-                       : pass_of(coarse_kernel<CB, FB, QG, false>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0);
+  snprintf(e, sizeof e, "fbla::coarse_item<%d, %d, %d, %d>", CB, FB, QG, (int)a.deal);
+  cudaError_t st = a.deal == FBLA_K_DEAL_LENGTHS ? pass_of(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_LENGTHS>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0)
+                   : a.deal == FBLA_K_DEAL_FIXED ? pass_of(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_FIXED>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0)
+                                                 : pass_of(coarse_kernel<CB, FB, QG, FBLA_K_DEAL_COST>, a.coarse_ctas, 1, 32 * CoarseShape<CB>::TOTAL, csm, e, p + 0);
   snprintf(e, sizeof e, "fbla::select_item<%d>", QG);
   if (st == cudaSuccess) st = pass_of(select_kernel<QG>, a.nslices, vheads, 256, 0, e, p + 1);
   snprintf(e, sizeof e, "fbla::refine_item<%d, %d, %d>", CB, FB, QG);
@@ -172,18 +175,25 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
   return cudaSuccess;
 }
 
-// The split of the coarse CTAs' warps (coarse_warps, see split_of): by the lengths when, at `tokens` per row, the BF16
-// windows would get three or more of a CTA's warps -- contexts up to about 4 700 tokens; else the fixed one.
+// How the coarse CTAs' warps share the work (see split_of, deal_of), from the tokens a row has at most:
+//   by the lengths when the BF16 windows would get three or more of a CTA's eight warps (contexts up to about 4 700 tokens);
+//   by cost -- every warp an equal share of windows and groups -- when that shortens a warp's work by more than the ~5 %
+//   that eight streaming warps lose against seven and a window warp: contexts from about 20K (3+3) / 27K (4+2) tokens
+//   (measured on B200, by cost against seven + one: batch 1 x 128K tokens 80.0 -> 75.3 us per step in 3+3 and 65.7 -> 63.7
+//   in 4+2, batch 64 x 1K..64K 2.07 -> 2.02 ms, but batch 8 x 16K 120.0 -> 123.9);
+//   seven streaming warps and one window warp per CTA between the two.
 extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
   const int total = (a->cb == 4 ? fbla::CoarseShape<4>::TOTAL : fbla::CoarseShape<3>::TOTAL);
   const long long groups = (tokens + fbla::G - 1) / fbla::G, S = groups > 2 ? groups - 2 : 0;
   const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : 2 * fbla::SBG;  // (a full open window: the choice is monotone in tokens)
-  const bool dyn = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
-  a->coarse_warps = dyn ? total : total - 1;
+  const bool by_lengths = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
+  const int wc = a->cb == 3 ? 6 : 8;  // (deal_of's cost of a window sub-block, a group's being 8)
+  a->coarse_warps = total;
+  a->deal = by_lengths ? FBLA_K_DEAL_LENGTHS : 8 * S > 13 * wc * W ? FBLA_K_DEAL_COST : FBLA_K_DEAL_FIXED;
   // Folding the warps' partial rows per CTA costs the coarse pass a barrier and a few microseconds at its very end and saves
   // the later passes their walk over the rows: it pays when a virtual head is spread over many warps, i.e. when there are
   // few heads (measured on B200: batch 1 x 8 KV heads at 128K tokens -4.5 us per step, batch 8 x 8 heads at 16K +3 us).
-  a->fold = !dyn && a->batch * a->kv_heads * a->vg <= 32;
+  a->fold = !by_lengths && a->batch * a->kv_heads * a->vg <= 32;
 }
 
 extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream) {

@@ -183,29 +183,54 @@ struct __align__(16) ExactWarp {
   float q[4][D];
   uint8_t pst[4][16];
 };
-// (a warp streams or serves windows, never both, and the last warp never streams: when the split follows the lengths, a
-// window warp other than the last keeps its ExactWarp in the streaming buffers it does not use)
+// (every warp has streaming buffers; a warp that serves windows keeps its ExactWarp in the buffers it does not stream
+// into yet, or at all)
 template <int CB> struct CoarseSmem {
-  StreamWarp<CB> w[CoarseShape<CB>::WARPS];
-  ExactWarp x[1];
+  StreamWarp<CB> w[CoarseShape<CB>::TOTAL];
 };
+static_assert(sizeof(CoarseSmem<3>) + 128 <= 227 * 1024 && sizeof(CoarseSmem<4>) + 128 <= 227 * 1024, "one CTA's shared memory");
 static_assert(sizeof(ExactWarp) <= sizeof(StreamWarp<3>) && sizeof(ExactWarp) <= sizeof(StreamWarp<4>), "a window warp's state fits a streaming warp's");
 
 // ---- the coarse pass's work, split over its warps --------------------------------------------------------------------------
 // Streaming units are the closed groups of all virtual heads, flattened; window units the 16-token sub-blocks of the
-// BF16 sink / open windows, flattened. Of a CTA's warps the last xw serve windows and the others stream. Each kind's
-// units are dealt in equal contiguous runs over its warps of all CTAs, so the split depends on the lengths alone and no
-// warp between two that serve a head is empty: the readers (slots_of) take every slot from the first to the last warp
-// of a head as written.
-// a.coarse_warps names the split. WARPS (the default): the fixed WARPS + 1, the measured optimum of long contexts.
-// TOTAL: xw follows the lengths -- the windows' share of all units (one unit of either kind costs a warp about the same
-// time), at least one warp for the windows (the last warp has no streaming buffers) and one for the groups if there are
-// any. The host asks for it when the windows are a large part of the work: short contexts at large batch
-// (batch 256 x 512 tokens: 638 -> 352 us per step, batch 32 x 4096: 182 -> 166).
+// BF16 sink / open windows, flattened. Either way of dealing them depends on the lengths alone and leaves no empty warp
+// between two that serve a head: the readers (slots_of) take every slot from the first to the last warp of a head as
+// written.
+// Split by the lengths (short contexts, FBLA_K_DEAL_LENGTHS): of a CTA's warps the last xw serve windows and the others stream, and
+// each kind's units are dealt in equal contiguous runs over its warps of all CTAs. xw is the windows' share of all units
+// (at these lengths one unit of either kind costs a warp about the same time), at least one warp for the windows and one
+// for the groups if there are any. The host asks for it when the windows are a large part of the work: short contexts
+// at large batch (batch 256 x 512 tokens: 638 -> 352 us per step, batch 32 x 4096: 182 -> 166).
+//
+// FBLA_K_DEAL_FIXED (contexts in between): the same with xw = 1, whatever the lengths.
+//
+// FBLA_K_DEAL_COST (long contexts): no warp is set aside. All units form one list, window sub-blocks first, then the groups, each
+// with a cost in eighths of a group's time (a window sub-block takes a warp about as long as a 4-bit group and three
+// quarters of a 3-bit one); every warp of the grid takes the units whose cost interval starts inside its equal share
+// [w P, (w + 1) P) of the total, serves its window sub-blocks and then streams its groups. A share is at least one
+// unit's cost, so consecutive units lie in the same or in consecutive warps. At batch 1 and 128K tokens a warp then
+// streams 7 groups instead of 8.
+struct Deal { long long S, X, P; int wc; };  // groups, window sub-blocks, cost share per warp, cost of a window sub-block
+constexpr int GROUP_COST = 8;
+__device__ __forceinline__ Deal deal_of(const fbla_k_decode &a, int hpr) {
+  Deal d;
+  d.S = total_units<false>(a, hpr);
+  d.X = total_units<true>(a, hpr);
+  d.wc = a.cb == 3 ? 6 : 8;
+  d.P = max((long long)GROUP_COST, ceil_div(GROUP_COST * d.S + d.wc * d.X, (long long)a.coarse_ctas * a.coarse_warps));
+  return d;
+}
+// the units of warp w: window sub-blocks [xlo, xhi), groups [lo, hi)
+__device__ __forceinline__ void deal_range(const Deal &d, long long w, long long &xlo, long long &xhi, long long &lo, long long &hi) {
+  const long long c0 = w * d.P, c1 = c0 + d.P, wx = d.wc * d.X;
+  xlo = min(d.X, ceil_div(c0, (long long)d.wc)); xhi = min(d.X, ceil_div(c1, (long long)d.wc));
+  lo = c0 <= wx ? 0 : min(d.S, ceil_div(c0 - wx, (long long)GROUP_COST));
+  hi = c1 <= wx ? 0 : min(d.S, ceil_div(c1 - wx, (long long)GROUP_COST));
+}
 struct Split { int sw, xw; };  // streaming / window warps per CTA
 __device__ __forceinline__ Split split_of(const fbla_k_decode &a, int hpr) {
   const int total = (a.cb == 4 ? FBLA_CW4 : FBLA_CW3) + 1;
-  if (a.coarse_warps < total) return Split{a.coarse_warps, 1};
+  if (a.deal == FBLA_K_DEAL_FIXED) return Split{total - 1, 1};
   const long long S = total_units<false>(a, hpr), W = total_units<true>(a, hpr);
   const int xw = S == 0 ? total : max(1, min(total - 1, (int)((2 * total * W + S + W) / (2 * (S + W)))));
   return Split{total - xw, xw};
@@ -232,11 +257,10 @@ struct WindowTile {
 };
 // AHEAD: the next sub-block's loads are issued before the current one is computed (two tiles of registers); without it
 // a warp that shares its CTA with many others stays within their register budget.
+// the window sub-blocks [lo, hi) of the flattened list; the partial rows go to window slot xw + virtual head
 template <int QG, bool AHEAD = true>
-__device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
+__device__ void exact_range(const fbla_k_decode &a, ExactWarp &sm, int lane, long long lo, long long hi, int xw) {
   const int hpr = a.kv_heads * a.vg;
-  const long long total = total_units<true>(a, hpr), per = ceil_div(total, nxw);
-  const long long lo = (long long)xw * per, hi = min(total, lo + per);
   if (lo >= hi) return;
   const int slot0 = a.coarse_ctas * a.coarse_warps + a.batch * hpr;  // after the coarse slots
   const int t = lane & 15, h = lane >> 4;
@@ -349,6 +373,12 @@ __device__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int 
     if (AHEAD) cur = nxt;
   }
   flush();
+}
+// window warp xw of nxw: an equal contiguous run of the sub-blocks
+template <int QG>
+__device__ __forceinline__ void exact_warp(const fbla_k_decode &a, ExactWarp &sm, int lane, int xw, int nxw) {
+  const long long total = total_units<true>(a, a.kv_heads * a.vg), per = ceil_div(total, nxw), lo = (long long)xw * per;
+  exact_range<QG>(a, sm, lane, lo, min(total, lo + per), xw);
 }
 
 // ---- one closed group on the tensor cores ----------------------------------------------------------------------------------
@@ -615,7 +645,9 @@ __device__ __forceinline__ void fold_rows(float *dst, const float *own, const fl
   }
 }
 
-template <int CB, int FB, int QG, bool DYN>
+// DEAL: how the work is dealt to the warps (FBLA_K_DEAL_*, the host's choice in fbla_k_decode::deal; one build per way, so
+// that none carries the others' code)
+template <int CB, int FB, int QG, int DEAL>
 __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *smem_raw) {
   using Sh = CoarseShape<CB>;
   allow_next_pass();
@@ -623,21 +655,27 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   CoarseSmem<CB> &sm = *reinterpret_cast<CoarseSmem<CB> *>(smem_raw);
   const int lane = FBLA_POS::tid() & 31, warp = FBLA_POS::tid() >> 5;
   if (FBLA_POS::x() == 0 && FBLA_POS::tid() == 0 && a.status && !a.status_cleared) { a.status[0] = 0; a.status[1] = 0; }
-  if (!DYN) {
-    if (warp >= Sh::WARPS) {
-      exact_warp<QG>(a, sm.x[warp - Sh::WARPS], lane, FBLA_POS::x() + (warp - Sh::WARPS), FBLA_POS::nx());
-      return;
-    }
-  }
   const int hpr = a.kv_heads * a.vg;
-  int sw = Sh::WARPS;  // streaming warps of this CTA
-  if (DYN) {
-    const Split sp = split_of(a, hpr);
+  int sw = Sh::TOTAL;                 // streaming warps of this CTA
+  long long gw, lo, hi;               // the warp's index among the grid's streaming warps and its run of the flattened groups
+  if (DEAL != FBLA_K_DEAL_COST) {  // the CTA's last xw warps serve windows, the others stream
+    const Split sp = DEAL == FBLA_K_DEAL_LENGTHS ? split_of(a, hpr) : Split{Sh::WARPS, 1};
     sw = sp.sw;
     if (warp >= sw) {
-      exact_warp<QG>(a, warp == Sh::WARPS ? sm.x[0] : *reinterpret_cast<ExactWarp *>(&sm.w[warp]), lane, FBLA_POS::x() * sp.xw + (warp - sw), FBLA_POS::nx() * sp.xw);
+      exact_warp<QG>(a, *reinterpret_cast<ExactWarp *>(&sm.w[warp]), lane, FBLA_POS::x() * sp.xw + (warp - sw), FBLA_POS::nx() * sp.xw);
       return;
     }
+    const long long total = total_units<false>(a, hpr), per = ceil_div(total, (long long)FBLA_POS::nx() * sw);
+    gw = (long long)FBLA_POS::x() * sw + warp;
+    lo = gw * per;
+    hi = min(total, lo + per);
+  } else {  // the warp's share of all units by cost: its window sub-blocks first, then its groups
+    const Deal d = deal_of(a, hpr);
+    long long xlo, xhi;
+    gw = (long long)FBLA_POS::x() * sw + warp;
+    deal_range(d, gw, xlo, xhi, lo, hi);
+    exact_range<QG>(a, *reinterpret_cast<ExactWarp *>(&sm.w[warp]), lane, xlo, xhi, (int)gw);
+    __syncwarp();
   }
   StreamWarp<CB> &w = sm.w[warp];
   for (int i = lane; i < (int)sizeof(w.qst) / 4; i += 32) reinterpret_cast<uint32_t *>(w.qst)[i] = 0u;
@@ -651,8 +689,6 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
   }
   __syncwarp();
 
-  const long long total = total_units<false>(a, hpr), tw = (long long)FBLA_POS::nx() * sw, per = ceil_div(total, tw);
-  const long long gw = (long long)FBLA_POS::x() * sw + warp, lo = gw * per, hi = min(total, lo + per);
   // (before leaving, a warp invalidates its barriers: an executor may run another item on this CTA, whose initialisation
   // then meets no live barrier object)
   auto retire = [&]() {
@@ -734,7 +770,7 @@ __device__ __forceinline__ void coarse_item(const fbla_k_decode &a, uint8_t *sme
       ++more;
       if (sm.w[x].stage_vh[1] >= 0) break;
     }
-    fold_rows<QG, StreamWarp<CB>>(a.part + (size_t)(cta + v) * QG * PSTRIDE, &w.stage[r][0][0], warp + 1 < Sh::WARPS ? &sm.w[warp + 1].stage[0][0][0] : nullptr, more, lane, sizeof(StreamWarp<CB>) / sizeof(float));
+    fold_rows<QG, StreamWarp<CB>>(a.part + (size_t)(cta + v) * QG * PSTRIDE, &w.stage[r][0][0], warp + 1 < sw ? &sm.w[warp + 1].stage[0][0][0] : nullptr, more, lane, sizeof(StreamWarp<CB>) / sizeof(float));
   }
 }
 
@@ -744,12 +780,21 @@ __device__ __forceinline__ Slots slots_of(const fbla_k_decode &a, int vh) {
   const int hpr = a.kv_heads * a.vg;
   Slots s{0, -1, 0, -1};
   int n;
+  if (a.deal == FBLA_K_DEAL_COST) {  // a unit belongs to the warp whose cost share holds the start of its cost interval (deal_range)
+    const Deal d = deal_of(a, hpr);
+    long long off = head_offset<false>(a, hpr, vh, n);
+    if (n > 0) {
+      const long long div = d.P * (a.fold ? a.coarse_warps : 1);  // (a.fold: one row per CTA = coarse_warps consecutive warps)
+      s.c0 = (int)((d.wc * d.X + GROUP_COST * off) / div);
+      s.c1 = (int)((d.wc * d.X + GROUP_COST * (off + n - 1)) / div);
+    }
+    off = head_offset<true>(a, hpr, vh, n);
+    if (n > 0) { s.x0 = (int)(d.wc * off / d.P); s.x1 = (int)(d.wc * (off + n - 1) / d.P); }
+    return s;
+  }
   const Split sp = split_of(a, hpr);
   long long off = head_offset<false>(a, hpr, vh, n);
-  if (n > 0) {  // (a.fold: a CTA's sw streaming warps take sw consecutive runs of units and leave one folded row per CTA)
-    const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw) * (a.fold ? sp.sw : 1);
-    s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per);
-  }
+  if (n > 0) { const long long per = ceil_div(total_units<false>(a, hpr), (long long)a.coarse_ctas * sp.sw) * (a.fold ? sp.sw : 1); s.c0 = (int)(off / per); s.c1 = (int)((off + n - 1) / per); }
   off = head_offset<true>(a, hpr, vh, n);
   if (n > 0) { const long long per = ceil_div(total_units<true>(a, hpr), (long long)a.coarse_ctas * sp.xw); s.x0 = (int)(off / per); s.x1 = (int)((off + n - 1) / per); }
   return s;
@@ -1130,14 +1175,16 @@ __device__ __forceinline__ void refine_item(const fbla_k_decode &a, uint8_t *sme
 }
 
 // ---- merge: out = (sum 2^(m_c - R) o_c + sum do) / (sum 2^(m_c - R) l_c + sum dl), BF16 ---------------------------------
-// One CTA per output row (virtual head, query): thread (ch, sl) sums the partial rows sl, sl + 4, ... of its channel,
-// the four lanes of a channel are then added in a fixed order.
+// One CTA per output row (virtual head, query): thread (c4, sl) sums the partial rows sl, sl + 16, ... of channels
+// 4 c4 .. 4 c4 + 3, the sixteen sums of a channel are then added in a fixed order.
 template <int QG>
 __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem_raw) {
-  __shared__ float so[4][D], sl_[4];
+  constexpr int NS = 16, MJ = 6;  // row slices of the CTA; rows a thread has in flight (two CTAs share an SM's registers)
+  __shared__ float4 so[NS][32];
+  __shared__ float sl_[NS];
   __shared__ Slots ss;
   __shared__ int rr[3];
-  const int vh = FBLA_POS::x() / QG, qi = FBLA_POS::x() % QG, ch = FBLA_POS::tid() & 127, sl = FBLA_POS::tid() >> 7;
+  const int vh = FBLA_POS::x() / QG, qi = FBLA_POS::x() % QG, c4 = FBLA_POS::tid() & 31, sl = FBLA_POS::tid() >> 5;
   const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, b = vh / hpr, hir = vh - b * hpr;
   if (FBLA_POS::tid() == 0) ss = slots_of(a, vh);
   wait_previous_pass();
@@ -1152,43 +1199,63 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
   __syncthreads();
   const Slots s = ss;
   const float Rq = __ldcg(a.row_r + vh * QG + qi);
-  float O = 0.f, L = 0.f;
+  float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+  float L = 0.f;
   const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
-  // (a long sequence at a small batch gives a head ~200 partial rows: MJ loads per thread in flight keep the number of
-  // dependent round trips to memory small; the summation order is fixed by the loop alone)
-  constexpr int MJ = 12;
-  for (int i0 = sl; i0 < n; i0 += 4 * MJ) {
-    float m[MJ], l[MJ], o[MJ];
+  // (a long sequence at a small batch gives a head some tens of partial rows and a few hundred correction rows: NS * MJ
+  // rows of the CTA in flight keep the number of dependent round trips to memory small; the summation order is fixed
+  // by the loops alone)
+  for (int i0 = sl; i0 < n; i0 += NS * MJ) {
+    float m[MJ], l[MJ];
+    float4 o[MJ];
 #pragma unroll
     for (int j = 0; j < MJ; ++j) {
-      const int i = min(i0 + 4 * j, n - 1);
+      const int i = min(i0 + NS * j, n - 1);
       const float *p = i < nc ? coarse_slot(a, s.c0 + i, vh, qi) : window_slot(a, s.x0 + i - nc, vh, qi);
-      m[j] = __ldcg(p + D); l[j] = __ldcg(p + D + 1); o[j] = __ldcg(p + ch);
+      m[j] = __ldcg(p + D); l[j] = __ldcg(p + D + 1); o[j] = __ldcg(reinterpret_cast<const float4 *>(p) + c4);
     }
 #pragma unroll
     for (int j = 0; j < MJ; ++j)
-      if (i0 + 4 * j < n) {
+      if (i0 + NS * j < n) {
         const float e = m[j] == -FBLA_INF ? 0.f : ex2(m[j] - Rq);
-        L = fmaf(e, l[j], L); O = fmaf(e, o[j], O);
+        L = fmaf(e, l[j], L);
+        O.x = fmaf(e, o[j].x, O.x); O.y = fmaf(e, o[j].y, O.y); O.z = fmaf(e, o[j].z, O.z); O.w = fmaf(e, o[j].w, O.w);
       }
   }
   const int w0 = rr[0], w1 = rr[1];
-  for (int i0 = w0 + sl; i0 <= w1; i0 += 4 * MJ) {  // (one correction row per refine warp that met the head: up to a few hundred)
-    float l[MJ], o[MJ];
+  for (int i0 = w0 + sl; i0 <= w1; i0 += NS * MJ) {  // (one correction row per refine warp that met the head)
+    float l[MJ];
+    float4 o[MJ];
 #pragma unroll
     for (int j = 0; j < MJ; ++j) {
-      const float *p = a.dpart + ((size_t)(min(i0 + 4 * j, w1) + vh) * QG + qi) * PSTRIDE;
-      l[j] = __ldcg(p + D); o[j] = __ldcg(p + ch);
+      const float *p = a.dpart + ((size_t)(min(i0 + NS * j, w1) + vh) * QG + qi) * PSTRIDE;
+      l[j] = __ldcg(p + D); o[j] = __ldcg(reinterpret_cast<const float4 *>(p) + c4);
     }
 #pragma unroll
     for (int j = 0; j < MJ; ++j)
-      if (i0 + 4 * j <= w1) { L += l[j]; O += o[j]; }
+      if (i0 + NS * j <= w1) { L += l[j]; O.x += o[j].x; O.y += o[j].y; O.z += o[j].z; O.w += o[j].w; }
   }
-  so[sl][ch] = O;
-  if (ch == 0) sl_[sl] = L;
+  so[sl][c4] = O;
+  if (c4 == 0) sl_[sl] = L;
   __syncthreads();
-  if (sl == 0) {
-    const float Os = (so[0][ch] + so[1][ch]) + (so[2][ch] + so[3][ch]), Ls = (sl_[0] + sl_[1]) + (sl_[2] + sl_[3]);
+  if (FBLA_POS::tid() < D) {
+    const int ch = FBLA_POS::tid();
+    const float *col = reinterpret_cast<const float *>(so) + ch;  // so as [NS][128] floats
+    float os[NS];
+#pragma unroll
+    for (int x = 0; x < NS; ++x) os[x] = col[x * D];
+#pragma unroll
+    for (int w = 1; w < NS; w <<= 1)  // pairwise: ((0 + 1) + (2 + 3)) + ...
+#pragma unroll
+      for (int x = 0; x < NS; x += 2 * w) os[x] += os[x + w];
+    float ls[NS];
+#pragma unroll
+    for (int x = 0; x < NS; ++x) ls[x] = sl_[x];
+#pragma unroll
+    for (int w = 1; w < NS; w <<= 1)
+#pragma unroll
+      for (int x = 0; x < NS; x += 2 * w) ls[x] += ls[x + w];
+    const float Os = os[0], Ls = ls[0];
     const size_t row = (size_t)q_row(a, b, hir, qi);
     // a pass of this call reported a wait that gave up: some partial rows were never written, so the row is NaN, not a
     // plausible number (every pass has completed by now, so every report is visible)

@@ -23,8 +23,8 @@ typedef struct {
 // queries each (virtual head vh = kv_head_linear * vg + j owns queries j * qg .. j * qg + qg - 1 of its KV head).
 // Scratch arrays (all written before they are read; no initial contents needed):
 //   lse    [VH][nblocks][qg]  float  log2 mass of every closed sub-block under the coarse scores
-//   part   [2 TW + 2 VH][qg][132] float  (o[128], m, l) partials: slot w + vh for streaming warp w, coarse_ctas * coarse_warps + VH + x + vh
-//          for window warp x
+//   part   [2 TW + 2 VH][qg][132] float  (o[128], m, l) partials: slot w + vh for streaming warp (or, folded, CTA) w,
+//          coarse_ctas * coarse_warps + VH + x + vh for window warp x; TW = coarse_ctas * coarse_warps
 //   dpart  [RW + VH][qg][129] float  (dl, do[128]) corrections of refine warp w at slot w + vh
 //   row_r  [VH][qg]           float  log2 of the row's total coarse mass
 //   counts [VH][nslices]      int    selected sub-blocks per slice of 1024 sub-blocks
@@ -44,8 +44,7 @@ typedef struct {
   int hs, gs;            // units between KV heads and between groups
   int qg, vg;            // queries per virtual head, virtual heads per KV head
   int cb, fb;            // plane bits
-  int coarse_ctas, coarse_warps;  // persistent coarse CTAs; coarse_warps: 7 = seven streaming warps + one window warp per CTA,
-                                  // 8 = the CTA's eight warps split by the lengths (8 coarse_ctas bounds both layouts)
+  int coarse_ctas, coarse_warps;  // persistent coarse CTAs and their warps (8): how the work is dealt to them is `deal`
   int refine_ctas, refine_warps;  // RW = refine_ctas * refine_warps
   float sl, log2_tau;
   // Sequence shards (one GPU's part of a long context); shard_on 0: the whole cache. A shard processes the closed groups
@@ -55,8 +54,12 @@ typedef struct {
   int shard_on, sh_first, sh_count, sh_windows, phase;
   float *out_partial;  // [rows][FBLA_K_PSTRIDE] floats (phase 2)
   int status_cleared;  // 1: the launcher zeroes the status word on the stream before the first pass; 0: CTA 0 of the coarse pass does
-  int fold;            // 1: the coarse pass leaves one partial row per (CTA, virtual head) instead of one per (warp, virtual head)
+  short fold;          // 1: the coarse pass leaves one partial row per (CTA, virtual head) instead of one per (warp, virtual head)
+  short deal;          // how the coarse pass's warps share the work, FBLA_K_DEAL_*
 } fbla_k_decode;
+#define FBLA_K_DEAL_LENGTHS 0 /* a CTA's warps are split between windows and groups by the rows' lengths (short contexts) */
+#define FBLA_K_DEAL_FIXED 1   /* seven warps of a CTA stream groups, the eighth serves windows */
+#define FBLA_K_DEAL_COST 2    /* every warp takes an equal cost share of windows and groups (long contexts) */
 
 #define FBLA_K_PSTRIDE 132 /* floats of one partial row: o[128], then (m, l) or (dl) and padding */
 #define FBLA_K_SLICE 1024  /* sub-blocks per select slice */

@@ -50,15 +50,14 @@ __device__ int g_status = 0;  // nonzero: a bounded wait gave up in some launch 
 
 struct __align__(1024) Smem {
   uint8_t q[2][TILE];   // Qop of BF16 passes: the rows' q, BF16
-  uint8_t qp[2][TILE];  // Qop of closed passes (qhat, FP16), then P' of the same pass
+  uint8_t qp[2][TILE];  // Qop of closed passes: qhat as FP16 (at the very end: staging of the output rows)
   uint8_t k[TILE];      // Kop
   uint8_t v[TILE];      // V'
   uint8_t raw[RAW];     // the group's coarse records, then its fine records
   uint8_t meta[2][1024];  // the metadata of closed pass c in buffer c % 2, fetched two passes ahead
-  float ks[128], kb[128];  // the group's K steps and bases as FP32
-  float qscale[2][128], qbias[2][128];  // per row of a tile: the pass's score scale and bias (from the quantising lanes to the row's threads)
+  float qscale[2][2][128], qbias[2][2][128];  // [pass parity][tile][row]: the pass's score scale and bias (from the quantising lanes to the row's threads)
   float ex2[2][128][2];  // exchange between the two threads of a row: pass maximum, final sum
-  uint64_t bar_raw, bar_meta[2], bar_mf, bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
+  uint64_t bar_raw, bar_meta[2], bar_k, bar_v, bar_q[2], bar_s[2], bar_p[2], bar_o[2];
   uint32_t tmem_base;
   int abort;
 };
@@ -138,7 +137,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
   };
 
   if (tid == 0) {
-    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_meta[0], 1); mbar_init(&sm.bar_meta[1], 1); mbar_init(&sm.bar_mf, PT); mbar_init(&sm.bar_k, PT); mbar_init(&sm.bar_v, PT);
+    mbar_init(&sm.bar_raw, 1); mbar_init(&sm.bar_meta[0], 1); mbar_init(&sm.bar_meta[1], 1); mbar_init(&sm.bar_k, PT); mbar_init(&sm.bar_v, PT);
     for (int x = 0; x < 2; ++x) { mbar_init(&sm.bar_q[x], 256); mbar_init(&sm.bar_s[x], 1); mbar_init(&sm.bar_p[x], 256); mbar_init(&sm.bar_o[x], 1); }
     sm.abort = 0;
     mbar_init_fence();
@@ -195,8 +194,8 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           if (!(ok = wait(sm, &sm.bar_p[x], ph))) break;
           tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_f16(tmem + 256 + 128 * x, smem_desc(sm.qp[x], kk >> 2, kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
+          for (int kk = 0; kk < 8; ++kk)  // P' of token block kk: eight columns inside the tile's S columns (see the row threads)
+            mma_f16_ts(tmem + 256 + 128 * x, tmem + 128 * x + 64 * (kk >> 2) + 8 * (kk & 3), smem_desc(sm.v, kk >> 2, kk & 3), IDESC_F16, n > 0 || kk > 0);
           mma_commit(&sm.bar_o[x]);
         }
         if (!ok) break;
@@ -211,19 +210,10 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       bool closed;
       const int g = pass_group(n, closed);
       const uint32_t prev = (n - 1) & 1;
-      // ---- Kop (free once both tiles' S of the previous pass are complete; the row threads are then done with the previous
-      // pass's steps and bases too) ----
+      // ---- Kop (free once both tiles' S of the previous pass are complete) ----
       if (n > 0 && (!wait(sm, &sm.bar_s[0], prev) || !wait(sm, &sm.bar_s[1], prev))) break;
       if (closed) {
         if (!wait(sm, &sm.bar_meta[n & 1], (uint32_t)(n >> 1) & 1u)) break;
-        {  // K bases and steps as FP32 for the row threads: long before they ask for them
-          for (int ch = pt; ch < D; ch += PT) {
-            const uint8_t *m = sm.meta[n & 1] + 16 * (ch >> 2) + 2 * (ch & 3);
-            sm.kb[ch] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m));
-            sm.ks[ch] = bf16_to_f32(*reinterpret_cast<const uint16_t *>(m + 8));
-          }
-        }
-        mbar_arrive(&sm.bar_mf);
         if (!wait(sm, &sm.bar_raw, raw_uses++ & 1)) break;
       }
       if (closed) {
@@ -307,11 +297,6 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     const int i = valid ? R / qg : 0, hq = kh * qg + (valid ? R - i * qg : 0), pos = n0 + i, own = pos / G;
     const int tile_last = min(r0 + ROWS * X + ROWS, rows) - 1;                 // the tile's last row, if it has any
     const int tile_own = tile_last >= r0 + ROWS * X ? (n0 + tile_last / qg) / G : -1;  // closed group g concerns the tile iff g < tile_own
-    // byte offsets of the row's eight 16-byte chunks within a slab
-    uint32_t sw[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) sw[c] = r * 128 + ((c ^ (r & 7)) << 4);
-    uint8_t *const pt_ = sm.qp[X] + hf * SLAB;  // the thread's slab of the P' tile
     // quantiser lane: chunk qc of rows qrow0 + 2 it, it = 0 .. 7 (qrow0 % 8 is 0 or 1, so (row % 8) = (2 it) | (qrow0 & 1))
     const int qc = lane & 15, qrow0 = 16 * ((warp & 3) + 4 * hf) + (lane >> 4);
     const uint32_t qoff = (qc >> 3) * SLAB + qrow0 * 128, qcx = (uint32_t)((qc & 7) ^ (qrow0 & 1)) << 4;
@@ -330,93 +315,104 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     float m_run = -FBLA_INF, l_run = 0.f;  // l_run: this thread's tokens only
     const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
     const uint32_t tmem_s = tmem + 128 * X + 64 * hf + lane_base, tmem_o = tmem + 256 + 128 * X + 64 * hf + lane_base;
-    int mf_uses = 0;
     bool ok = true;
+    // Qop of pass np into the qhat tile (free once the S product of pass np - 1 is complete), then the tile's arrival for it
+    auto prepare = [&](int np) {
+      bool closed;
+      const int g = pass_group(np, closed);
+      if (closed) {
+        // the group's metadata (fetched two passes ahead; it is replaced only after both tiles have arrived for this pass)
+        ok &= __all_sync(FULL, wait(sm, &sm.bar_meta[np & 1], (uint32_t)(np >> 1) & 1u));
+        if (g < tile_own) {
+      // qhat for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r) written as FP16; four rows per batch, with
+      // every load ahead of the arithmetic and every store behind it, so that the rows' dependency chains overlap
+      // K bases and steps of channels 8 qc .. 8 qc + 7: per four channels, four BF16 bases then four BF16 steps
+      const uint4 ma = lds128(sm.meta[np & 1] + 32 * qc), mb = lds128(sm.meta[np & 1] + 32 * qc + 16);
+      const float4 b0 = make_float4(bf_lo(ma.x), bf_hi(ma.x), bf_lo(ma.y), bf_hi(ma.y)), s0 = make_float4(bf_lo(ma.z), bf_hi(ma.z), bf_lo(ma.w), bf_hi(ma.w));
+      const float4 b1 = make_float4(bf_lo(mb.x), bf_hi(mb.x), bf_lo(mb.y), bf_hi(mb.y)), s1 = make_float4(bf_lo(mb.z), bf_hi(mb.z), bf_lo(mb.w), bf_hi(mb.w));
+      const float2 mg = splat(MAGICF), ng = splat(-MAGICF);
+      const float sl127 = __fmul_rn(a.sl, 1.f / 127.f);
+      const bool h3 = lane & 8, h2 = lane & 4;
+#pragma unroll
+      for (int bt = 0; bt < 2; ++bt) {
+        uint4 qv[4];
+        uint32_t off[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int it = 4 * bt + k;
+          off[k] = qoff + 2 * it * 128 + (qcx ^ (((2 * it) & 7) << 4));
+          qv[k] = *reinterpret_cast<const uint4 *>(sm.q[X] + off[k]);
+        }
+        float amax[4], dot[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {  // the lane's share of max |z| and of the bias dot product
+          const float2 q0 = bf2(qv[k].x), q1 = bf2(qv[k].y), q2 = bf2(qv[k].z), q3 = bf2(qv[k].w);
+          const float2 z0 = mul2(q0, make_float2(s0.x, s0.y)), z1 = mul2(q1, make_float2(s0.z, s0.w));
+          const float2 z2 = mul2(q2, make_float2(s1.x, s1.y)), z3 = mul2(q3, make_float2(s1.z, s1.w));
+          amax[k] = fmaxf(fmaxf(fmaxf(fabsf(z0.x), fabsf(z0.y)), fmaxf(fabsf(z1.x), fabsf(z1.y))),
+                          fmaxf(fmaxf(fabsf(z2.x), fabsf(z2.y)), fmaxf(fabsf(z3.x), fabsf(z3.y))));
+          float2 d2 = fma2(q0, make_float2(b0.x, b0.y), mul2(q1, make_float2(b0.z, b0.w)));
+          d2 = fma2(q2, make_float2(b1.x, b1.y), fma2(q3, make_float2(b1.z, b1.w), d2));
+          dot[k] = d2.x + d2.y;
+        }
+        // over the 16 lanes of a row: the maxima by independent reductions (nonnegative floats order as integers), the
+        // dot products by a merging butterfly that leaves row 2 b3 + b2 of the batch in the lanes with bits 3, 2 = b3, b2
+#pragma unroll
+        for (int k = 0; k < 4; ++k) amax[k] = __uint_as_float(__reduce_max_sync(qmask, __float_as_uint(amax[k])));
+        const float e0 = (h3 ? dot[2] : dot[0]) + __shfl_xor_sync(FULL, h3 ? dot[0] : dot[2], 8);
+        const float e1 = (h3 ? dot[3] : dot[1]) + __shfl_xor_sync(FULL, h3 ? dot[1] : dot[3], 8);
+        float dsum = (h2 ? e1 : e0) + __shfl_xor_sync(FULL, h2 ? e0 : e1, 4);
+        dsum += __shfl_xor_sync(FULL, dsum, 2);
+        dsum += __shfl_xor_sync(FULL, dsum, 1);
+        if (!(lane & 3)) sm.qbias[np & 1][X][qrow0 + 2 * (4 * bt + ((lane >> 2) & 3))] = __fmul_rn(dsum, a.sl);
+        float rr[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float am = amax[k];
+          float rc;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(am));
+          rc = fmaf(fmaf(-am, rc, 1.f), rc, rc);
+          const float q0_ = __fmul_rn(127.f, rc);
+          rr[k] = am > 0.f ? fmaf(fmaf(-am, q0_, 127.f), rc, q0_) : 0.f;
+        }
+        uint4 out[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
+          const float2 rr2 = splat(rr[k]);
+          const float2 t0 = add2(fma2(mul2(bf2(qv[k].x), make_float2(s0.x, s0.y)), rr2, mg), ng);
+          const float2 t1 = add2(fma2(mul2(bf2(qv[k].y), make_float2(s0.z, s0.w)), rr2, mg), ng);
+          const float2 t2 = add2(fma2(mul2(bf2(qv[k].z), make_float2(s1.x, s1.y)), rr2, mg), ng);
+          const float2 t3 = add2(fma2(mul2(bf2(qv[k].w), make_float2(s1.z, s1.w)), rr2, mg), ng);
+          out[k] = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          *reinterpret_cast<uint4 *>(sm.qp[X] + off[k]) = out[k];
+          if (qc == 0) sm.qscale[np & 1][X][qrow0 + 2 * (4 * bt + k)] = __fmul_rn(amax[k], sl127);
+        }
+      }
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&sm.bar_q[X]);
+    };
+    prepare(0);
+    // Per pass: the softmax of S(n), whose P' goes back into tensor memory over the S columns it came from -- row r in lane
+    // r, tokens 2 c and 2 c + 1 of this thread's 64 in column c of its 64 S columns, so the O product takes P' as its
+    // tensor-memory operand and no shared memory is written -- then Qop of pass n + 1, while the O product of pass n runs.
+    // Products execute in the order they were issued: S(n + 1) overwrites P'(n) only after O(n) has read it.
     for (int n = 0; n < n_pass; ++n) {
       bool closed;
       const int g = pass_group(n, closed);
       const bool include = valid && (closed ? g < own : (g == 0 || g == own));
       const bool any = __any_sync(FULL, include);
-      // the previous pass's O product has read P' (the buffer qhat goes to) and O is stable
-      if (n > 0) ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n - 1) & 1));
-      if (closed) {
-        ok &= __all_sync(FULL, wait(sm, &sm.bar_mf, mf_uses++ & 1));
-        if (g < tile_own) {
-          // qhat for this group: z = q * step_K, r = fl(127 / max|z|), rint(z r) written as FP16; four rows per batch, with
-          // every load ahead of the arithmetic and every store behind it, so that the rows' dependency chains overlap
-          const float4 s0 = *reinterpret_cast<const float4 *>(&sm.ks[8 * qc]), s1 = *reinterpret_cast<const float4 *>(&sm.ks[8 * qc + 4]);
-          const float4 b0 = *reinterpret_cast<const float4 *>(&sm.kb[8 * qc]), b1 = *reinterpret_cast<const float4 *>(&sm.kb[8 * qc + 4]);
-          const float2 mg = splat(MAGICF), ng = splat(-MAGICF);
-          const float sl127 = __fmul_rn(a.sl, 1.f / 127.f);
-          const bool h3 = lane & 8, h2 = lane & 4;
-#pragma unroll
-          for (int bt = 0; bt < 2; ++bt) {
-            uint4 qv[4];
-            uint32_t off[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int it = 4 * bt + k;
-              off[k] = qoff + 2 * it * 128 + (qcx ^ (((2 * it) & 7) << 4));
-              qv[k] = *reinterpret_cast<const uint4 *>(sm.q[X] + off[k]);
-            }
-            float amax[4], dot[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {  // the lane's share of max |z| and of the bias dot product
-              const float2 q0 = bf2(qv[k].x), q1 = bf2(qv[k].y), q2 = bf2(qv[k].z), q3 = bf2(qv[k].w);
-              const float2 z0 = mul2(q0, make_float2(s0.x, s0.y)), z1 = mul2(q1, make_float2(s0.z, s0.w));
-              const float2 z2 = mul2(q2, make_float2(s1.x, s1.y)), z3 = mul2(q3, make_float2(s1.z, s1.w));
-              amax[k] = fmaxf(fmaxf(fmaxf(fabsf(z0.x), fabsf(z0.y)), fmaxf(fabsf(z1.x), fabsf(z1.y))),
-                              fmaxf(fmaxf(fabsf(z2.x), fabsf(z2.y)), fmaxf(fabsf(z3.x), fabsf(z3.y))));
-              float2 d2 = fma2(q0, make_float2(b0.x, b0.y), mul2(q1, make_float2(b0.z, b0.w)));
-              d2 = fma2(q2, make_float2(b1.x, b1.y), fma2(q3, make_float2(b1.z, b1.w), d2));
-              dot[k] = d2.x + d2.y;
-            }
-            // over the 16 lanes of a row: the maxima by independent reductions (nonnegative floats order as integers), the
-            // dot products by a merging butterfly that leaves row 2 b3 + b2 of the batch in the lanes with bits 3, 2 = b3, b2
-#pragma unroll
-            for (int k = 0; k < 4; ++k) amax[k] = __uint_as_float(__reduce_max_sync(qmask, __float_as_uint(amax[k])));
-            const float e0 = (h3 ? dot[2] : dot[0]) + __shfl_xor_sync(FULL, h3 ? dot[0] : dot[2], 8);
-            const float e1 = (h3 ? dot[3] : dot[1]) + __shfl_xor_sync(FULL, h3 ? dot[1] : dot[3], 8);
-            float dsum = (h2 ? e1 : e0) + __shfl_xor_sync(FULL, h2 ? e0 : e1, 4);
-            dsum += __shfl_xor_sync(FULL, dsum, 2);
-            dsum += __shfl_xor_sync(FULL, dsum, 1);
-            if (!(lane & 3)) sm.qbias[X][qrow0 + 2 * (4 * bt + ((lane >> 2) & 3))] = __fmul_rn(dsum, a.sl);
-            float rr[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float am = amax[k];
-              float rc;
-              asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(am));
-              rc = fmaf(fmaf(-am, rc, 1.f), rc, rc);
-              const float q0_ = __fmul_rn(127.f, rc);
-              rr[k] = am > 0.f ? fmaf(fmaf(-am, q0_, 127.f), rc, q0_) : 0.f;
-            }
-            uint4 out[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
-              const float2 rr2 = splat(rr[k]);
-              const float2 t0 = add2(fma2(mul2(bf2(qv[k].x), make_float2(s0.x, s0.y)), rr2, mg), ng);
-              const float2 t1 = add2(fma2(mul2(bf2(qv[k].y), make_float2(s0.z, s0.w)), rr2, mg), ng);
-              const float2 t2 = add2(fma2(mul2(bf2(qv[k].z), make_float2(s1.x, s1.y)), rr2, mg), ng);
-              const float2 t3 = add2(fma2(mul2(bf2(qv[k].w), make_float2(s1.z, s1.w)), rr2, mg), ng);
-              out[k] = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
-            }
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              *reinterpret_cast<uint4 *>(sm.qp[X] + off[k]) = out[k];
-              if (qc == 0) sm.qscale[X][qrow0 + 2 * (4 * bt + k)] = __fmul_rn(amax[k], sl127);
-            }
-          }
-        }
-      }
-      fence_async_smem();
-      mbar_arrive(&sm.bar_q[X]);
+      // S(n) is complete, and with it every product issued before: O of pass n - 1 is stable
       ok &= __all_sync(FULL, wait(sm, &sm.bar_s[X], n & 1));
       tc_fence_after();
       // softmax of the row over the pass's 128 tokens, by 16-token blocks; P' = fp16(2^(m_block - m_row) p)
       const int lim = (include ? (closed ? G : pos - g * G) : -1) - 64 * hf;  // this thread's tokens 0 .. lim are attended
-      const float mul1 = closed ? sm.qscale[X][r] : a.sl, add1 = closed ? sm.qbias[X][r] : 0.f;  // score = mul x + add, monotonic in x (mul >= 0)
+      const float mul1 = closed ? sm.qscale[n & 1][X][r] : a.sl, add1 = closed ? sm.qbias[n & 1][X][r] : 0.f;  // score = mul x + add, monotonic in x (mul >= 0)
       // sweep 1: the block maxima, from the raw sums
       float mbk[4];
       if (any) {
@@ -442,8 +438,9 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       }
       pair_sync();
       if (!any) {  // (warp-uniform, and the same in both warps of the pair) nothing to attend: P' = 0
+        const uint32_t zero[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
 #pragma unroll
-        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(pt_ + sw[c]) = make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < 4; ++c) tmem_st8(tmem_s + 8 * c, zero);
       } else {
         const float2 e = *reinterpret_cast<const float2 *>(&sm.ex2[X][r][0]);
         const float mp = fmaxf(e.x, e.y);
@@ -499,15 +496,15 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
               h[t] = pack_half2(pw.x, pw.y);
             }
             lacc = fma2(acc, w2, lacc);
-            *reinterpret_cast<uint4 *>(pt_ + sw[4 * cq + 2 * hb]) = make_uint4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<uint4 *>(pt_ + sw[4 * cq + 2 * hb + 1]) = make_uint4(h[4], h[5], h[6], h[7]);
+            tmem_st8(tmem_s + 16 * cq + 8 * hb, h);  // (over S columns this thread has already taken into registers)
           }
         }
         l_run += lacc.x + lacc.y;
       }
-      fence_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&sm.bar_p[X]);
+      if (n + 1 < n_pass) prepare(n + 1);
     }
     ok &= __all_sync(FULL, wait(sm, &sm.bar_o[X], (n_pass - 1) & 1));
     tc_fence_after();
@@ -544,7 +541,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
   if (tid == 0) {  // no live barrier object is left behind: an executor may run another item on this CTA next
-    mbar_inval(&sm.bar_raw); mbar_inval(&sm.bar_meta[0]); mbar_inval(&sm.bar_meta[1]); mbar_inval(&sm.bar_mf); mbar_inval(&sm.bar_k); mbar_inval(&sm.bar_v);
+    mbar_inval(&sm.bar_raw); mbar_inval(&sm.bar_meta[0]); mbar_inval(&sm.bar_meta[1]); mbar_inval(&sm.bar_k); mbar_inval(&sm.bar_v);
     for (int x = 0; x < 2; ++x) { mbar_inval(&sm.bar_q[x]); mbar_inval(&sm.bar_s[x]); mbar_inval(&sm.bar_p[x]); mbar_inval(&sm.bar_o[x]); }
   }
 }

@@ -38,13 +38,15 @@ def test_decode_at_equals_decode(ours, mode, B, QH, KH, N, tau, seed):
 
 
 @pytest.mark.parametrize("mode", MODES)
-def test_decode_at_equals_decode_under_a_large_capacity(ours, mode):
-    """Rows far shorter than the cache's capacity: the coarse pass picks how its warps are split from the capacity for
-    both calls, so host-length and device-length decodes still run the same kernels and agree bit for bit."""
+@pytest.mark.parametrize("capacity", [8192, 40000])
+def test_decode_at_equals_decode_under_a_large_capacity(ours, mode, capacity):
+    """Rows far shorter than the cache's capacity: the coarse pass picks how its warps share the work from the capacity
+    for both calls (8192: split by the lengths, 40000: windows and groups dealt to every warp by cost -- here with far
+    fewer units than warps), so host-length and device-length decodes still run the same kernels and agree bit for bit."""
     B, QH, KH, N = 2, 8, 2, 700
     q, k, v = datagen.uneven_case(47, B, QH, KH, N)
     qd, kd, vd = gu.bf16_tensor(q), gu.bf16_tensor(k), gu.bf16_tensor(v)
-    c = ours.encode(kd, vd, mode, capacity=8192)
+    c = ours.encode(kd, vd, mode, capacity=capacity)
     want = ours.decode(c, qd, tau=1e-3)
     got = ours.decode_at(c, qd, _i32(N), tau=1e-3)
     small = ours.decode(ours.encode(kd, vd, mode, capacity=1024), qd, tau=1e-3)  # (the split by the lengths)

@@ -113,7 +113,8 @@ def test_linked_step_with_the_peer_data_already_delivered(mode):
     # what rank 0 stored for its peer: its own masses and sums in slot 0 of the peer's mailbox, stamped 1
     assert box1[256:264].view(torch.int32)[0].item() == 1 and box1[512:520].view(torch.int32)[0].item() == 1
     assert torch.equal(box1[off_mass_in:off_mass_in + rows * 4].view(torch.float32), masses[:rows])
-    assert torch.equal(box1[off_part_in:off_part_in + rows * 132 * 4].view(torch.float32), partials[0])
+    sent = box1[off_part_in:off_part_in + rows * 132 * 4].view(torch.float32).view(rows, 132)
+    assert torch.equal(sent[:, :129], partials[0].view(rows, 132)[:, :129])  # o[128] and l; the row's last three floats are padding
 
 
 def test_linked_step_gives_up_on_a_silent_peer():

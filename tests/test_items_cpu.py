@@ -18,7 +18,7 @@ ENTRIES = [
     ("fbla::close_item<3, 3>", "fbla_k_prefill", 256), ("fbla::close_item<4, 2>", "fbla_k_prefill", 256), ("fbla::finish_item", "fbla_k_prefill", 256),
     ("fbla::attend_rows_item<3, 3>", "fbla_k_prefill", 256), ("fbla::attend_rows_item<4, 2>", "fbla_k_prefill", 256),
     ("fbla::tc::attend_tc_item<3, 3>", "fbla_k_prefill", 672), ("fbla::tc::attend_tc_item<4, 2>", "fbla_k_prefill", 672),
-    ("fbla::coarse_item<3, 3, 4, false>", "fbla_k_decode", 256), ("fbla::coarse_item<4, 2, 2, true>", "fbla_k_decode", 256), ("fbla::coarse_item<4, 2, 1, false>", "fbla_k_decode", 256),
+    ("fbla::coarse_item<3, 3, 4, 2>", "fbla_k_decode", 256), ("fbla::coarse_item<4, 2, 2, 0>", "fbla_k_decode", 256), ("fbla::coarse_item<4, 2, 1, 1>", "fbla_k_decode", 256),
     ("fbla::select_item<4>", "fbla_k_decode", 256), ("fbla::refine_item<3, 3, 4>", "fbla_k_decode", 384), ("fbla::refine_item<4, 2, 2>", "fbla_k_decode", 384),
     ("fbla::merge_item<4>", "fbla_k_decode", 512),
     ("fbla::qkv_token_item<true>", "fbla_k_token", 256), ("fbla::qkv_token_item<false>", "fbla_k_token", 256),
