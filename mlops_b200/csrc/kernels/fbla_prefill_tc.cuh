@@ -332,64 +332,48 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
       const float4 b1 = make_float4(bf_lo(mb.x), bf_hi(mb.x), bf_lo(mb.y), bf_hi(mb.y)), s1 = make_float4(bf_lo(mb.z), bf_hi(mb.z), bf_lo(mb.w), bf_hi(mb.w));
       const float2 mg = splat(MAGICF), ng = splat(-MAGICF);
       const float sl127 = __fmul_rn(a.sl, 1.f / 127.f);
-      const bool h3 = lane & 8, h2 = lane & 4;
+      const bool h3 = lane & 8;
 #pragma unroll
-      for (int bt = 0; bt < 2; ++bt) {
-        uint4 qv[4];
-        uint32_t off[4];
+      for (int bt = 0; bt < 4; ++bt) {  // two rows per batch; their z = q * step stay in registers for the second sweep
+        float2 z[2][4];
+        uint32_t off[2];
+        float amax[2], dot[2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int it = 4 * bt + k;
+        for (int k = 0; k < 2; ++k) {  // the lane's share of max |z| and of the bias dot product
+          const int it = 2 * bt + k;
           off[k] = qoff + 2 * it * 128 + (qcx ^ (((2 * it) & 7) << 4));
-          qv[k] = *reinterpret_cast<const uint4 *>(sm.q[X] + off[k]);
-        }
-        float amax[4], dot[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {  // the lane's share of max |z| and of the bias dot product
-          const float2 q0 = bf2(qv[k].x), q1 = bf2(qv[k].y), q2 = bf2(qv[k].z), q3 = bf2(qv[k].w);
-          const float2 z0 = mul2(q0, make_float2(s0.x, s0.y)), z1 = mul2(q1, make_float2(s0.z, s0.w));
-          const float2 z2 = mul2(q2, make_float2(s1.x, s1.y)), z3 = mul2(q3, make_float2(s1.z, s1.w));
-          amax[k] = fmaxf(fmaxf(fmaxf(fabsf(z0.x), fabsf(z0.y)), fmaxf(fabsf(z1.x), fabsf(z1.y))),
-                          fmaxf(fmaxf(fabsf(z2.x), fabsf(z2.y)), fmaxf(fabsf(z3.x), fabsf(z3.y))));
+          const uint4 qv = *reinterpret_cast<const uint4 *>(sm.q[X] + off[k]);
+          const float2 q0 = bf2(qv.x), q1 = bf2(qv.y), q2 = bf2(qv.z), q3 = bf2(qv.w);
+          z[k][0] = mul2(q0, make_float2(s0.x, s0.y)); z[k][1] = mul2(q1, make_float2(s0.z, s0.w));
+          z[k][2] = mul2(q2, make_float2(s1.x, s1.y)); z[k][3] = mul2(q3, make_float2(s1.z, s1.w));
+          amax[k] = fmaxf(fmaxf(fmaxf(fabsf(z[k][0].x), fabsf(z[k][0].y)), fmaxf(fabsf(z[k][1].x), fabsf(z[k][1].y))),
+                          fmaxf(fmaxf(fabsf(z[k][2].x), fabsf(z[k][2].y)), fmaxf(fabsf(z[k][3].x), fabsf(z[k][3].y))));
           float2 d2 = fma2(q0, make_float2(b0.x, b0.y), mul2(q1, make_float2(b0.z, b0.w)));
           d2 = fma2(q2, make_float2(b1.x, b1.y), fma2(q3, make_float2(b1.z, b1.w), d2));
           dot[k] = d2.x + d2.y;
         }
-        // over the 16 lanes of a row: the maxima by independent reductions (nonnegative floats order as integers), the
-        // dot products by a merging butterfly that leaves row 2 b3 + b2 of the batch in the lanes with bits 3, 2 = b3, b2
+        // over the 16 lanes of a row: the maxima by reductions (nonnegative floats order as integers), the dot products by
+        // a merging butterfly that leaves row b3 of the batch in the lanes with bit 3 = b3
 #pragma unroll
-        for (int k = 0; k < 4; ++k) amax[k] = __uint_as_float(__reduce_max_sync(qmask, __float_as_uint(amax[k])));
-        const float e0 = (h3 ? dot[2] : dot[0]) + __shfl_xor_sync(FULL, h3 ? dot[0] : dot[2], 8);
-        const float e1 = (h3 ? dot[3] : dot[1]) + __shfl_xor_sync(FULL, h3 ? dot[1] : dot[3], 8);
-        float dsum = (h2 ? e1 : e0) + __shfl_xor_sync(FULL, h2 ? e0 : e1, 4);
+        for (int k = 0; k < 2; ++k) amax[k] = __uint_as_float(__reduce_max_sync(qmask, __float_as_uint(amax[k])));
+        float dsum = (h3 ? dot[1] : dot[0]) + __shfl_xor_sync(FULL, h3 ? dot[0] : dot[1], 8);
+        dsum += __shfl_xor_sync(FULL, dsum, 4);
         dsum += __shfl_xor_sync(FULL, dsum, 2);
         dsum += __shfl_xor_sync(FULL, dsum, 1);
-        if (!(lane & 3)) sm.qbias[np & 1][X][qrow0 + 2 * (4 * bt + ((lane >> 2) & 3))] = __fmul_rn(dsum, a.sl);
-        float rr[4];
+        if (!(lane & 7)) sm.qbias[np & 1][X][qrow0 + 2 * (2 * bt + ((lane >> 3) & 1))] = __fmul_rn(dsum, a.sl);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < 2; ++k) {
           const float am = amax[k];
           float rc;
           asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(am));
           rc = fmaf(fmaf(-am, rc, 1.f), rc, rc);
           const float q0_ = __fmul_rn(127.f, rc);
-          rr[k] = am > 0.f ? fmaf(fmaf(-am, q0_, 127.f), rc, q0_) : 0.f;
-        }
-        uint4 out[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
           // rint(z r) as the exact float (t - 1.5 * 2^23), then FP16 (an integer of magnitude <= 127: exact)
-          const float2 rr2 = splat(rr[k]);
-          const float2 t0 = add2(fma2(mul2(bf2(qv[k].x), make_float2(s0.x, s0.y)), rr2, mg), ng);
-          const float2 t1 = add2(fma2(mul2(bf2(qv[k].y), make_float2(s0.z, s0.w)), rr2, mg), ng);
-          const float2 t2 = add2(fma2(mul2(bf2(qv[k].z), make_float2(s1.x, s1.y)), rr2, mg), ng);
-          const float2 t3 = add2(fma2(mul2(bf2(qv[k].w), make_float2(s1.z, s1.w)), rr2, mg), ng);
-          out[k] = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          *reinterpret_cast<uint4 *>(sm.qp[X] + off[k]) = out[k];
-          if (qc == 0) sm.qscale[np & 1][X][qrow0 + 2 * (4 * bt + k)] = __fmul_rn(amax[k], sl127);
+          const float2 rr2 = splat(am > 0.f ? fmaf(fmaf(-am, q0_, 127.f), rc, q0_) : 0.f);
+          const float2 t0 = add2(fma2(z[k][0], rr2, mg), ng), t1 = add2(fma2(z[k][1], rr2, mg), ng);
+          const float2 t2 = add2(fma2(z[k][2], rr2, mg), ng), t3 = add2(fma2(z[k][3], rr2, mg), ng);
+          *reinterpret_cast<uint4 *>(sm.qp[X] + off[k]) = make_uint4(pack_half2(t0.x, t0.y), pack_half2(t1.x, t1.y), pack_half2(t2.x, t2.y), pack_half2(t3.x, t3.y));
+          if (qc == 0) sm.qscale[np & 1][X][qrow0 + 2 * (2 * bt + k)] = __fmul_rn(am, sl127);
         }
       }
         }
@@ -463,7 +447,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           if (need) { l_run *= al; m_run = mp; }
         }
         // sweep 2: the integer P blocks times their weights
-        const float2 mul = splat(mul1), add = splat(add1), c255 = splat(255.f), mg = splat(MAGICF), ng = splat(-MAGICF);
+        const float2 mul = splat(mul1), c255 = splat(255.f), mg = splat(MAGICF), ng = splat(-MAGICF);
         float2 lacc = make_float2(0.f, 0.f);
 #pragma unroll
         for (int cq = 0; cq < 2; ++cq) {
@@ -473,11 +457,12 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
           for (int hb = 0; hb < 2; ++hb) {
             const int t0 = 32 * cq + 16 * hb;
             const float mb = mbk[2 * cq + hb];
-            const float2 nm = splat(mb == -FBLA_INF ? 0.f : -mb), w2 = splat(mb == -FBLA_INF ? 0.f : ex2(mb - m_run));
+            // score - block maximum in one step: mul x + (add - m_block)
+            const float2 addm = splat(mb == -FBLA_INF ? add1 : add1 - mb), w2 = splat(mb == -FBLA_INF ? 0.f : ex2(mb - m_run));
             float2 sc[8];
 #pragma unroll
             for (int t = 0; t < 8; ++t)
-              sc[t] = fma2(make_float2(__uint_as_float(x[16 * hb + 2 * t]), __uint_as_float(x[16 * hb + 2 * t + 1])), mul, add);
+              sc[t] = fma2(make_float2(__uint_as_float(x[16 * hb + 2 * t]), __uint_as_float(x[16 * hb + 2 * t + 1])), mul, addm);
             if (lim < t0 + 15) {  // the causal edge (or a row that does not attend to this group)
 #pragma unroll
               for (int t = 0; t < 8; ++t) {
@@ -489,8 +474,7 @@ __device__ __forceinline__ void attend_tc_item(const fbla_k_prefill &a, uint8_t 
             float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
-              const float2 d = add2(sc[t], nm);
-              const float2 pf = add2(fma2(make_float2(ex2(d.x), ex2(d.y)), c255, mg), ng);
+              const float2 pf = add2(fma2(make_float2(ex2(sc[t].x), ex2(sc[t].y)), c255, mg), ng);
               acc = add2(acc, pf);
               const float2 pw = mul2(pf, w2);
               h[t] = pack_half2(pw.x, pw.y);

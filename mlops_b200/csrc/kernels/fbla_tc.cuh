@@ -16,10 +16,6 @@ __device__ __forceinline__ uint64_t smem_desc_at(const void *tile_base, uint32_t
 }
 constexpr uint32_t IDESC_F16 = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);           // D FP32, A / B FP16, M 128, N 128
 constexpr uint32_t IDESC_BF16 = IDESC_F16 | (1u << 7) | (1u << 10);                                // A / B BF16
-// 8-bit integer products: D s32, A u8, B s8 (b_signed) or u8, M 128, N columns
-__host__ __device__ constexpr uint32_t idesc_i8(int n, bool b_signed) {
-  return (2u << 4) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
-}
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, bool accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
