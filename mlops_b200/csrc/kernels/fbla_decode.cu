@@ -178,8 +178,8 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
 // How the coarse CTAs' warps share the work (see split_of, deal_of), from the tokens a row has at most:
 //   by the lengths when the BF16 windows would get three or more of a CTA's eight warps (contexts up to about 4 700 tokens);
 //   by cost -- every warp an equal share of windows and groups -- when that shortens a warp's work by more than the ~5 %
-//   that eight streaming warps lose against seven and a window warp: contexts from about 20K (3+3) / 27K (4+2) tokens
-//   (measured on B200, by cost against seven + one: batch 1 x 128K tokens 80.0 -> 75.3 us per step in 3+3 and 65.7 -> 63.7
+//   that eight streaming warps lose against seven and a window warp: contexts from about 20K (3+3) / 34K (4+2) tokens
+//   (measured on B200, by cost against seven + one: batch 1 x 128K tokens 80.0 -> 75.3 us per step in 3+3 and 65.7 -> 61.6
 //   in 4+2, batch 64 x 1K..64K 2.07 -> 2.02 ms, but batch 8 x 16K 120.0 -> 123.9);
 //   seven streaming warps and one window warp per CTA between the two.
 extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
@@ -187,7 +187,7 @@ extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
   const long long groups = (tokens + fbla::G - 1) / fbla::G, S = groups > 2 ? groups - 2 : 0;
   const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : 2 * fbla::SBG;  // (a full open window: the choice is monotone in tokens)
   const bool by_lengths = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
-  const int wc = a->cb == 3 ? 6 : 8;  // (deal_of's cost of a window sub-block, a group's being 8)
+  const int wc = a->cb == 3 ? 6 : 10;  // (deal_of's cost of a window sub-block, a group's being 8)
   a->coarse_warps = total;
   a->deal = by_lengths ? FBLA_K_DEAL_LENGTHS : 8 * S > 13 * wc * W ? FBLA_K_DEAL_COST : FBLA_K_DEAL_FIXED;
   // Folding the warps' partial rows per CTA costs the coarse pass a barrier and a few microseconds at its very end and saves

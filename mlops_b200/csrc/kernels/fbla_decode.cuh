@@ -205,19 +205,21 @@ static_assert(sizeof(ExactWarp) <= sizeof(StreamWarp<3>) && sizeof(ExactWarp) <=
 // FBLA_K_DEAL_FIXED (contexts in between): the same with xw = 1, whatever the lengths.
 //
 // FBLA_K_DEAL_COST (long contexts): no warp is set aside. All units form one list, window sub-blocks first, then the groups, each
-// with a cost in eighths of a group's time (a window sub-block takes a warp about as long as a 4-bit group and three
-// quarters of a 3-bit one); every warp of the grid takes the units whose cost interval starts inside its equal share
-// [w P, (w + 1) P) of the total, serves its window sub-blocks and then streams its groups. A share is at least one
-// unit's cost, so consecutive units lie in the same or in consecutive warps. At batch 1 and 128K tokens a warp then
-// streams 7 groups instead of 8.
+// with a cost in eighths of a group's time. A window sub-block costs 6 beside 3-bit groups and 10 beside 4-bit ones:
+// measured, batch 1 x 128K tokens, us per step for costs 4 / 5 / 6 / 7 / 8 in 3+3: 81.3 / 72.2 / 72.1 / 71.3 / 72.7, for
+// 5 / 6 / 8 / 10 / 12 / 14 in 4+2: 72.8 / 70.1 / 61.7 / 59.6 / 61.4 / 59.7 (a CTA whose eight warps all serve windows
+// runs them slower than one window warp among streaming ones, and 4-bit groups are the faster ones). Every warp of the
+// grid takes the units whose cost interval starts inside its equal share [w P, (w + 1) P) of the total, serves its
+// window sub-blocks and then streams its groups. A share is at least one unit's cost, so consecutive units lie in the
+// same or in consecutive warps. At batch 1 and 128K tokens a warp then streams 7 groups instead of 8.
 struct Deal { long long S, X, P; int wc; };  // groups, window sub-blocks, cost share per warp, cost of a window sub-block
 constexpr int GROUP_COST = 8;
 __device__ __forceinline__ Deal deal_of(const fbla_k_decode &a, int hpr) {
   Deal d;
   d.S = total_units<false>(a, hpr);
   d.X = total_units<true>(a, hpr);
-  d.wc = a.cb == 3 ? 6 : 8;
-  d.P = max((long long)GROUP_COST, ceil_div(GROUP_COST * d.S + d.wc * d.X, (long long)a.coarse_ctas * a.coarse_warps));
+  d.wc = a.cb == 3 ? 6 : 10;
+  d.P = max((long long)max(GROUP_COST, d.wc), ceil_div(GROUP_COST * d.S + d.wc * d.X, (long long)a.coarse_ctas * a.coarse_warps));
   return d;
 }
 // the units of warp w: window sub-blocks [xlo, xhi), groups [lo, hi)

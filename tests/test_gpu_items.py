@@ -57,11 +57,11 @@ def _write_ranges(lib, passes, n, arg):
 
 
 @pytest.mark.parametrize("mode,QH,KH,N,cap,ctas", [("4+2", 8, 2, 3000, 4096, None), ("3+3", 4, 4, 3000, 4096, None),
-                                                     # capacities beyond ~27 000 tokens take the coarse kernel that deals windows and groups
+                                                     # capacities beyond ~34 000 tokens take the coarse kernel that deals windows and groups
                                                      # to every warp by cost; ctas = 3: every pass as a persistent loop of three CTAs
                                                      # walking its items back to back
                                                      ("4+2", 8, 2, 9000, 16384, None), ("3+3", 8, 2, 9000, 16384, 3), ("4+2", 4, 4, 3000, 4096, 3),
-                                                     ("4+2", 8, 2, 9000, 32768, 3), ("3+3", 8, 2, 9000, 32768, None)])
+                                                     ("4+2", 8, 2, 9000, 40960, 3), ("3+3", 8, 2, 9000, 32768, None)])
 def test_decode_plan_equals_decode_at(ours, mode, QH, KH, N, cap, ctas):
     B = 2
     q, k, v = datagen.baseline_case(41, B, QH, KH, N)
