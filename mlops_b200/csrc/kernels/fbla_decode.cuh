@@ -1185,22 +1185,17 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
   __shared__ float4 so[NS][32];
   __shared__ float sl_[NS];
   __shared__ Slots ss;
-  __shared__ int rr[3];
   const int vh = FBLA_POS::x() / QG, qi = FBLA_POS::x() % QG, c4 = FBLA_POS::tid() & 31, sl = FBLA_POS::tid() >> 5;
   const int hpr = a.kv_heads * a.vg, vheads = a.batch * hpr, b = vh / hpr, hir = vh - b * hpr;
-  if (FBLA_POS::tid() == 0) ss = slots_of(a, vh);
-  wait_previous_pass();
-  if (FBLA_POS::tid() == 0) {
-    const int it0 = __ldcg(a.item_off + vh), it1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
-    rr[0] = 0; rr[1] = -1;
-    if (it1 > it0) {
-      const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
-      rr[0] = it0 / per; rr[1] = (it1 - 1) / per;
-    }
-  }
+  if (FBLA_POS::tid() == 0) ss = slots_of(a, vh);  // (from the lengths alone: before the previous pass has completed)
   __syncthreads();
+  wait_previous_pass();
   const Slots s = ss;
+  // every load that does not depend on another is issued here, ahead of the rows: the head's range of correction rows,
+  // the row's mass, the status word
+  const int it0 = __ldcg(a.item_off + vh), it1 = __ldcg(a.item_off + vh + 1), total = __ldcg(a.item_off + vheads);
   const float Rq = __ldcg(a.row_r + vh * QG + qi);
+  const int status = a.status ? __ldcg(a.status) : 0;
   float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
   float L = 0.f;
   const int nc = s.c1 - s.c0 + 1, nx = s.x1 - s.x0 + 1, n = nc + nx;
@@ -1224,7 +1219,11 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
         O.x = fmaf(e, o[j].x, O.x); O.y = fmaf(e, o[j].y, O.y); O.z = fmaf(e, o[j].z, O.z); O.w = fmaf(e, o[j].w, O.w);
       }
   }
-  const int w0 = rr[0], w1 = rr[1];
+  int w0 = 0, w1 = -1;  // the refine warps whose runs of items met this head
+  if (it1 > it0) {
+    const int per = (int)ceil_div(total, (long long)a.refine_ctas * a.refine_warps);
+    w0 = it0 / per; w1 = (it1 - 1) / per;
+  }
   for (int i0 = w0 + sl; i0 <= w1; i0 += NS * MJ) {  // (one correction row per refine warp that met the head)
     float l[MJ];
     float4 o[MJ];
@@ -1261,7 +1260,7 @@ __device__ __forceinline__ void merge_item(const fbla_k_decode &a, uint8_t *smem
     const size_t row = (size_t)q_row(a, b, hir, qi);
     // a pass of this call reported a wait that gave up: some partial rows were never written, so the row is NaN, not a
     // plausible number (every pass has completed by now, so every report is visible)
-    const bool failed = a.status && __ldcg(a.status) != 0;
+    const bool failed = status != 0;
     const float nan = __int_as_float(0x7fc00000);
     if (a.out_partial) {  // a shard's share of the row, in units of 2^-R: summed over the shards before the division
       a.out_partial[row * PSTRIDE + ch] = failed ? nan : Os;

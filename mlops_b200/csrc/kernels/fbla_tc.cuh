@@ -1,4 +1,4 @@
-// Blackwell tensor-core plumbing shared by the prefill and the decode: tcgen05.mma / commit / fences, tensor-memory
+// Blackwell tensor-core plumbing of the prefill attention: tcgen05.mma / commit / fences, tensor-memory
 // loads and stores of one 32-lane x 32-column block per warp, shared-memory operand descriptors (K-major, 128-byte
 // swizzle: 8-row x 128-byte atoms, 16-byte chunk c of row r stored at c ^ (r % 8)), and the polling primitive of the
 // bounded mbarrier waits.
