@@ -55,6 +55,12 @@ WORKLOADS = {
     "seqsplit_256k": dict(kind="seqsplit", tokens=262144, name="sequence-split decode B1 32q/8kv ctx262144 3+3 (BASELINE configs[2])"),
     "seqsplit_1m": dict(kind="seqsplit", tokens=1 << 20, name="sequence-split decode B1 32q/8kv ctx1048576 3+3 (BASELINE configs[2])"),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from the ncu captures summarised
+# under profiles/ (1 GPU); reported with their source, never as a measurement of the run that prints them
+NCU_TRAFFIC = {
+    "decode_128k": dict(kernel="coarse_kernel<3,3,4,2>", bytes=113178368, file="profiles/decode_b1_ctx128k_3p3_launches.md"),
+    "decode_b8": dict(kernel="refine_kernel<4,2,4>", bytes=164004352, file="profiles/decode_b8_ctx16k_4p2_launches.md"),
+}
 SUBS = ["decode_128k_4p2", "decode_b8", "prefill_b4", "serving_b64"]
 MIN_TIMED_S = 0.5
 
@@ -342,8 +348,12 @@ def decode_record(cfg, rec, n_gpus):
     per_step = rec["ms_per_step"] * 1e-3
     achieved = rec["abytes"] / per_step / 1e9
     peak = rec["peak"] * rec["world"]
-    roof = dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
-                traffic_source="not captured in this run; ncu captures of the same command are summarised under profiles/",
+    # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum): not measured in this run --
+    # a profiler cannot run inside the timed program -- but taken from the ncu capture of this workload on one GPU
+    captured = NCU_TRAFFIC.get(cfg.get("key")) if n_gpus == 1 else None
+    roof = dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=captured["bytes"] if captured else None,
+                traffic_source=(f"ncu capture of {captured['kernel']} on this workload, one launch, not this run: {captured['file']}" if captured
+                                else "not captured for this workload; ncu captures of other workloads are summarised under profiles/"),
                 peak_kind=rec["peak_kind"] + (f", x {rec['world']} GPUs" if rec["world"] > 1 else ""),
                 kernel="decode call: coarse, select, refine, merge", algorithmic_bytes=rec["abytes"], bytes_parts=rec["parts"])
     if rec["pass_us"]:
@@ -631,7 +641,7 @@ def run_reference(args):
 
 # ---- driver -------------------------------------------------------------------------------------------------------------------------
 def run_workload(D, name, args, headline):
-    cfg = WORKLOADS[name]
+    cfg = dict(WORKLOADS[name], key=name)
     if cfg["kind"] == "decode":
         rec = run_decode(D, cfg, args, headline)
         return None if rec is None else (decode_record(cfg, rec, D.world), rec)
