@@ -196,6 +196,14 @@ extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
   a->fold = !by_lengths && a->batch * a->kv_heads * a->vg <= 32;
 }
 
+extern "C" void fbla_k_decode_split_of(int cb, int batch, int kv_heads, int vg, long long tokens, int *deal, int *fold) {
+  fbla_k_decode a = {};
+  a.cb = cb; a.batch = batch; a.kv_heads = kv_heads; a.vg = vg;
+  fbla_k_decode_split(&a, tokens);
+  *deal = a.deal;
+  *fold = a.fold;
+}
+
 extern "C" cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStream_t stream) {
   using namespace fbla;
   if (a->cb == 3) {

@@ -71,6 +71,8 @@ FBLA_HOST_API(cudaError_t fbla_k_decode_launch(const fbla_k_decode *a, cudaStrea
 FBLA_HOST_API(cudaError_t fbla_k_decode_pass_launch(const fbla_k_decode *a, int pass, cudaStream_t stream);)
 // chooses the split of the coarse CTAs' warps for rows of about `tokens` tokens (after fbla_k_decode_shape; the scratch layout holds either)
 FBLA_HOST_API(void fbla_k_decode_split(fbla_k_decode *a, long long tokens);)
+// the same choice for a shape given by its numbers (pure host arithmetic: no device is touched): deal and fold as fbla_k_decode_split sets them
+FBLA_HOST_API(void fbla_k_decode_split_of(int cb, int batch, int kv_heads, int vg, long long tokens, int *deal, int *fold);)
 // out[row][ch] = bf16(partial[row][ch] / partial[row][128]) for rows rows of FBLA_K_PSTRIDE floats
 // total[i] = log2 sum over shards of 2^mass[s][i]
 FBLA_HOST_API(cudaError_t fbla_k_total_mass_launch(const float *mass, float *total, int shards, int rows, cudaStream_t stream);)
