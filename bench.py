@@ -496,30 +496,41 @@ def run_prefill(D, cfg, args):
 
     ms, blocks, clocks = timed_blocks(D, step, steps, min(args.warmup, 5))
     out_host = torch.empty(qd.shape, dtype=torch.bfloat16).pin_memory()
-    # end to end: the three inputs come from pinned host memory in batch-row pieces on a second stream, so that the copy of
-    # piece i + 1 overlaps the prefill of piece i; the output goes back piece by piece
-    copy_stream = torch.cuda.Stream()
+    # end to end: a three-stage pipeline over batch rows and steps. The inputs come from pinned host memory row by row on a
+    # copy stream into one of two sets of device buffers (so the next step's copies do not wait for this step's kernels),
+    # the prefill of row b starts when its three inputs have arrived, and its output goes back on a third stream.
+    h2d, d2h = torch.cuda.Stream(), torch.cuda.Stream()
     main = torch.cuda.current_stream()
     row_caches = [attention.FBLACache(cache.coarse[b:b + 1], cache.fine[b:b + 1], cache.meta[b:b + 1], cache.sink_k[b:b + 1], cache.sink_v[b:b + 1],
                                       cache.open_k[b:b + 1], cache.open_v[b:b + 1], 0, S, cache.format) for b in range(nb)]
-    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    sets = [tuple(torch.empty_like(x) for x in (qd, kd, vd)) for _ in range(2)]
+    set_free = [None, None]  # the event after which a set's buffers may be overwritten
 
     def step_e2e(i):
+        dq, dk, dv = sets[i & 1]
         ready = []
-        copy_stream.wait_stream(main)
-        with torch.cuda.stream(copy_stream):
+        with torch.cuda.stream(h2d):
+            if set_free[i & 1] is not None:
+                h2d.wait_event(set_free[i & 1])
             for b in range(nb):
                 dq[b:b + 1].copy_(host[0][b:b + 1], non_blocking=True)
                 dk[b:b + 1].copy_(host[1][b:b + 1], non_blocking=True)
                 dv[b:b + 1].copy_(host[2][b:b + 1], non_blocking=True)
                 ev = torch.cuda.Event()
-                ev.record(copy_stream)
+                ev.record(h2d)
                 ready.append(ev)
         for b in range(nb):
             main.wait_event(ready[b])
             row_caches[b].tokens = 0
             o = attention.prefill(dq[b:b + 1], dk[b:b + 1], dv[b:b + 1], row_caches[b])
-            out_host[b:b + 1].copy_(o, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            o.record_stream(d2h)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(done)
+                out_host[b:b + 1].copy_(o, non_blocking=True)
+        set_free[i & 1] = torch.cuda.Event()
+        set_free[i & 1].record(main)
 
     ms_e2e, _, _ = timed_blocks(D, step_e2e, steps, 3)
     flops = 4.0 * 128 * B * QH * S * (S + 1) / 2
