@@ -177,19 +177,23 @@ extern "C" cudaError_t fbla_k_decode_shape(fbla_k_decode *a) {
 
 // How the coarse CTAs' warps share the work (see split_of, deal_of), from the tokens a row has at most:
 //   by the lengths when the BF16 windows would get three or more of a CTA's eight warps (contexts up to about 4 700 tokens);
-//   by cost -- every warp an equal share of windows and groups -- when that shortens a warp's work by more than the ~5 %
-//   that eight streaming warps lose against seven and a window warp: contexts from about 20K (3+3) / 34K (4+2) tokens
-//   (measured on B200, by cost against seven + one: batch 1 x 128K tokens 80.0 -> 75.3 us per step in 3+3 and 65.7 -> 61.6
-//   in 4+2, batch 64 x 1K..64K 2.07 -> 2.02 ms, but batch 8 x 16K 120.0 -> 123.9);
-//   seven streaming warps and one window warp per CTA between the two.
+//   else seven streaming warps and one window warp per CTA, or every warp an equal cost share of windows and groups --
+//   whichever leaves a streaming warp fewer groups, counted as the kernels deal them (whole groups per warp), with 5 %
+//   against the deal by cost: its eight streaming warps per CTA run a group that much slower than seven beside a window
+//   warp do. Measured on B200, by cost against seven + one: batch 1 x 128K tokens 80.0 -> 75.3 us per step in 3+3 and
+//   65.7 -> 61.6 in 4+2 (7 groups per warp instead of 8), batch 64 x 1K..64K 2.07 -> 2.02 ms, but batch 8 x 16K 120.0 ->
+//   123.9 (8 groups per warp either way).
 extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
   const int total = (a->cb == 4 ? fbla::CoarseShape<4>::TOTAL : fbla::CoarseShape<3>::TOTAL);
   const long long groups = (tokens + fbla::G - 1) / fbla::G, S = groups > 2 ? groups - 2 : 0;
   const long long W = groups <= 1 ? (tokens + fbla::S - 1) / fbla::S : 2 * fbla::SBG;  // (a full open window: the choice is monotone in tokens)
   const bool by_lengths = S == 0 || (2 * total * W + S + W) / (2 * (S + W)) >= 3;
-  const int wc = a->cb == 3 ? 6 : 10;  // (deal_of's cost of a window sub-block, a group's being 8)
+  const long long heads = (long long)a->batch * a->kv_heads * a->vg, ctas = a->coarse_ctas > 0 ? a->coarse_ctas : 148;
+  // groups a streaming warp takes: seven + one; by cost (deal_of's share, a whole number of groups)
+  const long long fixed = (heads * S + ctas * (total - 1) - 1) / (ctas * (total - 1));
+  const long long cost = (fbla::GROUP_COST * heads * S + fbla::WINDOW_COST * heads * W + fbla::GROUP_COST * ctas * total - 1) / (fbla::GROUP_COST * ctas * total);
   a->coarse_warps = total;
-  a->deal = by_lengths ? FBLA_K_DEAL_LENGTHS : 8 * S > 13 * wc * W ? FBLA_K_DEAL_COST : FBLA_K_DEAL_FIXED;
+  a->deal = by_lengths ? FBLA_K_DEAL_LENGTHS : 21 * cost < 20 * fixed ? FBLA_K_DEAL_COST : FBLA_K_DEAL_FIXED;
   // Folding the warps' partial rows per CTA costs the coarse pass a barrier and a few microseconds at its very end and saves
   // the later passes their walk over the rows: it pays when a virtual head is spread over many warps, i.e. when there are
   // few heads (measured on B200: batch 1 x 8 KV heads at 128K tokens -4.5 us per step, batch 8 x 8 heads at 16K +3 us).
@@ -199,6 +203,7 @@ extern "C" void fbla_k_decode_split(fbla_k_decode *a, long long tokens) {
 extern "C" void fbla_k_decode_split_of(int cb, int batch, int kv_heads, int vg, long long tokens, int *deal, int *fold) {
   fbla_k_decode a = {};
   a.cb = cb; a.batch = batch; a.kv_heads = kv_heads; a.vg = vg;
+  a.coarse_ctas = 148;  // (the shape of a B200; a caller with a device takes it from fbla_k_decode_shape)
   fbla_k_decode_split(&a, tokens);
   *deal = a.deal;
   *fold = a.fold;

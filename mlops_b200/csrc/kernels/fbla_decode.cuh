@@ -180,8 +180,9 @@ template <int CB> struct __align__(128) StreamWarp {
   int stage_vh[2];
 };
 struct __align__(16) ExactWarp {
-  float q[4][D];
-  uint8_t pst[4][16];
+  uint16_t q[8][D + 8];   // the virtual head's queries in BF16 (rows >= QG: zero); rows 272 bytes apart: 16-byte aligned, conflict-free
+  uint16_t v[S][D + 8];   // the sub-block's V rows
+  uint16_t p[8][S];       // P as BF16 integers: [query][token]
 };
 // (every warp has streaming buffers; a warp that serves windows keeps its ExactWarp in the buffers it does not stream
 // into yet, or at all)
@@ -198,28 +199,29 @@ static_assert(sizeof(ExactWarp) <= sizeof(StreamWarp<3>) && sizeof(ExactWarp) <=
 // written.
 // Split by the lengths (short contexts, FBLA_K_DEAL_LENGTHS): of a CTA's warps the last xw serve windows and the others stream, and
 // each kind's units are dealt in equal contiguous runs over its warps of all CTAs. xw is the windows' share of all units
-// (at these lengths one unit of either kind costs a warp about the same time), at least one warp for the windows and one
-// for the groups if there are any. The host asks for it when the windows are a large part of the work: short contexts
+// by cost (a sub-block 3 eighths of a group at these lengths), at least one warp for the windows and one for the groups
+// if there are any. The host asks for it when the windows are a large part of the work: short contexts
 // at large batch (batch 256 x 512 tokens: 638 -> 352 us per step, batch 32 x 4096: 182 -> 166).
 //
 // FBLA_K_DEAL_FIXED (contexts in between): the same with xw = 1, whatever the lengths.
 //
 // FBLA_K_DEAL_COST (long contexts): no warp is set aside. All units form one list, window sub-blocks first, then the groups, each
-// with a cost in eighths of a group's time. A window sub-block costs 6 beside 3-bit groups and 10 beside 4-bit ones:
-// measured, batch 1 x 128K tokens, us per step for costs 4 / 5 / 6 / 7 / 8 in 3+3: 81.3 / 72.2 / 72.1 / 71.3 / 72.7, for
-// 5 / 6 / 8 / 10 / 12 / 14 in 4+2: 72.8 / 70.1 / 61.7 / 59.6 / 61.4 / 59.7 (a CTA whose eight warps all serve windows
-// runs them slower than one window warp among streaming ones, and 4-bit groups are the faster ones). Every warp of the
-// grid takes the units whose cost interval starts inside its equal share [w P, (w + 1) P) of the total, serves its
-// window sub-blocks and then streams its groups. A share is at least one unit's cost, so consecutive units lie in the
-// same or in consecutive warps. At batch 1 and 128K tokens a warp then streams 7 groups instead of 8.
+// with a cost in eighths of a group's time: a window sub-block, on its BF16 tensor-core products, costs half a group
+// (measured, batch 1 x 128K tokens, us per step with costs 2 / 3 / 4 / 6 / 10: 3+3 67.9 / 69.8 / 66.0 / 66.3 / -, 4+2
+// 64.6 / 60.6 / 55.9 / - / 59.3; what matters most is that a share is a whole number of groups: with 57 instead of 56
+// eighths one warp in eight streams 8 groups instead of 7). Every warp of the grid takes the units whose cost interval
+// starts inside its equal share [w P, (w + 1) P) of the total, serves its window sub-blocks and then streams its
+// groups. A share is at least one unit's cost, so consecutive units lie in the same or in consecutive warps. At batch 1
+// and 128K tokens a warp then streams 7 groups instead of 8.
 struct Deal { long long S, X, P; int wc; };  // groups, window sub-blocks, cost share per warp, cost of a window sub-block
-constexpr int GROUP_COST = 8;
+constexpr int GROUP_COST = 8, WINDOW_COST = 4, WINDOW_COST_SHORT = 3;  // a warp's time for a group / a window sub-block, in eighths of a group
 __device__ __forceinline__ Deal deal_of(const fbla_k_decode &a, int hpr) {
   Deal d;
   d.S = total_units<false>(a, hpr);
   d.X = total_units<true>(a, hpr);
-  d.wc = a.cb == 3 ? 6 : 10;
-  d.P = max((long long)max(GROUP_COST, d.wc), ceil_div(GROUP_COST * d.S + d.wc * d.X, (long long)a.coarse_ctas * a.coarse_warps));
+  d.wc = WINDOW_COST;
+  // (a whole number of groups per share: every streaming warp then takes the same number of groups)
+  d.P = GROUP_COST * max(1ll, ceil_div(GROUP_COST * d.S + d.wc * d.X, (long long)GROUP_COST * a.coarse_ctas * a.coarse_warps));
   return d;
 }
 // the units of warp w: window sub-blocks [xlo, xhi), groups [lo, hi)
@@ -233,7 +235,7 @@ struct Split { int sw, xw; };  // streaming / window warps per CTA
 __device__ __forceinline__ Split split_of(const fbla_k_decode &a, int hpr) {
   const int total = (a.cb == 4 ? FBLA_CW4 : FBLA_CW3) + 1;
   if (a.deal == FBLA_K_DEAL_FIXED) return Split{total - 1, 1};
-  const long long S = total_units<false>(a, hpr), W = total_units<true>(a, hpr);
+  const long long S = GROUP_COST * total_units<false>(a, hpr), W = WINDOW_COST_SHORT * total_units<true>(a, hpr);  // in eighths of a group's time
   const int xw = S == 0 ? total : max(1, min(total - 1, (int)((2 * total * W + S + W) / (2 * (S + W)))));
   return Split{total - xw, xw};
 }
@@ -248,131 +250,137 @@ __device__ __forceinline__ void report(const fbla_k_decode &a, int pass) {
 }
 
 // ---- the BF16 windows ---------------------------------------------------------------------------------------------------
-// Unit = one 16-token sub-block of the sink (first) or the open window. Scores s = sl * (q . k) in FP32, the same
-// integer P block, values in FP32. Lane (t = lane % 16, h = lane / 16) scores token t over channels 64 h .. 64 h + 63;
-// for the values lane l owns channels 4 l .. 4 l + 3.
-// one window sub-block's rows in registers: the lane's 64 channels of its token's K row, and its 4 channels of all 16 V rows
+// Unit = one 16-token sub-block of the sink (first) or the open window, on BF16 tensor-core products with FP32 sums:
+//   S^T[16 tokens x 8 queries] = K[16 x 128] Q^T        (mma.sync m16n8k16, 8 steps over the channels)
+//   O^T[128 channels x 8 queries] += V^T[128 x 16] P^T  (8 tiles of 16 channels; P: the same integer block, exact in BF16)
+// Scores s = sl * (q . k): BF16 products are exact in FP32, so only the order of the sums differs from a chain of FMAs.
+// Thread (gid, tig) of a product holds rows gid, gid + 8 and columns 2 tig, 2 tig + 1 of its result. The channels are
+// taken in the order that lets a lane load 16 bytes of a K row (its 8 channels of a 32-channel round serve two steps);
+// the query fragments use the same order. V^T fragments come from shared memory through ldmatrix.trans.
+__device__ __forceinline__ void mma_bf16_k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(row)) : "memory");
+}
+// one window sub-block's rows in registers: 16 bytes of the K rows of tokens gid and gid + 8 per 32-channel round, and the
+// lane's share of the 16 V rows (256 x 16 bytes over the warp)
 struct WindowTile {
-  uint4 k[8];
-  uint2 v[16];
-  int j, count;  // sub-block within its window, the window's token count
+  uint4 ka[4], kb[4];
+  uint4 v[8];
+  int count;  // attended tokens of the sub-block (1 .. 16)
 };
-// AHEAD: the next sub-block's loads are issued before the current one is computed (two tiles of registers); without it
-// a warp that shares its CTA with many others stays within their register budget.
 // the window sub-blocks [lo, hi) of the flattened list; the partial rows go to window slot xw + virtual head
-template <int QG, bool AHEAD = true>
+template <int QG>
 __device__ void exact_range(const fbla_k_decode &a, ExactWarp &sm, int lane, long long lo, long long hi, int xw) {
   const int hpr = a.kv_heads * a.vg;
   if (lo >= hi) return;
   const int slot0 = a.coarse_ctas * a.coarse_warps + a.batch * hpr;  // after the coarse slots
-  const int t = lane & 15, h = lane >> 4;
+  const int gid = lane >> 2, tig = lane & 3;
   Cursor c = locate<true>(a, hpr, lo);
   int cur_vh = -1;
-  float m[QG], l[QG], o[QG][4];
+  float m[2], l[2], o[8][4];  // queries 2 tig + e; o[tile]: channels 16 tile + gid (.0, .1), + 8 (.2, .3) x the two queries
   auto flush = [&]() {
     float *p = a.part + (size_t)(slot0 + xw + cur_vh) * QG * PSTRIDE;
 #pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      *reinterpret_cast<float4 *>(p + qi * PSTRIDE + 4 * lane) = make_float4(o[qi][0], o[qi][1], o[qi][2], o[qi][3]);
-      if (!lane) { p[qi * PSTRIDE + D] = m[qi]; p[qi * PSTRIDE + D + 1] = l[qi]; }
+    for (int e = 0; e < 2; ++e) {
+      const int qi = 2 * tig + e;
+      if (qi < QG) {
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+          p[qi * PSTRIDE + 16 * mt + gid] = o[mt][e];
+          p[qi * PSTRIDE + 16 * mt + gid + 8] = o[mt][2 + e];
+        }
+        if (gid == 0) { p[qi * PSTRIDE + D] = m[e]; p[qi * PSTRIDE + D + 1] = l[e]; }
+      }
     }
   };
   // all loads of a sub-block at once (the next sub-block's are issued before the current one is computed)
   auto load = [&](const Cursor &cu, WindowTile &w) {
     const Row r = row_of(a, cu.b);
     const bool sink = cu.i < r.na;
-    w.j = sink ? cu.i : cu.i - r.na;
-    w.count = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
+    const int j = sink ? cu.i : cu.i - r.na;  // sub-block within its window
+    const int window = sink ? (r.groups == 1 ? r.tokens : G) : r.tokens - G * (r.groups - 1);
+    w.count = min(window - j * S, S);
     const size_t eh = (size_t)((cu.b * hpr + cu.hir) / a.vg) * G * D;
-    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh;
-    const int tok = w.j * S + t;
-    const uint4 *kp = reinterpret_cast<const uint4 *>(ek + (size_t)min(tok, G - 1) * D + 64 * h);
+    const uint16_t *ek = (sink ? a.c.sink_k : a.c.open_k) + eh + (size_t)j * S * D, *ev = (sink ? a.c.sink_v : a.c.open_v) + eh + (size_t)j * S * D;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) w.k[i] = tok < w.count ? __ldcg(kp + i) : make_uint4(0u, 0u, 0u, 0u);
+    for (int r4 = 0; r4 < 4; ++r4) {  // channels 32 r4 + 8 tig .. + 7 of tokens gid, gid + 8
+      w.ka[r4] = gid < w.count ? __ldcg(reinterpret_cast<const uint4 *>(ek + (size_t)gid * D + 32 * r4 + 8 * tig)) : zero;
+      w.kb[r4] = gid + 8 < w.count ? __ldcg(reinterpret_cast<const uint4 *>(ek + (size_t)(gid + 8) * D + 32 * r4 + 8 * tig)) : zero;
+    }
 #pragma unroll
-    for (int tt = 0; tt < S; ++tt)
-      w.v[tt] = w.j * S + tt < w.count ? __ldcg(reinterpret_cast<const uint2 *>(ev + (size_t)(w.j * S + tt) * D) + lane) : make_uint2(0u, 0u);
+    for (int i = 0; i < 8; ++i) {  // 16-byte piece 32 i + lane of the 16 x 256 bytes: row (32 i + lane) / 16
+      const int row = 2 * i + (lane >> 4);
+      w.v[i] = row < w.count ? __ldcg(reinterpret_cast<const uint4 *>(ev + (size_t)row * D) + (lane & 15)) : zero;
+    }
   };
+  for (int i = lane; i < 8 * (D + 8) / 2; i += 32) reinterpret_cast<uint32_t *>(&sm.q[0][0])[i] = 0u;
   WindowTile cur, nxt;
-  if (AHEAD) load(c, cur);
+  load(c, cur);
   for (long long u = lo; u < hi; ++u) {
-    if (!AHEAD) load(c, cur);
     const int vh = c.b * hpr + c.hir;
     if (vh != cur_vh) {
       if (cur_vh >= 0) flush();
       cur_vh = vh;
       __syncwarp();
 #pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const uint2 w = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, c.b, c.hir, qi) * D) + lane);
-        *reinterpret_cast<float4 *>(&sm.q[qi][4 * lane]) = make_float4(bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y));
-        m[qi] = -FBLA_INF; l[qi] = 0.f;
-        o[qi][0] = o[qi][1] = o[qi][2] = o[qi][3] = 0.f;
-      }
-      __syncwarp();
+      for (int qi = 0; qi < QG; ++qi)
+        *reinterpret_cast<uint2 *>(&sm.q[qi][4 * lane]) = __ldg(reinterpret_cast<const uint2 *>(a.q + (size_t)q_row(a, c.b, c.hir, qi) * D) + lane);
+      m[0] = m[1] = -FBLA_INF; l[0] = l[1] = 0.f;
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
     }
+    __syncwarp();  // (the queries are in place; the previous sub-block's V rows and P have been read)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4 *>(&sm.v[2 * i + (lane >> 4)][8 * (lane & 15)]) = cur.v[i];
+    // scores
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r4 = 0; r4 < 4; ++r4) {
+      const uint4 qq = *reinterpret_cast<const uint4 *>(&sm.q[gid][32 * r4 + 8 * tig]);
+      mma_bf16_k16(x, cur.ka[r4].x, cur.kb[r4].x, cur.ka[r4].y, cur.kb[r4].y, qq.x, qq.y);
+      mma_bf16_k16(x, cur.ka[r4].z, cur.kb[r4].z, cur.ka[r4].w, cur.kb[r4].w, qq.z, qq.w);
+    }
+    const int count = cur.count;
     advance<true>(a, hpr, c);
-    if (AHEAD && u + 1 < hi) load(c, nxt);
-    const int tok = cur.j * S + t;
-    float x[QG];
+    if (u + 1 < hi) load(c, nxt);
+    // x[2 r + e]: token gid + 8 r, query 2 tig + e
+    float al[2], w[2];
 #pragma unroll
-    for (int qi = 0; qi < QG; ++qi) x[qi] = 0.f;
+    for (int e = 0; e < 2; ++e) {
+      const float s0 = gid < count ? __fmul_rn(x[e], a.sl) : -FBLA_INF, s1 = gid + 8 < count ? __fmul_rn(x[2 + e], a.sl) : -FBLA_INF;
+      float mb = fmaxf(s0, s1);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 w = cur.k[i];
-      const float kv[8] = {bf_lo(w.x), bf_hi(w.x), bf_lo(w.y), bf_hi(w.y), bf_lo(w.z), bf_hi(w.z), bf_lo(w.w), bf_hi(w.w)};
+      for (int off = 4; off <= 16; off <<= 1) mb = fmaxf(mb, __shfl_xor_sync(FULL, mb, off));
+      const float mn = fmaxf(m[e], mb);
+      al[e] = ex2(m[e] - mn); w[e] = ex2(mb - mn);  // (2^-inf = 0; mb is finite: token 0 of a unit always exists)
+      m[e] = mn;
+      // the integer p as an exact float: (p + 1.5 * 2^23) - 1.5 * 2^23; its BF16 form is its upper half
+      const float p0 = fmaf(ex2(s0 - mb), 255.f, MAGICF) - MAGICF, p1 = fmaf(ex2(s1 - mb), 255.f, MAGICF) - MAGICF;
+      sm.p[2 * tig + e][gid] = (uint16_t)(__float_as_uint(p0) >> 16);
+      sm.p[2 * tig + e][gid + 8] = (uint16_t)(__float_as_uint(p1) >> 16);
+      float sp = p0 + p1;
 #pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        const float4 qa = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i]), qb = *reinterpret_cast<const float4 *>(&sm.q[qi][64 * h + 8 * i + 4]);
-        x[qi] = fmaf(qa.x, kv[0], x[qi]); x[qi] = fmaf(qa.y, kv[1], x[qi]); x[qi] = fmaf(qa.z, kv[2], x[qi]); x[qi] = fmaf(qa.w, kv[3], x[qi]);
-        x[qi] = fmaf(qb.x, kv[4], x[qi]); x[qi] = fmaf(qb.y, kv[5], x[qi]); x[qi] = fmaf(qb.z, kv[6], x[qi]); x[qi] = fmaf(qb.w, kv[7], x[qi]);
-      }
-    }
-    float al[QG], w[QG], sp[QG];
-    uint32_t P[QG][4];
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      x[qi] += __shfl_xor_sync(FULL, x[qi], 16);
-      const float s = tok < cur.count ? __fmul_rn(x[qi], a.sl) : -FBLA_INF;
-      float mb = s;
-#pragma unroll
-      for (int off = 8; off; off >>= 1) mb = fmaxf(mb, __shfl_xor_sync(FULL, mb, off));
-      const float mn = fmaxf(m[qi], mb);
-      al[qi] = ex2(m[qi] - mn); w[qi] = ex2(mb - mn);  // (2^-inf = 0; mb is finite: token 0 of a unit always exists)
-      m[qi] = mn;
-      const uint32_t pbits = __float_as_uint(fmaf(ex2(s - mb), 255.f, MAGICF));
-      if (lane < 16) sm.pst[qi][t] = (uint8_t)pbits;
+      for (int off = 4; off <= 16; off <<= 1) sp += __shfl_xor_sync(FULL, sp, off);
+      l[e] = fmaf(al[e], l[e], w[e] * sp);
     }
     __syncwarp();
+    // values: P^T fragments (tokens 2 tig, 2 tig + 1 and + 8 of query gid), V^T fragments per 16-channel tile
+    const uint32_t pb0 = *reinterpret_cast<const uint32_t *>(&sm.p[gid][2 * tig]), pb1 = *reinterpret_cast<const uint32_t *>(&sm.p[gid][2 * tig + 8]);
 #pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      const uint4 pw = *reinterpret_cast<const uint4 *>(sm.pst[qi]);
-      P[qi][0] = pw.x; P[qi][1] = pw.y; P[qi][2] = pw.z; P[qi][3] = pw.w;
-      sp[qi] = (float)(__dp4a(pw.x, 0x01010101u, 0u) + __dp4a(pw.y, 0x01010101u, 0u) + __dp4a(pw.z, 0x01010101u, 0u) + __dp4a(pw.w, 0x01010101u, 0u));
+    for (int mt = 0; mt < 8; ++mt) {
+      uint32_t va[4];  // matrices: (tokens 0-7, channels 16 mt ..), (0-7, + 8), (8-15, ..), (8-15, + 8)
+      ldmatrix_x4_trans(va, &sm.v[8 * (lane >> 4) + (lane & 7)][16 * mt + 8 * ((lane >> 3) & 1)]);
+      float y[4] = {0.f, 0.f, 0.f, 0.f};
+      mma_bf16_k16(y, va[0], va[1], va[2], va[3], pb0, pb1);
+      o[mt][0] = fmaf(al[0], o[mt][0], w[0] * y[0]); o[mt][1] = fmaf(al[1], o[mt][1], w[1] * y[1]);
+      o[mt][2] = fmaf(al[0], o[mt][2], w[0] * y[2]); o[mt][3] = fmaf(al[1], o[mt][3], w[1] * y[3]);
     }
-    float y[QG][4];
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) y[qi][0] = y[qi][1] = y[qi][2] = y[qi][3] = 0.f;
-#pragma unroll
-    for (int tt = 0; tt < S; ++tt) {
-      const uint2 vw = cur.v[tt];
-      const float vv[4] = {bf_lo(vw.x), bf_hi(vw.x), bf_lo(vw.y), bf_hi(vw.y)};
-#pragma unroll
-      for (int qi = 0; qi < QG; ++qi) {
-        // the byte as a float without a conversion instruction: the bits of 2^23 + p, minus 2^23
-        const float p = __uint_as_float(0x4B000000u | ((P[qi][tt >> 2] >> (8 * (tt & 3))) & 255u)) - 8388608.f;
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) y[qi][cc] = fmaf(p, vv[cc], y[qi][cc]);
-      }
-    }
-#pragma unroll
-    for (int qi = 0; qi < QG; ++qi) {
-      l[qi] = fmaf(al[qi], l[qi], w[qi] * sp[qi]);
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) o[qi][cc] = fmaf(al[qi], o[qi][cc], w[qi] * y[qi][cc]);
-    }
-    __syncwarp();
-    if (AHEAD) cur = nxt;
+    cur = nxt;
   }
   flush();
 }

@@ -28,22 +28,22 @@ def split_of(lib, cb, batch, kv_heads, vg, tokens):
 
 
 @pytest.mark.parametrize("cb", [3, 4])
-def test_the_deal_is_monotone_in_the_token_count(lib, cb):
-    """Short rows: by the lengths; long ones: by cost; one window warp per CTA in between. The choice never goes back as
-    the rows grow (decode and decode_at of one cache must agree on it, and it is made from a ceiling)."""
-    seen = []
-    for tokens in list(range(1, 600, 7)) + list(range(600, 70000, 128)) + [131072, 262144, 1 << 20, 1 << 26]:
-        deal, _ = split_of(lib, cb, 1, 8, 1, tokens)
-        assert deal in (LENGTHS, FIXED, COST)
-        seen.append((tokens, deal))
-    deals = [d for _, d in seen]
-    assert deals == sorted(deals), "the regimes follow one another: lengths, fixed, cost"
-    first = {d: min(t for t, x in seen if x == d) for d in (LENGTHS, FIXED, COST)}
-    assert first[LENGTHS] == 1
-    assert 4000 <= first[FIXED] <= 5500            # about 4 700 tokens
-    assert (18000 if cb == 3 else 30000) <= first[COST] <= (23000 if cb == 3 else 37000)
-    assert split_of(lib, cb, 1, 8, 1, 131072)[0] == COST and split_of(lib, cb, 8, 8, 1, 16384)[0] == FIXED
-    assert split_of(lib, cb, 1, 8, 2, 4096)[0] == LENGTHS
+def test_the_deal_follows_the_groups_a_warp_would_stream(lib, cb):
+    """Short rows: by the lengths. Beyond: seven + one or by cost, whichever leaves a streaming warp fewer whole groups
+    (counted for 148 CTAs of eight warps), with 5 % against the deal by cost."""
+    for tokens in list(range(1, 4000, 97)):
+        assert split_of(lib, cb, 1, 8, 1, tokens)[0] == LENGTHS
+    assert split_of(lib, cb, 256, 8, 1, 512)[0] == LENGTHS and split_of(lib, cb, 1, 8, 2, 4096)[0] == LENGTHS
+    for tokens in list(range(6000, 70000, 128)) + [131072, 262144, 1 << 20, 1 << 26]:
+        for batch in (1, 8, 64):
+            deal, _ = split_of(lib, cb, batch, 8, 1, tokens)
+            heads, S = batch * 8, (tokens + 127) // 128 - 2
+            fixed = -(-heads * S // (148 * 7))
+            cost = -(-(8 * heads * S + 4 * heads * 16) // (8 * 148 * 8))
+            assert deal == (COST if 21 * cost < 20 * fixed else FIXED), (tokens, batch, fixed, cost)
+    assert split_of(lib, cb, 1, 8, 1, 131072)[0] == COST    # 7 groups per warp instead of 8
+    assert split_of(lib, cb, 8, 8, 1, 16384)[0] == FIXED    # 8 either way
+    assert split_of(lib, cb, 64, 8, 1, 65280)[0] == COST
 
 
 def test_rows_are_folded_per_cta_for_few_heads_only(lib):
