@@ -58,7 +58,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from the ncu captures summarised
 # under profiles/ (1 GPU); reported with their source, never as a measurement of the run that prints them
 NCU_TRAFFIC = {
-    "decode_128k": dict(kernel="coarse_kernel<3,3,4,2>", bytes=113178368, file="profiles/decode_b1_ctx128k_3p3_launches.md"),
+    "decode_128k": dict(kernel="coarse_kernel<3,3,4,2>", bytes=113223424, file="profiles/decode_b1_ctx128k_3p3_launches.md"),
     "decode_b8": dict(kernel="refine_kernel<4,2,4>", bytes=164004352, file="profiles/decode_b8_ctx16k_4p2_launches.md"),
 }
 SUBS = ["decode_128k_4p2", "decode_b8", "prefill_b4", "serving_b64"]
