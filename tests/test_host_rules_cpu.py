@@ -68,3 +68,20 @@ def test_bench_accounts_the_bytes_the_way_the_reference_bench_does():
     assert parts["bf16_windows"] == 8 * 256 * 512 and total == parts["coarse_and_meta"] + parts["bf16_windows"]
     total, parts = bench.decode_bytes(dict(batch=8, kv_heads=8, tokens=16384, mode="4+2"), 0.5)
     assert parts["coarse_and_meta"] == 64 * 126 * (8 * 2048 + 1024) and parts["refine"] == 0.5 * 64 * 126 * 8 * 3072
+
+
+def test_reference_arm_prints_the_contract_line_without_a_gpu():
+    """`bench.py --impl reference` is the oracle's port of the reference's host model on the host cores: it needs no GPU,
+    and its one JSON line carries the keys the measurement contract names."""
+    import json
+    import subprocess
+    run = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [l for l in run.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "decode_tokens_per_s" and d["unit"] == "tokens/s" and d["higher_is_better"] is True
+    assert d["config"]["tokens"] == 131072 and d["config"]["mode"] == "3+3" and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == dict(value=d["value"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0)
